@@ -1,0 +1,314 @@
+// Sequential state scan fused with the output stage.
+//
+// One CTA per (sequence, head, half of the value columns). Four consumer warps each own 16 value
+// columns of the fp32 state, held TRANSPOSED in mma.sync accumulator registers (S^T: 16 x 128 per
+// warp) for the whole sequence: because the accumulator fragment of one m16n8k16 MMA is exactly the
+// A fragment of the next, the chain
+//     v_new^T = u^T - S^T w^T ;  o^T = S^T qg^T + v_new^T Aqk^T ;  S^T <- S^T diag(decay) + v_new^T kg
+// runs without the state ever leaving registers and without any cross-warp synchronisation. A fifth
+// warp is the producer: it streams the per-chunk tile packs through a 3-stage shared-memory ring
+// with bulk (TMA-engine) copies signalled on mbarriers.
+//
+// Replaces chunk_gated_delta_rule_fwd_h (cula/ops/chunk_delta_h.py:1991-2168) and chunk_gla_fwd_o
+// (cula/ops/fwd_o.py:1755-1852); the per-chunk states h and v_new only go to HBM when the caller
+// asks for them (backward recomputation, return_intermediate_states).
+#include "kda_common.cuh"
+#include "kda_params.h"
+
+namespace kda {
+
+constexpr int SCAN_STAGES = 3;
+constexpr int SCAN_STAGE_BYTES = TP_HEAD_BYTES + 8192;   // W,QG,KG,AQK,DECAY + one U half = 66048
+constexpr int SCAN_STG_BYTES = 4096;                     // per-warp staging for coalesced stores
+constexpr int SCAN_CONSUMERS = 4;
+constexpr int SCAN_THREADS = (SCAN_CONSUMERS + 1) * 32;
+constexpr int SCAN_SMEM = SCAN_STAGES * SCAN_STAGE_BYTES + SCAN_CONSUMERS * SCAN_STG_BYTES + 64;
+constexpr int ST_U = TP_HEAD_BYTES;                      // offset of the U half inside a stage
+
+template <bool STORE_HV>
+__global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const ScanParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + SCAN_STAGES * SCAN_STAGE_BYTES + SCAN_CONSUMERS * SCAN_STG_BYTES);
+    uint64_t* empty = full + SCAN_STAGES;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int vh = blockIdx.x, h = blockIdx.y;
+    const int n = p.seq_order ? p.seq_order[blockIdx.z] : blockIdx.z;
+    int bos, len, chunk0;
+    if (p.cu_seqlens) {
+        bos = p.cu_seqlens[n];
+        len = p.cu_seqlens[n + 1] - bos;
+        chunk0 = p.chunk_offsets[n];
+    } else {
+        bos = n * p.T;
+        len = p.T;
+        chunk0 = n * ((p.T + BT - 1) / BT);
+    }
+    const int nchunks = (len + BT - 1) / BT;
+
+    if (tid == 0) {
+        for (int s = 0; s < SCAN_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], SCAN_CONSUMERS);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == SCAN_CONSUMERS) {
+        // ------------------------------- producer warp -------------------------------
+        if (lane == 0) {
+            for (int c = 0; c < nchunks; ++c) {
+                const int s = c % SCAN_STAGES, use = c / SCAN_STAGES;
+                if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
+                    atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+                    break;
+                }
+                const unsigned char* tile = p.tiles + ((size_t)(chunk0 + c) * p.H + h) * TP_BYTES;
+                unsigned char* dst = smem + s * SCAN_STAGE_BYTES;
+                mbar_arrive_expect_tx(&full[s], SCAN_STAGE_BYTES);
+                bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
+                bulk_g2s(dst + ST_U, tile + (vh ? TP_U1 : TP_U0), 8192, &full[s]);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------- consumer warps ----------------------------------
+    const int g = lane >> 2, t = lane & 3;
+    const int m = lane >> 3, r = lane & 7;          // ldmatrix/stmatrix: matrix index, row inside it
+    const int vb = vh * 64 + warp * 16;             // first value column of this warp
+    unsigned char* stg = smem + SCAN_STAGES * SCAN_STAGE_BYTES + warp * SCAN_STG_BYTES;
+    const uint32_t stg_u32 = smem_u32(stg);
+
+    float S[16][4];
+    if (p.h0) {
+        const float* h0 = p.h0 + ((size_t)n * p.H + h) * DK * DV;
+#pragma unroll
+        for (int jt = 0; jt < 16; ++jt) {
+            int k0 = 8 * jt + 2 * t;
+            S[jt][0] = h0[(size_t)k0 * DV + vb + g];
+            S[jt][1] = h0[(size_t)(k0 + 1) * DV + vb + g];
+            S[jt][2] = h0[(size_t)k0 * DV + vb + g + 8];
+            S[jt][3] = h0[(size_t)(k0 + 1) * DV + vb + g + 8];
+        }
+    } else {
+#pragma unroll
+        for (int jt = 0; jt < 16; ++jt) S[jt][0] = S[jt][1] = S[jt][2] = S[jt][3] = 0.f;
+    }
+
+    // per-lane swizzled column-group offsets for the four k-step pairs of a 256-byte-row operand
+    uint32_t x256[4];
+#pragma unroll
+    for (int kp = 0; kp < 4; ++kp) x256[kp] = (uint32_t)(((4 * kp + m) ^ r) << 4);
+
+    for (int c = 0; c < nchunks; ++c) {
+        const int s = c % SCAN_STAGES;
+        if (!mbar_wait(&full[s], (c / SCAN_STAGES) & 1)) {
+            atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+            return;
+        }
+        const uint32_t st = smem_u32(smem + s * SCAN_STAGE_BYTES);
+        const int valid = min(BT, len - c * BT);
+        const size_t tile_idx = (size_t)(chunk0 + c) * p.H + h;
+
+        // ---- S as fp16 A fragments (8 k-steps over the 128 key channels), scaled by a per-warp power
+        //      of two so that the largest entry sits near 2^13: fp16 then carries 11 significant bits
+        //      whatever the magnitude of the state, and cannot overflow ----
+        float smax = 0.f;
+#pragma unroll
+        for (int jt = 0; jt < 16; ++jt)
+            smax = fmaxf(smax, fmaxf(fmaxf(fabsf(S[jt][0]), fabsf(S[jt][1])), fmaxf(fabsf(S[jt][2]), fabsf(S[jt][3]))));
+#pragma unroll
+        for (int o = 16; o; o >>= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+        int shift = 13 - (((__float_as_int(smax) >> 23) & 0xff) - 127);
+        shift = max(-100, min(100, shift));
+        const float s_up = __int_as_float((shift + 127) << 23), s_down = __int_as_float((127 - shift) << 23);
+        uint32_t sa[8][4];
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            sa[ks][0] = pack_f16(S[2 * ks][0] * s_up, S[2 * ks][1] * s_up);
+            sa[ks][1] = pack_f16(S[2 * ks][2] * s_up, S[2 * ks][3] * s_up);
+            sa[ks][2] = pack_f16(S[2 * ks + 1][0] * s_up, S[2 * ks + 1][1] * s_up);
+            sa[ks][3] = pack_f16(S[2 * ks + 1][2] * s_up, S[2 * ks + 1][3] * s_up);
+        }
+        if (STORE_HV) {
+            // incoming state of this chunk, bf16 [128 k][128 v]; this warp owns a 32-byte column slice
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                int krow = 8 * (2 * ks + (m >> 1)) + r;
+                stsm_x4_t(stg_u32 + krow * 32 + (m & 1) * 16,
+                          pack_bf16(S[2 * ks][0], S[2 * ks][1]), pack_bf16(S[2 * ks][2], S[2 * ks][3]),
+                          pack_bf16(S[2 * ks + 1][0], S[2 * ks + 1][1]), pack_bf16(S[2 * ks + 1][2], S[2 * ks + 1][3]));
+            }
+            __syncwarp();
+            unsigned char* hg = reinterpret_cast<unsigned char*>(p.h_out) + tile_idx * (size_t)(DK * DV * 2);
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                int row = it * 16 + (lane >> 1), hf = lane & 1;
+                uint4 val = *reinterpret_cast<const uint4*>(stg + row * 32 + hf * 16);
+                *reinterpret_cast<uint4*>(hg + (size_t)row * 256 + vb * 2 + hf * 16) = val;
+            }
+            __syncwarp();
+        }
+
+        // ---- acc = S^T w^T : [16 v] x [64 tokens], contraction over 128 key channels ----
+        float acc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+        for (int kp = 0; kp < 4; ++kp) {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(st + TP_W + (8 * nt + r) * 256 + x256[kp], b0, b1, b2, b3);
+                mma_f16(acc[nt], sa[2 * kp], b0, b1);
+                mma_f16(acc[nt], sa[2 * kp + 1], b2, b3);
+            }
+        }
+        // ---- v_new^T = u^T - acc ----
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            uint32_t r0, r1, r2, r3;
+            int row = 8 * (2 * np + (m >> 1)) + r, ch = 2 * warp + (m & 1);
+            ldsm_x4_t(st + ST_U + row * 128 + ((ch ^ r) << 4), r0, r1, r2, r3);
+            float2 f;
+            f = unpack_f16(r0); acc[2 * np][0] = fmaf(-s_down, acc[2 * np][0], f.x); acc[2 * np][1] = fmaf(-s_down, acc[2 * np][1], f.y);
+            f = unpack_f16(r1); acc[2 * np][2] = fmaf(-s_down, acc[2 * np][2], f.x); acc[2 * np][3] = fmaf(-s_down, acc[2 * np][3], f.y);
+            f = unpack_f16(r2); acc[2 * np + 1][0] = fmaf(-s_down, acc[2 * np + 1][0], f.x); acc[2 * np + 1][1] = fmaf(-s_down, acc[2 * np + 1][1], f.y);
+            f = unpack_f16(r3); acc[2 * np + 1][2] = fmaf(-s_down, acc[2 * np + 1][2], f.x); acc[2 * np + 1][3] = fmaf(-s_down, acc[2 * np + 1][3], f.y);
+        }
+        uint32_t va[4][4];   // v_new^T as fp16 A fragments (4 k-steps over the 64 tokens)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            va[ks][0] = pack_f16(acc[2 * ks][0], acc[2 * ks][1]);
+            va[ks][1] = pack_f16(acc[2 * ks][2], acc[2 * ks][3]);
+            va[ks][2] = pack_f16(acc[2 * ks + 1][0], acc[2 * ks + 1][1]);
+            va[ks][3] = pack_f16(acc[2 * ks + 1][2], acc[2 * ks + 1][3]);
+        }
+        if (STORE_HV) {
+            // v_new, fp16 [64 tokens][128 v]
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                int trow = 8 * (2 * ks + (m >> 1)) + r;
+                stsm_x4_t(stg_u32 + trow * 32 + (m & 1) * 16, va[ks][0], va[ks][1], va[ks][2], va[ks][3]);
+            }
+            __syncwarp();
+            unsigned char* vg = reinterpret_cast<unsigned char*>(p.vnew_out) + tile_idx * (size_t)(BT * DV * 2);
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                int row = it * 16 + (lane >> 1), hf = lane & 1;
+                uint4 val = *reinterpret_cast<const uint4*>(stg + row * 32 + hf * 16);
+                *reinterpret_cast<uint4*>(vg + (size_t)row * 256 + vb * 2 + hf * 16) = val;
+            }
+            __syncwarp();
+        }
+
+        // ---- o^T = S^T qg^T + v_new^T Aqk^T ----
+        {
+            float oacc[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) oacc[nt][0] = oacc[nt][1] = oacc[nt][2] = oacc[nt][3] = 0.f;
+#pragma unroll
+            for (int kp = 0; kp < 4; ++kp) {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(st + TP_QG + (8 * nt + r) * 256 + x256[kp], b0, b1, b2, b3);
+                    mma_f16(oacc[nt], sa[2 * kp], b0, b1);
+                    mma_f16(oacc[nt], sa[2 * kp + 1], b2, b3);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                oacc[nt][0] *= s_down; oacc[nt][1] *= s_down; oacc[nt][2] *= s_down; oacc[nt][3] *= s_down;
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int ksp = 0; ksp < 2; ++ksp) {
+                    if (32 * ksp <= 8 * nt + 7) {      // causal: skip column blocks right of the diagonal
+                        uint32_t b0, b1, b2, b3;
+                        ldsm_x4(st + TP_AQK + (8 * nt + r) * 128 + (((4 * ksp + m) ^ r) << 4), b0, b1, b2, b3);
+                        mma_f16(oacc[nt], va[2 * ksp], b0, b1);
+                        if (32 * ksp + 16 <= 8 * nt + 7) mma_f16(oacc[nt], va[2 * ksp + 1], b2, b3);
+                    }
+                }
+            }
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                int trow = 8 * (2 * np + (m >> 1)) + r;
+                stsm_x4_t(stg_u32 + trow * 32 + (m & 1) * 16,
+                          pack_bf16(oacc[2 * np][0], oacc[2 * np][1]), pack_bf16(oacc[2 * np][2], oacc[2 * np][3]),
+                          pack_bf16(oacc[2 * np + 1][0], oacc[2 * np + 1][1]), pack_bf16(oacc[2 * np + 1][2], oacc[2 * np + 1][3]));
+            }
+            __syncwarp();
+            unsigned char* og = reinterpret_cast<unsigned char*>(p.o) +
+                                ((size_t)(bos + c * BT) * p.H + h) * (size_t)(DV * 2) + vb * 2;
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                int row = it * 16 + (lane >> 1), hf = lane & 1;
+                if (row < valid) {
+                    uint4 val = *reinterpret_cast<const uint4*>(stg + row * 32 + hf * 16);
+                    *reinterpret_cast<uint4*>(og + (size_t)row * p.H * (DV * 2) + hf * 16) = val;
+                }
+            }
+            __syncwarp();
+        }
+
+        // ---- S^T <- S^T diag(decay) + v_new^T kg ----
+        {
+            const float* dec = reinterpret_cast<const float*>(smem + s * SCAN_STAGE_BYTES + TP_DECAY);
+#pragma unroll
+            for (int jt = 0; jt < 16; ++jt) {
+                float2 d2 = *reinterpret_cast<const float2*>(dec + 8 * jt + 2 * t);
+                S[jt][0] *= d2.x; S[jt][1] *= d2.y; S[jt][2] *= d2.x; S[jt][3] *= d2.y;
+            }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                for (int jp = 0; jp < 8; ++jp) {
+                    uint32_t b0, b1, b2, b3;
+                    int row = 16 * ks + (m & 1) * 8 + r, ch = 2 * jp + (m >> 1);
+                    ldsm_x4_t(st + TP_KG + row * 256 + ((ch ^ r) << 4), b0, b1, b2, b3);
+                    mma_f16(S[2 * jp], va[ks], b0, b1);
+                    mma_f16(S[2 * jp + 1], va[ks], b2, b3);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+
+    if (p.ht) {
+        float* ht = p.ht + ((size_t)n * p.H + h) * DK * DV;
+#pragma unroll
+        for (int jt = 0; jt < 16; ++jt) {
+            int k0 = 8 * jt + 2 * t;
+            ht[(size_t)k0 * DV + vb + g] = S[jt][0];
+            ht[(size_t)(k0 + 1) * DV + vb + g] = S[jt][1];
+            ht[(size_t)k0 * DV + vb + g + 8] = S[jt][2];
+            ht[(size_t)(k0 + 1) * DV + vb + g + 8] = S[jt][3];
+        }
+    }
+}
+
+}  // namespace kda
+
+extern "C" int kda_fwd_scan_smem_bytes() { return kda::SCAN_SMEM; }
+
+extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream) {
+    using namespace kda;
+    if (p->N <= 0) return 0;
+    dim3 grid(2, p->H, p->N);
+    cudaError_t e;
+    if (p->h_out) {
+        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        kda_fwd_scan_kernel<true><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+    } else {
+        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        kda_fwd_scan_kernel<false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+    }
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,197 @@
+"""``chunk_kda``: chunkwise Kimi Delta Attention on B200, same call surface as the reference's
+``cula.kda.chunk_kda`` (cula/kda/chunk.py:217-412).
+
+Host side only: argument checks, output allocation and two (forward) C-ABI launches on the current
+torch stream. All arithmetic happens in the sm_100a kernels of libcula_kda.so; there is no Triton,
+no FLA dispatch and no CPU fallback.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from ..utils import CHUNK, assert_blackwell, get_varlen_tables
+
+GATE_NONE, GATE_SOFTPLUS, GATE_LOWER_BOUND = 0, 1, 2
+
+_status_words: dict = {}
+
+
+def _status_word(device):
+    key = str(device)
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_status(device=None):
+    """Synchronise and raise if any kernel on ``device`` reported a pipeline wait that gave up."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_words.get(str(device))
+    if word is None:
+        return
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"cula_b200 kernel status {code}: a bounded in-kernel wait timed out")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _gate_mode(use_gate_in_kernel, safe_gate, lower_bound):
+    if not use_gate_in_kernel:
+        return GATE_NONE
+    return GATE_LOWER_BOUND if (safe_gate and lower_bound is not None) else GATE_SOFTPLUS
+
+
+def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
+                  use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias,
+                  store_states=False, store_akk=False):
+    """Forward orchestration (the role of cula/kda/chunk_fwd.py:39-152): the chunk-parallel stage
+    writes one tile pack per (chunk, head); the scan consumes them, carries the fp32 state and
+    writes ``o``. Returns a dict with o, final_state and the intermediates kept for backward."""
+    lib = _native.lib()
+    B, T, H, K = q.shape
+    dev = q.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    if cu_seqlens is not None:
+        tab = get_varlen_tables(cu_seqlens, cu_seqlens_cpu)
+        if tab.total_tokens > T:
+            raise ValueError(f"cu_seqlens[-1]={tab.total_tokens} exceeds the {T} packed tokens")
+        n_seqs, num_chunks = tab.n_seqs, tab.num_chunks
+        cu_p, ci_p, co_p, so_p = (tab.cu_seqlens.data_ptr(), tab.chunk_indices.data_ptr(),
+                                  tab.chunk_offsets.data_ptr(), tab.seq_order.data_ptr())
+        o = torch.zeros_like(v)        # rows past cu_seqlens[-1] stay zero (cula/kda/chunk_fwd.py:129-130)
+    else:
+        n_seqs, num_chunks = B, B * ((T + CHUNK - 1) // CHUNK)
+        cu_p = ci_p = co_p = so_p = None
+        o = torch.empty_like(v)
+    tiles = torch.empty(num_chunks * H * lib.cula_kda_tile_pack_bytes(), dtype=torch.uint8, device=dev)
+    akk = torch.empty(num_chunks * H, CHUNK, CHUNK, dtype=torch.float32, device=dev) if store_akk else None
+    gate_mode = _gate_mode(use_gate_in_kernel, safe_gate, lower_bound)
+    _native.check(lib.cula_kda_fwd_intra(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32),
+        beta.data_ptr(), int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias),
+        cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
+        float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), stream),
+        "cula_kda_fwd_intra")
+    final_state = torch.empty(n_seqs, H, K, v.shape[-1], dtype=torch.float32, device=dev) if output_final_state else None
+    h = vnew = None
+    if store_states:
+        h = torch.empty(num_chunks * H, K, v.shape[-1], dtype=torch.bfloat16, device=dev)
+        vnew = torch.empty(num_chunks * H, CHUNK, v.shape[-1], dtype=torch.float16, device=dev)
+    _native.check(lib.cula_kda_fwd_scan(
+        tiles.data_ptr(), _ptr(initial_state), o.data_ptr(), _ptr(final_state), _ptr(h), _ptr(vnew),
+        cu_p, co_p, so_p, n_seqs, T, H, _status_word(dev).data_ptr(), stream), "cula_kda_fwd_scan")
+    return dict(o=o, final_state=final_state, tiles=tiles, akk=akk, h=h, vnew=vnew, num_chunks=num_chunks)
+
+
+class ChunkKDAFunction(torch.autograd.Function):
+    """Autograd boundary (cula/kda/chunk.py:28-214)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
+                use_qk_l2norm_in_kernel, use_gate_in_kernel, cu_seqlens, cu_seqlens_cpu, safe_gate, lower_bound,
+                disable_recompute, return_intermediate_states):
+        q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+        if A_log is not None:
+            A_log = A_log.float().contiguous()
+        if dt_bias is not None:
+            dt_bias = dt_bias.float().contiguous()
+        if initial_state is not None:
+            initial_state = initial_state.contiguous()
+        with torch.cuda.device(q.device):
+            out = chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
+                                cu_seqlens_cpu, use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound,
+                                A_log, dt_bias, store_states=return_intermediate_states)
+        if return_intermediate_states:
+            assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
+            assert disable_recompute is False, "return_intermediate_states must be used with disable_recompute=False"
+            B, T, H, K = q.shape
+            h = out["h"].view(out["num_chunks"], H, K, v.shape[-1])
+            if cu_seqlens is None:
+                h = h.view(B, -1, H, K, v.shape[-1])
+            else:
+                h = h.unsqueeze(0)
+            return out["o"], out["final_state"], h
+        ctx.save_for_backward(q, k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens)
+        ctx.cu_seqlens_cpu = cu_seqlens_cpu
+        ctx.scale = scale
+        ctx.flags = (use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound)
+        return out["o"], out["final_state"]
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        raise NotImplementedError("chunk_kda backward kernels are not built yet")
+
+
+@torch.compiler.disable
+def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+              use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, cu_seqlens=None, cu_seqlens_cpu=None,
+              safe_gate=False, lower_bound=None, disable_recompute=False, return_intermediate_states=False,
+              cp_context=None, **kwargs):
+    r"""Chunkwise KDA forward (+ autograd backward).
+
+    Args mirror ``cula.kda.chunk_kda`` (cula/kda/chunk.py:218-346):
+        q, k: ``[B, T, H, 128]`` bf16.  v: ``[B, T, H, 128]`` bf16.
+        g: ``[B, T, H, 128]``; the natural-log decay (fp32 or bf16) when ``use_gate_in_kernel=False``,
+            else the raw gate input, activated in-kernel with ``A_log`` ``[H]`` and optional ``dt_bias``
+            ``[H*128]`` passed as keyword arguments.
+        beta: ``[B, T, H]`` bf16 or fp32.
+        scale: defaults to ``128 ** -0.5``.
+        initial_state: ``[N, H, 128, 128]`` fp32 (N sequences) or None.
+        output_final_state: also return the ``[N, H, 128, 128]`` fp32 final state.
+        use_qk_l2norm_in_kernel: L2-normalise q and k rows in-kernel.
+        safe_gate / lower_bound: with ``use_gate_in_kernel`` selects
+            ``lower_bound * sigmoid(exp(A_log) * (g + dt_bias))``; lower_bound must lie in [-5, 0).
+        cu_seqlens: int32 ``[N+1]`` for a packed batch (then B must be 1); cu_seqlens_cpu: optional host copy.
+        disable_recompute: keep forward intermediates for backward instead of recomputing them.
+        return_intermediate_states: inference only; also return h ``[B, NT, H, 128, 128]`` bf16.
+
+    Returns ``(o, final_state)`` (``final_state`` is None unless requested).
+    Raises ValueError / AssertionError on the same conditions as the reference (cula/kda/chunk.py:348-388).
+    """
+    if cp_context is not None:
+        raise NotImplementedError("context parallelism is driven through cula_b200.kda.cp, not cp_context")
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError(
+                f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
+                f"Please flatten variable-length inputs before processing.")
+        if initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+            raise ValueError(
+                f"The number of initial states is expected to be equal to the number of input sequences, "
+                f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
+    if initial_state is not None:
+        assert initial_state.dtype == torch.float32, "initial_state must be in float32."
+
+    A_log, dt_bias = None, None
+    if use_gate_in_kernel:
+        assert "A_log" in kwargs, "A_log must be provided when use_gate_in_kernel=True."
+        A_log, dt_bias = kwargs["A_log"], kwargs.get("dt_bias")
+
+    if safe_gate and use_gate_in_kernel:
+        if lower_bound is None:
+            raise ValueError("`lower_bound` must be specified when `safe_gate=True` and `use_gate_in_kernel=True`.")
+        if not (-5 <= lower_bound < 0):
+            raise ValueError(f"`lower_bound` must be in the safe range [-5, 0), got {lower_bound}.")
+
+    assert q.shape == k.shape == g.shape, "q, k, g must have the same shape."
+    assert k.shape[-1] <= 256, "Currently we only support key headdim <=256 for KDA :-("
+    assert beta.shape == q.shape[:3], "beta must be of shape (batch size, seq len, num of head)."
+    assert v.shape == (*q.shape[:3], v.shape[-1]), "v must be of shape (batch size, seq len, num of head, head dim)."
+    assert q.dtype == k.dtype == v.dtype == torch.bfloat16, "q, k, v must be in bfloat16."
+    assert beta.dtype == torch.bfloat16 or beta.dtype == torch.float32, "beta must be in bfloat16 or float32."
+    assert q.shape[-1] == k.shape[-1] == v.shape[-1] == 128, "Currently we only support head dim of 128 for KDA"
+    assert g.dtype in (torch.bfloat16, torch.float32), "g must be in bfloat16 or float32."
+    if initial_state is not None and cu_seqlens is None:
+        assert initial_state.shape[0] == q.shape[0], "one initial state per batch entry is expected."
+    assert_blackwell(q.device)
+
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
+                                  use_qk_l2norm_in_kernel, use_gate_in_kernel, cu_seqlens, cu_seqlens_cpu, safe_gate,
+                                  lower_bound, disable_recompute, return_intermediate_states)

@@ -1,0 +1,84 @@
+/*
+ * C ABI of libcula_kda.so: the B200 (sm_100a) kernels behind cula.kda.chunk_kda.
+ *
+ * Conventions
+ *   - every pointer named d_* is a DEVICE pointer owned by the caller; the library never allocates,
+ *     frees or keeps device memory (same ownership rule as the reference's native layer, where
+ *     Python allocates every output and workspace: cula/kda/chunk_intra.py:776-791,
+ *     cula/ops/chunk_delta_h.py:2119-2138);
+ *   - tensors are contiguous, token-major: q/k/g [B*T, H, 128], v/o [B*T, H, 128], beta [B*T, H];
+ *     a packed (varlen) batch is one sequence axis of cu_seqlens[N] tokens, B == 1;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises;
+ *   - return value: 0 = ok, < 0 = argument error (CULA_KDA_E*), > 0 = a cudaError_t from the launch.
+ *     The reference instead throws c10::Error from TORCH_CHECK (csrc/api/kda_sm100.cu:46-50) and
+ *     exit(1)s on CUDA errors (csrc/kerutils/include/kerutils/common/common.h:24-31).
+ *   - head dim is 128 for keys and values, chunk length 64 (cula/kda/chunk.py:54,386-388).
+ */
+#ifndef CULA_KDA_H_
+#define CULA_KDA_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CULA_KDA_EINVAL (-1)   /* null pointer / non-positive size / bad enum */
+#define CULA_KDA_EALIGN (-2)   /* a pointer is not 16-byte aligned */
+
+#define CULA_KDA_GATE_NONE 0         /* g already holds the natural-log decay (use_gate_in_kernel=False) */
+#define CULA_KDA_GATE_SOFTPLUS 1     /* a = -exp(A_log[h]) * softplus(g + dt_bias[h,:]) */
+#define CULA_KDA_GATE_LOWER_BOUND 2  /* a = lower_bound * sigmoid(exp(A_log[h]) * (g + dt_bias[h,:])) (safe_gate) */
+
+/* Bytes of one forward tile pack, the per-(chunk, head) record handed from the chunk-parallel stage
+ * to the state scan: w, qg, kg, Aqk, u (fp16), 2^g_last (fp32), pre-swizzled for the scan. */
+int cula_kda_tile_pack_bytes(void);
+
+/* Shared memory (bytes) each kernel asks for; lets a caller check the device limit up front. */
+int cula_kda_fwd_intra_smem_bytes(void);
+int cula_kda_fwd_scan_smem_bytes(void);
+
+/*
+ * Chunk-parallel forward stage, one CTA per (chunk, head).
+ * Replaces, fused into one launch:
+ *   l2norm_fwd(q), l2norm_fwd(k)            cula/kda/chunk.py:58-60
+ *   kda_gate_chunk_cumsum / chunk_local_cumsum   cula/kda/chunk_fwd.py:69-80
+ *   chunk_kda_fwd_intra_cuda(q,k,g,beta,cu_seqlens,chunk_indices,Aqk_out,Akk_out,tile_counter,scale,
+ *                            chunk_size,use_tf32_inverse,unified_gref)   csrc/api/pybind.cu:70-79, csrc/api/kda_sm100.cu:22-68
+ *   recompute_w_u_cuda(k,v,beta,A,g,cu_seqlens,chunk_indices,w_out,u_out,kg_out,chunk_size,q,qg_out)
+ *                                                                 csrc/api/kda_sm100.cu:70-120
+ * d_cu_seqlens [N+1] / d_chunk_indices [num_chunks][2] (sequence, chunk-in-sequence) are the tables of
+ * prepare_chunk_indices; pass both NULL for a fixed-length batch of sequences of T tokens.
+ * d_tiles: num_chunks*H tile packs (output). d_akk: optional [num_chunks*H][64][64] fp32 (I+L)^-1.
+ */
+int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* d_v,
+                       const void* d_g, int g_is_fp32,
+                       const void* d_beta, int beta_is_fp32,
+                       const float* d_A_log, const float* d_dt_bias,
+                       const int* d_cu_seqlens, const int* d_chunk_indices,
+                       int num_chunks, int T, int H,
+                       float scale, int use_qk_l2norm, int gate_mode, float lower_bound,
+                       void* d_tiles, float* d_akk, void* stream);
+
+/*
+ * Sequential state scan fused with the output stage, one CTA per (sequence, head, value half).
+ * Replaces chunk_gated_delta_rule_fwd_h(k=kg, w, u, gk, initial_state, output_final_state, cu_seqlens, ...)
+ *   (cula/ops/chunk_delta_h.py:1991-2168, called at cula/kda/chunk_fwd.py:111-120) and
+ *   chunk_gla_fwd_o(q, v_new, g, A=Aqk, h, o, scale, ...) (cula/ops/fwd_o.py:1755-1852, chunk_fwd.py:131-143).
+ * d_h0 / d_ht: [N, H, 128, 128] fp32 or NULL. d_o: [B*T, H, 128] bf16; only rows of real tokens are written.
+ * d_h_out (bf16 [num_chunks*H][128][128], state entering each chunk) and d_vnew_out (fp16
+ * [num_chunks*H][64][128]) are both given or both NULL.
+ * d_chunk_offsets [N+1]: first global chunk of each sequence (prepare_chunk_offsets);
+ * d_seq_order [N]: optional launch order of the sequences (longest first balances a ragged batch).
+ * d_status: one int the kernel sets non-zero if a bounded pipeline wait gave up (never in a healthy run).
+ */
+int cula_kda_fwd_scan(const void* d_tiles, const float* d_h0, void* d_o, float* d_ht,
+                      void* d_h_out, void* d_vnew_out,
+                      const int* d_cu_seqlens, const int* d_chunk_offsets, const int* d_seq_order,
+                      int N, int T, int H, int* d_status, void* stream);
+
+/* Human-readable text for a return value of the functions above. */
+const char* cula_kda_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CULA_KDA_H_ */

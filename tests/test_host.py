@@ -1,0 +1,89 @@
+"""CPU-side checks: index tables, argument validation of chunk_kda, and that the C-ABI library
+loads and exports every symbol include/cula_kda.h declares (no compute calls without a GPU)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from cula_b200 import _native
+from cula_b200.kda import chunk_kda
+from cula_b200.utils import VarlenTables, prepare_chunk_indices, prepare_chunk_offsets, prepare_uniform_cu_seqlens
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_chunk_tables():
+    cu = torch.tensor([0, 15, 85, 149, 186])
+    idx = prepare_chunk_indices(cu)
+    assert idx.tolist() == [[0, 0], [1, 0], [1, 1], [2, 0], [3, 0]]
+    assert prepare_chunk_offsets(cu).tolist() == [0, 1, 3, 4, 5]
+    assert prepare_uniform_cu_seqlens(3, 100).tolist() == [0, 100, 200, 300]
+    tab = VarlenTables(cu.to(torch.int32))
+    assert tab.n_seqs == 4 and tab.num_chunks == 5 and tab.total_tokens == 186
+    assert tab.seq_order.tolist() == [1, 2, 3, 0]
+
+
+def test_chunk_tables_empty_sequence():
+    cu = torch.tensor([0, 64, 64, 70])
+    assert prepare_chunk_indices(cu).tolist() == [[0, 0], [2, 0]]
+    assert prepare_chunk_offsets(cu).tolist() == [0, 1, 1, 2]
+
+
+def test_bad_cu_seqlens():
+    with pytest.raises(ValueError):
+        VarlenTables(torch.tensor([0, 10, 5], dtype=torch.int32))
+    with pytest.raises(ValueError):
+        VarlenTables(torch.tensor([3, 10], dtype=torch.int32))
+
+
+def _inputs(B=1, T=8, H=1, dtype=torch.bfloat16):
+    q = torch.zeros(B, T, H, 128, dtype=dtype)
+    return q, q.clone(), q.clone(), q.clone(), torch.zeros(B, T, H, dtype=dtype)
+
+
+def test_argument_errors_match_reference():
+    q, k, v, g, beta = _inputs(B=2)
+    with pytest.raises(ValueError, match="batch size is expected to be 1"):
+        chunk_kda(q, k, v, g, beta, cu_seqlens=torch.tensor([0, 8], dtype=torch.int32))
+    q, k, v, g, beta = _inputs()
+    with pytest.raises(ValueError, match="number of initial states"):
+        chunk_kda(q, k, v, g, beta, cu_seqlens=torch.tensor([0, 4, 8], dtype=torch.int32),
+                  initial_state=torch.zeros(1, 1, 128, 128))
+    with pytest.raises(AssertionError, match="float32"):
+        chunk_kda(q, k, v, g, beta, initial_state=torch.zeros(1, 1, 128, 128, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError, match="A_log"):
+        chunk_kda(q, k, v, g, beta, use_gate_in_kernel=True)
+    with pytest.raises(ValueError, match="lower_bound"):
+        chunk_kda(q, k, v, g, beta, use_gate_in_kernel=True, safe_gate=True, A_log=torch.zeros(1))
+    with pytest.raises(ValueError, match="safe range"):
+        chunk_kda(q, k, v, g, beta, use_gate_in_kernel=True, safe_gate=True, lower_bound=-6.0, A_log=torch.zeros(1))
+    with pytest.raises(AssertionError, match="bfloat16"):
+        chunk_kda(q.float(), k.float(), v.float(), g, beta)
+    with pytest.raises(AssertionError, match="beta must be of shape"):
+        chunk_kda(q, k, v, g, beta[..., None])
+    q64 = torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError, match="head dim of 128"):
+        chunk_kda(q64, q64, q64, q64, beta)
+
+
+def test_no_cpu_fallback():
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    q, k, v, g, beta = _inputs()
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        chunk_kda(q, k, v, g, beta)
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "cula_kda.h")).read()
+    declared = set(re.findall(r"\b(cula_kda_\w+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_native.SIGNATURES), "binding table and header disagree"
+    handle = ctypes.CDLL(_native.LIB_PATH)
+    for name in declared:
+        assert hasattr(handle, name), name
+    assert handle.cula_kda_tile_pack_bytes() == 74240
+    _native.lib().cula_kda_strerror.restype = ctypes.c_char_p
+    assert b"invalid" in _native.lib().cula_kda_strerror(-1)

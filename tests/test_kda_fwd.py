@@ -1,0 +1,193 @@
+"""GPU parity of the chunk_kda forward path (through the C ABI) against the CPU oracle and the golden
+vectors. Tolerances: o relative RMS <= 5e-3 and max-abs <= 2e-2; final_state relative <= 1e-3
+(headline configurations) -- the reference's own test asks 5e-3 for both (tests/test_kda.py:145-146)."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from chunkwise_ref import chunk_quantities, decode_tiles
+from conftest import GOLDEN_CASES, load_golden
+from oracle import c_oracle
+from oracle.naive_kda import err_ratio, kda_gate, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+O_RMS, O_MAXABS, HT_REL = 5e-3, 2e-2, 1e-3
+
+
+def _cuda(x):
+    return None if x is None else x.cuda()
+
+
+def run_chunk_kda(inp, cu_seqlens=None, l2=True, gate=True, safe=True, lower_bound=-5.0, **kw):
+    from cula_b200.kda import check_status, chunk_kda
+    extra = dict(A_log=_cuda(inp.get("A_log")), dt_bias=_cuda(inp.get("dt_bias"))) if gate else {}
+    o, ht = chunk_kda(_cuda(inp["q"]), _cuda(inp["k"]), _cuda(inp["v"]), _cuda(inp["g"]), _cuda(inp["beta"]),
+                      initial_state=_cuda(inp.get("initial_state")), output_final_state=True,
+                      use_qk_l2norm_in_kernel=l2, use_gate_in_kernel=gate, safe_gate=safe,
+                      lower_bound=lower_bound if (gate and safe) else None,
+                      cu_seqlens=_cuda(cu_seqlens), **extra, **kw)
+    torch.cuda.synchronize()
+    check_status()
+    return o, ht
+
+
+def oracle_fwd(inp, cu_seqlens=None, l2=True, gate=True, safe=True, lower_bound=-5.0):
+    f = lambda x: None if x is None else x.float().numpy()
+    mode = 0 if not gate else (2 if safe else 1)
+    o, ht = c_oracle.naive_kda_fwd(f(inp["q"]), f(inp["k"]), f(inp["v"]), f(inp["g"]), f(inp["beta"]),
+                                   f(inp.get("A_log")) if gate else None, f(inp.get("dt_bias")) if gate else None,
+                                   f(inp.get("initial_state")),
+                                   cu_seqlens=None if cu_seqlens is None else cu_seqlens.numpy(),
+                                   use_l2norm=l2, gate_mode=mode, lower_bound=lower_bound)
+    return torch.from_numpy(o), torch.from_numpy(ht)
+
+
+def assert_fwd_close(o, ht, o_ref, ht_ref, ht_tol=HT_REL, tag=""):
+    o, ht = o.float().cpu(), ht.float().cpu()
+    assert torch.isfinite(o).all() and torch.isfinite(ht).all(), tag
+    e_o, e_h = err_ratio(o_ref, o), err_ratio(ht_ref, ht)
+    mx = float((o_ref - o).abs().max())
+    assert e_o <= O_RMS and mx <= O_MAXABS and e_h <= ht_tol, f"{tag}: o rms {e_o:.2e} maxabs {mx:.2e} ht {e_h:.2e}"
+    return e_o, mx, e_h
+
+
+@pytest.mark.parametrize("gate_offset", [0.0, -8.0])
+def test_chunk_parallel_stage_against_fp64_model(gate_offset):
+    """The chunk-parallel stage alone: decode its tile packs and compare each array with an fp64
+    torch model of the chunk algebra (w, u, kg, qg, Aqk, decay, Akk)."""
+    from cula_b200.kda.chunk import chunk_kda_fwd
+    B, T, H = 1, 150, 2
+    inp = make_inputs(B, T, H, seed=3, gate_offset=gate_offset)
+    inp["A_log"] = inp["A_log"] + 0.2
+    dev = {k: _cuda(v) for k, v in inp.items()}
+    out = chunk_kda_fwd(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], 128 ** -0.5, None, False, None, None,
+                        True, True, True, -5.0, dev["A_log"], dev["dt_bias"], store_akk=True)
+    torch.cuda.synchronize()
+    nt = (T + 63) // 64
+    got = {k: v.cpu() for k, v in decode_tiles(out["tiles"], nt * H).items()}
+    akk = out["akk"].cpu()
+    a = kda_gate(inp["g"], inp["A_log"], inp["dt_bias"], -5.0).double()
+    qn = F.normalize(inp["q"].double(), dim=-1)
+    kn = F.normalize(inp["k"].double(), dim=-1)
+    msgs = []
+    for h in range(H):
+        ref = chunk_quantities(qn[0, :, h], kn[0, :, h], inp["v"][0, :, h].double(), a[0, :, h],
+                               inp["beta"][0, :, h].double(), 128 ** -0.5)
+        for c in range(nt):
+            ti = c * H + h
+            for name, tol in (("w", 1e-3), ("qg", 1e-3), ("kg", 1e-3), ("u", 1e-3), ("aqk", 1e-3)):
+                e = err_ratio(ref[c][name], got[name][ti])
+                if not e <= tol:
+                    msgs.append(f"{name}[c={c},h={h}] rel {e:.2e} > {tol}")
+            if not float((ref[c]["decay"] - got["decay"][ti]).abs().max()) <= 1e-5:   # underflows to 0 with strong gates
+                msgs.append(f"decay[c={c},h={h}]")
+            e = err_ratio(ref[c]["akk"], akk[ti])
+            if not e <= 1e-4:
+                msgs.append(f"akk[c={c},h={h}] rel {e:.2e}")
+    assert not msgs, "; ".join(msgs[:12])
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_forward_matches_golden(name):
+    case, inp, exp = load_golden(name)
+    inp["initial_state"] = inp.pop("h0", None)
+    o, ht = run_chunk_kda(inp, cu_seqlens=case["cu_seqlens"], l2=case["use_l2norm"], gate=case["use_gate_in_kernel"],
+                          safe=case["safe_gate"], lower_bound=case["lower_bound"])
+    assert_fwd_close(o, ht, exp["o"], exp["ht"], tag=name)
+
+
+def test_headline_cpu_config():
+    """B=1, T=512, H=4: the configuration the CPU baseline is quoted on."""
+    inp = make_inputs(1, 512, 4, seed=0)
+    o, ht = run_chunk_kda(inp)
+    o_ref, ht_ref = oracle_fwd(inp)
+    assert_fwd_close(o, ht, o_ref, ht_ref, tag="config1")
+
+
+@pytest.mark.parametrize("B,T,H,gate_offset,h0_std", [
+    (1, 63, 1, -6.0, 1.0), (2, 500, 3, -8.0, 1.0), (2, 1000, 3, 0.0, 1.0), (2, 1500, 4, -8.0, 0.5),
+    (1, 1, 2, -8.0, 1.0), (1, 65, 2, -8.0, 0.0), (1, 127, 1, -4.0, 1.0), (4, 2048, 8, -8.0, 0.1),
+])
+def test_forward_shapes_of_the_reference_suite(B, T, H, gate_offset, h0_std):
+    """Ragged lengths of tests/test_kda.py:52-59 plus tiny ones, weak and strong gates, with initial state."""
+    inp = make_inputs(B, T, H, seed=42, gate_offset=gate_offset, h0_std=h0_std)
+    inp["A_log"] = inp["A_log"] + 0.1
+    inp["dt_bias"] = 0.1 * torch.randn(H * 128, generator=torch.Generator().manual_seed(7))
+    o, ht = run_chunk_kda(inp)
+    o_ref, ht_ref = oracle_fwd(inp)
+    assert_fwd_close(o, ht, o_ref, ht_ref, ht_tol=2e-3, tag=f"B{B}T{T}H{H}")
+
+
+@pytest.mark.parametrize("beta_dtype,g_fp32", [(torch.float32, False), (torch.bfloat16, True)])
+def test_forward_pre_gated_and_dtypes(beta_dtype, g_fp32):
+    """use_gate_in_kernel=False (g is the fp32 log decay, clamped to [-5, 0]) and fp32 beta."""
+    B, T, H = 2, 200, 2
+    inp = make_inputs(B, T, H, seed=5, h0_std=1.0, beta_dtype=beta_dtype)
+    gen = torch.Generator().manual_seed(11)
+    a = (F.logsigmoid(torch.randn(B, T, H, 128, generator=gen)) / 4.0).clamp(-5, 0)
+    inp["g"] = a if g_fp32 else a.to(torch.bfloat16)
+    inp["q"] = F.normalize(inp["q"].float(), dim=-1).to(torch.bfloat16)
+    inp["k"] = F.normalize(inp["k"].float(), dim=-1).to(torch.bfloat16)
+    o, ht = run_chunk_kda(inp, l2=False, gate=False)
+    o_ref, ht_ref = oracle_fwd(inp, l2=False, gate=False)
+    assert_fwd_close(o, ht, o_ref, ht_ref, ht_tol=2e-3, tag="pre-gated")
+
+
+VARLEN = [[15], [64], [1, 63, 65], [100, 300, 56], [256, 100, 300, 400, 1], [33, 128, 200, 95]]
+
+
+@pytest.mark.parametrize("lens", VARLEN)
+def test_forward_varlen(lens):
+    H, T = 3, sum(lens)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    inp = make_inputs(1, T, H, seed=9, gate_offset=-7.0)
+    inp["initial_state"] = torch.randn(len(lens), H, 128, 128, generator=torch.Generator().manual_seed(1))
+    o, ht = run_chunk_kda(inp, cu_seqlens=cu)
+    o_ref, ht_ref = oracle_fwd(inp, cu_seqlens=cu)
+    assert_fwd_close(o, ht, o_ref, ht_ref, ht_tol=2e-3, tag=f"varlen{lens}")
+    # one packed sequence equals the fixed-length call bit for bit
+    if len(lens) == 1:
+        o2, ht2 = run_chunk_kda(inp)
+        assert torch.equal(o, o2) and torch.equal(ht, ht2)
+
+
+def test_varlen_padding_rows_stay_zero():
+    """Tokens past cu_seqlens[-1] (serving stacks pad the packed batch) must come back as zeros."""
+    H, T = 2, 200
+    cu = torch.tensor([0, 70, 150], dtype=torch.int32)
+    inp = make_inputs(1, T, H, seed=2, gate_offset=-6.0)
+    o, _ = run_chunk_kda(inp, cu_seqlens=cu)
+    assert float(o[:, 150:].abs().max()) == 0.0
+    assert float(o[:, :150].abs().max()) > 0.0
+
+
+def test_forward_is_deterministic_and_without_final_state():
+    from cula_b200.kda import chunk_kda
+    inp = make_inputs(2, 300, 4, seed=1, gate_offset=-8.0, h0_std=1.0)
+    outs = [run_chunk_kda(inp) for _ in range(3)]
+    for o, ht in outs[1:]:
+        assert torch.equal(o, outs[0][0]) and torch.equal(ht, outs[0][1])
+    o, ht = chunk_kda(inp["q"].cuda(), inp["k"].cuda(), inp["v"].cuda(), inp["g"].cuda(), inp["beta"].cuda(),
+                      use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+                      A_log=inp["A_log"].cuda(), dt_bias=inp["dt_bias"].cuda(), initial_state=inp["initial_state"].cuda())
+    assert ht is None and torch.equal(o, outs[0][0])
+
+
+def test_return_intermediate_states():
+    """h[b, c] is the state entering chunk c (bf16), as the reference returns it in inference mode."""
+    from cula_b200.kda import chunk_kda
+    B, T, H = 1, 192, 2
+    inp = make_inputs(B, T, H, seed=4, gate_offset=-8.0, h0_std=1.0)
+    with torch.inference_mode():
+        o, ht, h = chunk_kda(inp["q"].cuda(), inp["k"].cuda(), inp["v"].cuda(), inp["g"].cuda(), inp["beta"].cuda(),
+                             use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+                             A_log=inp["A_log"].cuda(), dt_bias=inp["dt_bias"].cuda(),
+                             initial_state=inp["initial_state"].cuda(), output_final_state=True,
+                             return_intermediate_states=True)
+    assert h.shape == (B, 3, H, 128, 128)
+    assert err_ratio(inp["initial_state"], h[:, 0].float().cpu()) < 4e-3      # bf16 rounding of h0
+    short = {k: (v[:, :128] if k in ("q", "k", "v", "g", "beta") else v) for k, v in inp.items()}
+    _, ht128 = oracle_fwd(short)
+    assert err_ratio(ht128, h[:, 2].float().cpu()) < 5e-3
