@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Benchmark of the chunk_kda forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one chunk_kda forward over one synthetic batch. At N=1 the workload is the headline
+configuration (B=2, T=2048, H=32, K=V=128, bf16, in-kernel gate + L2 norm, safe gate, final state).
+With N>1 (launched under torch.distributed.run, one rank per GPU) every rank runs the same-sized
+shard of a batch that is N times larger (weak scaling over batch x head; the path has no
+data-path collective there). Rank 0 prints ONE JSON line.
+
+`--impl reference` times the reference's CPU implementation of the path (the fp32 naive token
+recurrence, here the plain-C restatement under oracle/) on the host cores, same metric and config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, T, H, lens or None)
+    "fwd_B2_T2048_H32": (2, 2048, 32),
+    "fwd_B4_T8192_H32": (4, 8192, 32),
+    "fwd_B1_T512_H4": (1, 512, 4),
+}
+FLOP_PER_TOKEN_HEAD = 180224          # dense-tile convention, forward
+BYTES_PER_TOKEN_HEAD = 1282           # compulsory forward traffic: q,k,v,g bf16 + beta + o
+TILE_PACK_BYTES = 74240
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(B, T, H, budget_s=10.0):
+    """Time the plain-C oracle on the host cores on the same workload; tokens/s."""
+    from oracle import c_oracle
+    from oracle.naive_kda import make_inputs
+    inp = make_inputs(B, T, H, seed=0)
+    f = lambda x: x.float().numpy()
+    args = [f(inp[k]) for k in ("q", "k", "v", "g", "beta")]
+    extra = (f(inp["A_log"]), f(inp["dt_bias"]), None)
+    run = lambda: c_oracle.naive_kda_fwd(*args, *extra, use_l2norm=True, gate_mode=2, lower_bound=-5.0)
+    run()
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        run()
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or reps >= 400:
+            break
+    return dict(value=B * T * reps / dt, unit="tokens/s", cores=c_oracle.num_threads(), kind="port",
+                sample=f"{reps} full forward passes of B={B} T={T} H={H} ({dt:.1f} s) with the OpenMP C "
+                       f"restatement of the fp32 naive recurrence"), dt / reps
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    B, T, H = WORKLOADS[args.workload]
+    from oracle import c_oracle
+    from oracle.naive_kda import make_inputs
+    inp = make_inputs(B, T, H, seed=0)
+    f = lambda x: x.float().numpy()
+    a = [f(inp[k]) for k in ("q", "k", "v", "g", "beta")] + [f(inp["A_log"]), f(inp["dt_bias"]), None]
+    run = lambda: c_oracle.naive_kda_fwd(*a, use_l2norm=True, gate_mode=2, lower_bound=-5.0)
+    for _ in range(args.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = B * T / dt
+    cores = c_oracle.num_threads()
+    print(json.dumps({
+        "impl": "reference", "metric": "chunk_kda forward tokens/s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "B": B, "T": T, "H": H, "K": 128, "V": 128},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"each step = one full forward of B={B} T={T} H={H} on {cores} host threads "
+                                   "(plain-C restatement of the reference's fp32 naive recurrence)"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="fwd_B2_T2048_H32", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch.distributed as dist
+    from cula_b200 import _native
+    from cula_b200.kda import check_status, chunk_kda
+    from cula_b200.kda.chunk import chunk_kda_fwd
+    from oracle.naive_kda import make_inputs
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _native.lib()                     # fail loudly if the CUDA library is missing
+
+    B, T, H = WORKLOADS[args.workload]
+    inp = make_inputs(B, T, H, seed=rank)          # every rank owns an equally sized shard (weak scaling)
+    host = {k: v.pin_memory() for k, v in inp.items() if v is not None}
+    d = {k: v.to(dev) for k, v in host.items()}
+    kw = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+              output_final_state=True)
+    fwd = lambda t: chunk_kda(t["q"], t["k"], t["v"], t["g"], t["beta"], A_log=t["A_log"], dt_bias=t["dt_bias"], **kw)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps, warmup):
+        """Device time of `steps` calls: L2 is flushed (untimed) before each, each call has its own event pair."""
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        evs = []
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step_fn()
+            e1.record()
+            evs.append((e0, e1))
+        barrier()
+        total_ms = sum(a.elapsed_time(b) for a, b in evs)
+        if world > 1:
+            t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total_ms = float(t.item())
+        return total_ms / steps
+
+    # ---- device-resident throughput ("value") ----
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: fwd(d), args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    check_status(dev)
+    tokens = B * T * world
+
+    # ---- end to end through the public call with host buffers ----
+    o_host = torch.empty(B, T, H, 128, dtype=torch.bfloat16).pin_memory()
+    ht_host = torch.empty(B, H, 128, 128, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        o, ht = fwd(t)
+        o_host.copy_(o, non_blocking=True)
+        ht_host.copy_(ht, non_blocking=True)
+
+    ms_e2e = timed(e2e_step, max(3, args.steps // 2), 3)
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = o_host.numel() * 2 + ht_host.numel() * 4
+
+    # ---- per-kernel device time for the roofline of the dominant kernel ----
+    lib = _native.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    nchunks = B * ((T + 63) // 64)
+    tiles = torch.empty(nchunks * H * TILE_PACK_BYTES, dtype=torch.uint8, device=dev)
+    o_buf = torch.empty(B, T, H, 128, dtype=torch.bfloat16, device=dev)
+    ht_buf = torch.empty(B, H, 128, 128, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def k_intra():
+        _native.check(lib.cula_kda_fwd_intra(d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), d["g"].data_ptr(), 0,
+                                             d["beta"].data_ptr(), 0, d["A_log"].data_ptr(), d["dt_bias"].data_ptr(),
+                                             None, None, nchunks, T, H, 128 ** -0.5, 1, 2, -5.0, tiles.data_ptr(), None,
+                                             stream), "intra")
+
+    def k_scan():
+        _native.check(lib.cula_kda_fwd_scan(tiles.data_ptr(), None, o_buf.data_ptr(), ht_buf.data_ptr(), None, None,
+                                            None, None, None, B, T, H, status.data_ptr(), stream), "scan")
+
+    ms_intra = timed(k_intra, args.steps, 3)
+    ms_scan = timed(k_scan, args.steps, 3)
+    th = B * T * H
+    kernels = {
+        "kda_fwd_intra_kernel": dict(ms=ms_intra, bytes=th * (1282 - 256) + nchunks * H * TILE_PACK_BYTES),
+        "kda_fwd_scan_kernel": dict(ms=ms_scan, bytes=nchunks * H * TILE_PACK_BYTES + th * 256 + B * H * 65536),
+    }
+    dom = max(kernels, key=lambda k: kernels[k]["ms"])
+    peaks = load_peaks()
+    achieved = kernels[dom]["bytes"] / (kernels[dom]["ms"] * 1e-3) / 1e9
+    roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
+                "kernels_ms": {k: v["ms"] for k, v in kernels.items()}}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    base = None
+    if not args.no_cpu_baseline:
+        base, _ = cpu_baseline(B, T, H)
+    line = {
+        "metric": "chunk_kda forward tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "H": H, "K": 128, "V": 128,
+                   "flags": "l2norm+gate in kernel, safe_gate, lower_bound=-5, final state",
+                   "l2": "256 MB flush buffer written before every timed step",
+                   "sharding": "batch x head shards, one per rank, no collective"},
+        "tflops": tokens * H * FLOP_PER_TOKEN_HEAD / (ms * 1e-3) / 1e12,
+        "tflops_frac_of_bf16_peak": tokens / world * H * FLOP_PER_TOKEN_HEAD / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "hbm_frac_compulsory": tokens / world * H * BYTES_PER_TOKEN_HEAD / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+        "gpu_launches": 2 * args.steps,
+        "roofline": roofline,
+        "cpu_baseline": base,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
