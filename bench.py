@@ -91,8 +91,8 @@ class ClockSampler:
 
 def cpu_baseline(B, T, H, budget_s=10.0):
     """Time the plain-C oracle on the host cores on the same workload; tokens/s."""
+    from cula_b200.synthetic import make_inputs
     from oracle import c_oracle
-    from oracle.naive_kda import make_inputs
     inp = make_inputs(B, T, H, seed=0)
     f = lambda x: x.float().numpy()
     args = [f(inp[k]) for k in ("q", "k", "v", "g", "beta")]
@@ -115,8 +115,8 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     B, T, H = WORKLOADS[args.workload]
+    from cula_b200.synthetic import make_inputs
     from oracle import c_oracle
-    from oracle.naive_kda import make_inputs
     inp = make_inputs(B, T, H, seed=0)
     f = lambda x: x.float().numpy()
     a = [f(inp[k]) for k in ("q", "k", "v", "g", "beta")] + [f(inp["A_log"]), f(inp["dt_bias"]), None]
@@ -162,8 +162,7 @@ def main():
     import torch.distributed as dist
     from cula_b200 import _native
     from cula_b200.kda import check_status, chunk_kda
-    from cula_b200.kda.chunk import chunk_kda_fwd
-    from oracle.naive_kda import make_inputs
+    from cula_b200.synthetic import make_inputs
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
