@@ -18,7 +18,7 @@ SIGNATURES = {
     "cula_kda_fwd_intra_smem_bytes": (_i, []),
     "cula_kda_fwd_scan_smem_bytes": (_i, []),
     "cula_kda_fwd_intra": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _fp, _fp, _ip, _ip, _i, _i, _i,
-                                _f, _i, _i, _f, _vp, _fp, _vp]),
+                                _f, _i, _i, _f, _vp, _fp, _ip, _vp]),
     "cula_kda_fwd_scan": (_i, [_vp, _fp, _vp, _fp, _vp, _vp, _ip, _ip, _ip, _i, _i, _i, _ip, _vp]),
     "cula_kda_strerror": (ctypes.c_char_p, [_i]),
 }

@@ -21,9 +21,9 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
                                   const void* d_beta, int beta_is_fp32, const float* d_A_log, const float* d_dt_bias,
                                   const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H,
                                   float scale, int use_qk_l2norm, int gate_mode, float lower_bound, void* d_tiles,
-                                  float* d_akk, void* stream) {
+                                  float* d_akk, int* d_status, void* stream) {
     if (num_chunks == 0) return 0;
-    if (!d_q || !d_k || !d_v || !d_g || !d_beta || !d_tiles || num_chunks < 0 || H <= 0) return CULA_KDA_EINVAL;
+    if (!d_q || !d_k || !d_v || !d_g || !d_beta || !d_tiles || !d_status || num_chunks < 0 || H <= 0) return CULA_KDA_EINVAL;
     if (gate_mode < 0 || gate_mode > 2 || (gate_mode != 0 && !d_A_log)) return CULA_KDA_EINVAL;
     if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
     if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
@@ -36,6 +36,7 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
     p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices;
     p.tiles = static_cast<unsigned char*>(d_tiles);
     p.akk_out = d_akk;
+    p.status = d_status;
     p.T = T; p.H = H; p.g_fp32 = g_is_fp32; p.beta_fp32 = beta_is_fp32;
     p.use_l2norm = use_qk_l2norm; p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
     return kda_launch_fwd_intra(&p, num_chunks, static_cast<cudaStream_t>(stream));

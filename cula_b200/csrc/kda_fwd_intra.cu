@@ -1,6 +1,8 @@
-// Chunk-parallel forward stage: one CTA per (chunk, head) fuses
+// Chunk-parallel forward stage on tcgen05 tensor cores: one CTA per (chunk, head) fuses
 //   gate activation + per-chunk cumulative sum (log2 domain), q/k L2 normalisation,
-//   the gated 64x64 Gram matrices Aqk / L, Akk = (I + L)^-1, w = Akk (beta k 2^g), u = Akk (beta v),
+//   the gated 64x64 Gram matrices Aqk / L (one M=128 x N=160 TF32 UMMA chain, accumulators in TMEM),
+//   Akk = (I + L)^-1 (blocked 16 -> 32 -> 64 inverse in fp32),
+//   w = Akk (beta k 2^g), u = Akk (beta v) (two M=128 x N=64 FP16 UMMAs),
 //   kg = k 2^(g_last - g), qg = scale q 2^g,
 // and writes the tile pack the state scan consumes (layout in kda_common.cuh).
 //
@@ -8,244 +10,502 @@
 // kda_gate_chunk_cumsum (cula/kda/chunk_fwd.py:69-78), chunk_kda_fwd_intra_cuda and
 // recompute_w_u_cuda (csrc/api/kda_sm100.cu:22-120), so the fp32 gate, q-hat and k-hat never
 // travel through HBM.
+//
+// Exponent handling ("safe gate"): 2^(g_i - g_j) is never formed directly inside an MMA operand. Row i of
+// 16-row block I is scaled by 2^(g_i - r_I) (<= 1, r_I = g at the first row of the block) and column j by
+// 2^(r_I - g_j), which is <= 1 for earlier blocks and at most 2^(15*5*log2 e) ~ 2^108 inside block I.
+// So the B operand holds one copy of k-hat per anchor: 16 + 32 + 48 + 64 = 160 rows; the A operand
+// is [q-hat ; k-hat] scaled by their own block anchors (128 rows). Column block I of the 128 x 160
+// product is valid on the rows of block I only; the epilogue reads exactly those.
+//
+// Two CTAs are resident per SM (111 KB shared memory, 256 TMEM columns each), so one CTA's MUFU-heavy
+// operand generation overlaps the other's MMA, inverse and epilogues.
 #include "kda_common.cuh"
 #include "kda_params.h"
+#include "umma.cuh"
 
 namespace kda {
 
 constexpr int INTRA_THREADS = 256;
 
-struct IntraSmem {
-    float G[BT][DK];      // cumulative log2 gate; rows past the last real token repeat the last value
-    float Q[BT][DK];      // q-hat (zero for padding rows)
-    float Kh[BT][DK];     // k-hat (zero for padding rows)
-    float L[BT][BT];      // strictly lower: beta_i * sum_d k_i k_j 2^(g_i-g_j)
-    float P[BT][BT];      // lower incl. diagonal: scale * sum_d q_i k_j 2^(g_i-g_j)
-    float A[BT][BT];      // (I + L)^-1
-    float beta[BT];
-    float half_total[DK];
-};
+// shared-memory map (bytes from a 1024-aligned base)
+constexpr int SM_OPA = 0;                 // A operand of one 64-channel half: [2 k-atoms][128 rows][128 B], SW128
+constexpr int SM_OPB = 32768;             // B operand: [2 k-atoms][160 rows][128 B], SW128
+constexpr int SM_G = 73728;               // G [64][128] fp32
+constexpr int SM_TAB = 106496;            // 10 x [128] fp32 anchor tables
+constexpr int SM_MISC = 111616;           // beta[64], barriers, tmem base, half totals
+constexpr int SM_TOTAL = 112640;
+constexpr int KATOM_A = 16384, KATOM_B = 20480;
+// regions reused once the Gram MMAs have completed
+constexpr int SM_XS = SM_OPA;             // X = beta k 2^g, fp16 [2 mn-atoms][64 tokens][128 B], SW128 (MN-major A operand)
+constexpr int SM_YS = SM_OPA + 16384;     // Y = beta v, same layout
+constexpr int LROW = 68;                  // padded fp32 row of the 64x64 matrices
+constexpr int SM_LF = SM_OPB;             // L fp32 [64][68]
+constexpr int SM_AINV = SM_OPB + 17408;   // (I+L)^-1 fp32 [64][68]
+constexpr int SM_TM = SM_OPB + 34816;     // scratch for the block products [32][36]
+constexpr int TROW = 36;
+constexpr int SM_AKK16 = SM_G;            // Akk fp16 [64][128 B], SW128 (K-major B operand)
 
+// anchor tables
+constexpr int TAB_E = 0;     // [4]  2^(r_I)
+constexpr int TAB_T1 = 4;    // [3]  2^(g_last - r_{I+1}),  I = 0..2
+constexpr int TAB_T2 = 7;    // [3]  2^(r_2 - r_1), 2^(r_3 - r_1), 2^(r_3 - r_2)
+
+__device__ __forceinline__ uint64_t sdesc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return umma::make_sdesc(addr, lbo, sbo) | (2ull << 61);
+}
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ float4 tf32x4(float a, float b, float c, float d) {
+    return make_float4(to_tf32(a), to_tf32(b), to_tf32(c), to_tf32(d));
+}
 __device__ __forceinline__ float load_gate_raw(const void* g, int g_fp32, size_t idx) {
     return g_fp32 ? reinterpret_cast<const float*>(g)[idx]
                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g)[idx]);
 }
-
 __device__ __forceinline__ float gate_activation(float graw, float alpha, float bias, int gate_mode, float lower_bound) {
     if (gate_mode == GATE_NONE) return graw;
     float x = graw + bias;
-    if (gate_mode == GATE_LOWER_BOUND) return lower_bound / (1.f + __expf(-alpha * x));
-    // softplus with the usual large-argument shortcut
+    if (gate_mode == GATE_LOWER_BOUND) return __fdividef(lower_bound, 1.f + __expf(-alpha * x));
     return -alpha * (x > 20.f ? x : log1pf(__expf(x)));
 }
 
-__global__ void __launch_bounds__(INTRA_THREADS, 1) kda_fwd_intra_kernel(const IntraParams p) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    IntraSmem& s = *reinterpret_cast<IntraSmem*>(smem_raw);
+__global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const IntraParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t sm_u32 = smem_u32(sm);
+    float* sG = reinterpret_cast<float*>(sm + SM_G);
+    float* sTab = reinterpret_cast<float*>(sm + SM_TAB);
+    float* sBeta = reinterpret_cast<float*>(sm + SM_MISC);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SM_MISC + 256);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + SM_MISC + 288);
+    float* sHalf = reinterpret_cast<float*>(sm + SM_MISC + 512);
+
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
     const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
-    const size_t tok_stride = (size_t)p.H * DK;          // elements between consecutive tokens (K == V)
+    const size_t tok_stride = (size_t)p.H * DK;
     const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DK;
     unsigned char* tile = p.tiles + ((size_t)c * p.H + h) * TP_BYTES;
 
-    // ---- 1. gate activation + cumulative sum down the 64 rows, two half-columns per channel ----
+    if (tid == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_init(&bars[2], 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) umma::tmem_alloc(tmem_slot, 256);
+
+    // ---- 1. gate activation + cumulative sum down the 64 rows (two half-columns per channel) ----
     {
         const int d = tid & 127, half = tid >> 7;
         const float alpha = p.gate_mode != GATE_NONE ? __expf(p.A_log[h]) : 0.f;
         const float bias = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + d] : 0.f;
         float run = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int r = 0; r < 32; ++r) {
             int row = half * 32 + r;
             float a = 0.f;
             if (row < ci.valid)
                 a = gate_activation(load_gate_raw(p.g, p.g_fp32, base + (size_t)row * tok_stride + d), alpha, bias,
                                     p.gate_mode, p.lower_bound);
-            run += a * RCP_LN2;
-            s.G[row][d] = run;
+            run = fmaf(a, RCP_LN2, run);
+            sG[row * DK + d] = run;
         }
-        if (half == 0) s.half_total[d] = run;
-        __syncthreads();
-        if (half == 1) {
-            float t0 = s.half_total[d];
-#pragma unroll 4
-            for (int r = 32; r < 64; ++r) s.G[r][d] += t0;
-        }
+        if (half == 0) sHalf[d] = run;
     }
-    // ---- 2. L2 norms (a warp per row), beta ----
+    // ---- 2. q, k rows into registers, L2 norms. Thread (rq, l8): rows rq and rq+32, channels
+    //         32*grp + 4*l8 .. +3 for the four channel groups grp ----
+    const int l8 = tid & 7, rq = tid >> 3;
+    uint2 qraw[2][4], kraw[2][4];
+    float rstd_q[2], rstd_k[2], bet[2];
     {
         const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q);
         const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(p.k);
-        for (int r = 0; r < 8; ++r) {
-            int row = warp * 8 + r;
-            float qv[4] = {0, 0, 0, 0}, kv[4] = {0, 0, 0, 0};
-            if (row < ci.valid) {
-                uint2 qr = *reinterpret_cast<const uint2*>(qp + base + (size_t)row * tok_stride + lane * 4);
-                uint2 kr = *reinterpret_cast<const uint2*>(kp + base + (size_t)row * tok_stride + lane * 4);
-                float2 a = unpack_bf16(qr.x), b = unpack_bf16(qr.y);
-                qv[0] = a.x; qv[1] = a.y; qv[2] = b.x; qv[3] = b.y;
-                a = unpack_bf16(kr.x); b = unpack_bf16(kr.y);
-                kv[0] = a.x; kv[1] = a.y; kv[2] = b.x; kv[3] = b.y;
-            }
-            float rq = 1.f, rk = 1.f;
-            if (p.use_l2norm) {
-                float sq = qv[0] * qv[0] + qv[1] * qv[1] + qv[2] * qv[2] + qv[3] * qv[3];
-                float sk = kv[0] * kv[0] + kv[1] * kv[1] + kv[2] * kv[2] + kv[3] * kv[3];
 #pragma unroll
-                for (int o = 16; o; o >>= 1) {
-                    sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        for (int rs = 0; rs < 2; ++rs) {
+            const int row = rq + 32 * rs;
+            float sq = 0.f, sk = 0.f;
+#pragma unroll
+            for (int grp = 0; grp < 4; ++grp) {
+                uint2 qv = make_uint2(0, 0), kv = make_uint2(0, 0);
+                if (row < ci.valid) {
+                    size_t off = base + (size_t)row * tok_stride + 32 * grp + 4 * l8;
+                    qv = *reinterpret_cast<const uint2*>(qp + off);
+                    kv = *reinterpret_cast<const uint2*>(kp + off);
                 }
-                rq = rsqrtf(sq + 1e-6f);
-                rk = rsqrtf(sk + 1e-6f);
+                qraw[rs][grp] = qv;
+                kraw[rs][grp] = kv;
+                float2 a = unpack_bf16(qv.x), b = unpack_bf16(qv.y);
+                sq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+                a = unpack_bf16(kv.x); b = unpack_bf16(kv.y);
+                sk += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
             }
-            *reinterpret_cast<float4*>(&s.Q[row][lane * 4]) = make_float4(qv[0] * rq, qv[1] * rq, qv[2] * rq, qv[3] * rq);
-            *reinterpret_cast<float4*>(&s.Kh[row][lane * 4]) = make_float4(kv[0] * rk, kv[1] * rk, kv[2] * rk, kv[3] * rk);
-        }
-        if (tid < BT) {
             float b = 0.f;
-            if (tid < ci.valid) {
-                size_t bi = (size_t)(ci.row0 + tid) * p.H + h;
+            if (row < ci.valid) {
+                size_t bi = (size_t)(ci.row0 + row) * p.H + h;
                 b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
             }
-            s.beta[tid] = b;
-        }
-        for (int i = tid; i < BT * BT; i += INTRA_THREADS) {
-            (&s.L[0][0])[i] = 0.f;
-            (&s.P[0][0])[i] = 0.f;
+            bet[rs] = b;
+            if (l8 == 0) sBeta[row] = b;
+            if (p.use_l2norm) {
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+                    sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                }
+                rstd_q[rs] = rsqrtf(sq + 1e-6f);
+                rstd_k[rs] = rsqrtf(sk + 1e-6f);
+            } else {
+                rstd_q[rs] = rstd_k[rs] = 1.f;
+            }
         }
     }
     __syncthreads();
+    if (tid >= 128) {   // second half of every column adds the first half's total
+        const int d = tid & 127;
+        const float t0 = sHalf[d];
+#pragma unroll 8
+        for (int r = 32; r < 64; ++r) sG[r * DK + d] += t0;
+    }
+    __syncthreads();
+    // ---- anchor tables (r_I = G[16 I], g_last = G[63]) ----
+    for (int i = tid; i < 10 * DK; i += INTRA_THREADS) {
+        const int t = i >> 7, d = i & 127;
+        const float r0 = sG[d], r1 = sG[16 * DK + d], r2 = sG[32 * DK + d], r3 = sG[48 * DK + d], gl = sG[63 * DK + d];
+        float x;
+        switch (t) {
+            case 0: x = r0; break;
+            case 1: x = r1; break;
+            case 2: x = r2; break;
+            case 3: x = r3; break;
+            case 4: x = gl - r1; break;
+            case 5: x = gl - r2; break;
+            case 6: x = gl - r3; break;
+            case 7: x = r2 - r1; break;
+            case 8: x = r3 - r1; break;
+            default: x = r3 - r2; break;
+        }
+        sTab[i] = fast_exp2(x);
+    }
+    if (tid < DK) reinterpret_cast<float*>(tile + TP_DECAY)[tid] = fast_exp2(sG[63 * DK + tid]);
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
 
-    // ---- 3. gated Gram matrices on the lower-triangular 4x4 blocks (136 of them); the other
-    //         threads meanwhile emit kg, qg and the decay vector ----
-    if (tid < 136) {
-        int bi = (int)((sqrtf(8.f * tid + 1.f) - 1.f) * 0.5f);
-        while ((bi + 1) * (bi + 2) / 2 <= tid) ++bi;
-        while (bi * (bi + 1) / 2 > tid) --bi;
-        const int bj = tid - bi * (bi + 1) / 2;
-        float accP[4][4], accL[4][4];
+    // ---- 3. operand generation + Gram MMAs, one 64-channel half at a time ----
+    uint2 xpk[2][4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-            for (int b = 0; b < 4; ++b) accP[a][b] = accL[a][b] = 0.f;
-        for (int dd = 0; dd < DK; ++dd) {
-            const int d = (dd + lane) & (DK - 1);      // rotate per lane: conflict-free column reads
-            float qi[4], ki[4], gi[4], kj[4], gj[4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                qi[a] = s.Q[4 * bi + a][d];
-                ki[a] = s.Kh[4 * bi + a][d];
-                gi[a] = s.G[4 * bi + a][d];
-                kj[a] = s.Kh[4 * bj + a][d];
-                gj[a] = s.G[4 * bj + a][d];
-            }
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    float e = fast_exp2(fminf(gi[a] - gj[b], 0.f)) * kj[b];
-                    accP[a][b] = fmaf(qi[a], e, accP[a][b]);
-                    accL[a][b] = fmaf(ki[a], e, accL[a][b]);
-                }
+    for (int hf = 0; hf < 2; ++hf) {
+        if (hf == 1) {   // operand buffers are reused: wait until the first half's MMAs have read them
+            if (!mbar_wait(&bars[0], 0)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+            umma::fence_after_sync();
         }
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int rs = 0; rs < 2; ++rs) {
+            const int row = rq + 32 * rs, I = row >> 4, r7 = row & 7;
+            const int rowN = (I < 3) ? 16 * (I + 1) : 63;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                int i = 4 * bi + a, j = 4 * bj + b;
-                s.P[i][j] = (j <= i) ? p.scale * accP[a][b] : 0.f;
-                s.L[i][j] = (j < i) ? s.beta[i] * accL[a][b] : 0.f;
+            for (int it = 0; it < 2; ++it) {
+                const int grp = hf * 2 + it, d0 = 32 * grp + 4 * l8;
+                const float4 Gi = *reinterpret_cast<const float4*>(sG + row * DK + d0);
+                const float4 rI = *reinterpret_cast<const float4*>(sG + 16 * I * DK + d0);
+                const float4 rN = *reinterpret_cast<const float4*>(sG + rowN * DK + d0);
+                const float4 tE = *reinterpret_cast<const float4*>(sTab + (TAB_E + I) * DK + d0);
+                float4 t1 = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (I < 3) t1 = *reinterpret_cast<const float4*>(sTab + (TAB_T1 + I) * DK + d0);
+                const float gi[4] = {Gi.x, Gi.y, Gi.z, Gi.w}, ri[4] = {rI.x, rI.y, rI.z, rI.w};
+                const float rn[4] = {rN.x, rN.y, rN.z, rN.w}, te[4] = {tE.x, tE.y, tE.z, tE.w};
+                const float tt1[4] = {t1.x, t1.y, t1.z, t1.w};
+                float qv[4], kv[4];
+                {
+                    float2 a = unpack_bf16(qraw[rs][grp].x), b = unpack_bf16(qraw[rs][grp].y);
+                    qv[0] = a.x * rstd_q[rs]; qv[1] = a.y * rstd_q[rs]; qv[2] = b.x * rstd_q[rs]; qv[3] = b.y * rstd_q[rs];
+                    a = unpack_bf16(kraw[rs][grp].x); b = unpack_bf16(kraw[rs][grp].y);
+                    kv[0] = a.x * rstd_k[rs]; kv[1] = a.y * rstd_k[rs]; kv[2] = b.x * rstd_k[rs]; kv[3] = b.y * rstd_k[rs];
+                }
+                float qa[4], ka[4], kown[4], kend[4], kg[4], qg[4], xx[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float eA = fast_exp2(gi[e] - ri[e]);      // <= 1
+                    const float eB = fast_exp2(ri[e] - gi[e]);      // >= 1, <= 2^108 under the safe gate
+                    const float eE = fast_exp2(rn[e] - gi[e]);      // decay to the end of the block, <= 1
+                    qa[e] = qv[e] * eA;
+                    ka[e] = kv[e] * eA;
+                    kown[e] = kv[e] * eB;
+                    kend[e] = kv[e] * eE;
+                    kg[e] = kend[e] * tt1[e];
+                    const float eG = eA * te[e];                    // 2^(g_i)
+                    qg[e] = p.scale * qv[e] * eG;
+                    xx[e] = bet[rs] * kv[e] * eG;
+                }
+                const uint32_t sw = (uint32_t)((l8 ^ r7) << 4);
+                unsigned char* opa = sm + SM_OPA + it * KATOM_A + sw;
+                unsigned char* opb = sm + SM_OPB + it * KATOM_B + sw;
+                *reinterpret_cast<float4*>(opa + row * 128) = tf32x4(qa[0], qa[1], qa[2], qa[3]);
+                *reinterpret_cast<float4*>(opa + (row + 64) * 128) = tf32x4(ka[0], ka[1], ka[2], ka[3]);
+                *reinterpret_cast<float4*>(opb + (8 * I * (I + 1) + row) * 128) = tf32x4(kown[0], kown[1], kown[2], kown[3]);
+#pragma unroll
+                for (int Ip = 1; Ip < 4; ++Ip) {
+                    if (Ip > I) {
+                        float4 f = make_float4(1.f, 1.f, 1.f, 1.f);
+                        if (Ip > I + 1)   // (Ip, I+1) in {(2,1),(3,1),(3,2)}
+                            f = *reinterpret_cast<const float4*>(sTab + (TAB_T2 + (Ip == 2 ? 0 : I + 1)) * DK + d0);
+                        *reinterpret_cast<float4*>(opb + (8 * Ip * (Ip + 1) + row) * 128) =
+                            tf32x4(kend[0] * f.x, kend[1] * f.y, kend[2] * f.z, kend[3] * f.w);
+                    }
+                }
+                const int goff = swz256(row, d0);
+                *reinterpret_cast<uint2*>(tile + TP_KG + goff) = make_uint2(pack_f16(kg[0], kg[1]), pack_f16(kg[2], kg[3]));
+                *reinterpret_cast<uint2*>(tile + TP_QG + goff) = make_uint2(pack_f16(qg[0], qg[1]), pack_f16(qg[2], qg[3]));
+                xpk[rs][grp] = make_uint2(pack_f16(xx[0], xx[1]), pack_f16(xx[2], xx[3]));
             }
+        }
+        fence_proxy_async();
+        umma::fence_before_sync();
+        __syncthreads();
+        if (tid == 0) {
+            umma::fence_after_sync();
+            const uint32_t idesc = umma::make_idesc(umma::FMT_TF32, 128, 160, false, false);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint64_t ad = sdesc_sw128(sm_u32 + SM_OPA + (ks >> 2) * KATOM_A + (ks & 3) * 32, 16, 1024);
+                const uint64_t bd = sdesc_sw128(sm_u32 + SM_OPB + (ks >> 2) * KATOM_B + (ks & 3) * 32, 16, 1024);
+                umma::mma_tf32(tmem, ad, bd, idesc, (hf | ks) != 0);
+            }
+            umma::commit(&bars[hf]);
+        }
+    }
+    if (!mbar_wait(&bars[1], 0)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+    umma::fence_after_sync();
+
+    // ---- 4. X into shared memory (all threads); warps 0-3: Gram epilogue; warps 4-7: Y = beta v ----
+#pragma unroll
+    for (int rs = 0; rs < 2; ++rs) {
+        const int row = rq + 32 * rs;
+#pragma unroll
+        for (int grp = 0; grp < 4; ++grp) {
+            const int chunk = 4 * (grp & 1) + (l8 >> 1);
+            *reinterpret_cast<uint2*>(sm + SM_XS + (grp >> 1) * 8192 + row * 128 + ((chunk ^ (row & 7)) << 4) + (l8 & 1) * 8) =
+                xpk[rs][grp];
+        }
+    }
+    float* sL = reinterpret_cast<float*>(sm + SM_LF);
+    float* sAi = reinterpret_cast<float*>(sm + SM_AINV);
+    float* sT = reinterpret_cast<float*>(sm + SM_TM);
+    if (warp < 4) {
+        // TMEM lane = 32*warp + lane: lanes 0..63 are q rows (-> Aqk), 64..127 k rows (-> L)
+        const int row = (warp & 1) * 32 + lane;
+        const int I = row >> 4;
+        const bool is_q = warp < 2;
+        const float bi = sBeta[row];
+        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+        for (int bsel = 0; bsel < 2; ++bsel) {
+            const int blk = (warp & 1) * 2 + bsel;          // the two 16-row blocks living in this warp
+#pragma unroll
+            for (int gcol = 0; gcol < 4; ++gcol) {
+                uint32_t r[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) r[e] = 0u;
+                if (gcol <= blk) {                           // warp-uniform
+                    umma::ld_32x32b_x16(taddr + 8 * blk * (blk + 1) + 16 * gcol, r);
+                    umma::wait_ld();
+                }
+                if (I == blk) {
+                    float vals[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int j = 16 * gcol + e;
+                        float x = __uint_as_float(r[e]);
+                        if (is_q) x = (j <= row) ? p.scale * x : 0.f;
+                        else x = (j < row) ? bi * x : 0.f;
+                        vals[e] = x;
+                    }
+                    if (is_q) {
+#pragma unroll
+                        for (int hc = 0; hc < 2; ++hc) {
+                            uint4 pk = make_uint4(pack_f16(vals[8 * hc], vals[8 * hc + 1]), pack_f16(vals[8 * hc + 2], vals[8 * hc + 3]),
+                                                  pack_f16(vals[8 * hc + 4], vals[8 * hc + 5]), pack_f16(vals[8 * hc + 6], vals[8 * hc + 7]));
+                            *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol + 8 * hc)) = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4)
+                            *reinterpret_cast<float4*>(sL + row * LROW + 16 * gcol + 4 * q4) =
+                                make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
+                    }
+                }
+            }
+        }
     } else {
-        // kg / qg: one item = (row, 8 consecutive channels) -> one 16-byte store each
-        for (int it = tid - 136; it < BT * 16; it += INTRA_THREADS - 136) {
-            int row = it >> 4, ch = it & 15;
-            uint32_t kgp[4], qgp[4];
+        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(p.v);
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int idx = (tid - 128) + 128 * n, j = idx >> 4, ch = idx & 15;
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (j < ci.valid) raw = *reinterpret_cast<const uint4*>(vp + base + (size_t)j * tok_stride + 8 * ch);
+            const float b = sBeta[j];
+            const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+            uint32_t o4[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                int d = ch * 8 + 2 * e;
-                float g0 = s.G[row][d], g1 = s.G[row][d + 1];
-                float gl0 = s.G[BT - 1][d], gl1 = s.G[BT - 1][d + 1];
-                kgp[e] = pack_f16(s.Kh[row][d] * fast_exp2(gl0 - g0), s.Kh[row][d + 1] * fast_exp2(gl1 - g1));
-                qgp[e] = pack_f16(p.scale * s.Q[row][d] * fast_exp2(g0), p.scale * s.Q[row][d + 1] * fast_exp2(g1));
+                float2 f = unpack_bf16(w4[e]);
+                o4[e] = pack_f16(b * f.x, b * f.y);
             }
-            int off = swz256(row, ch * 8);
-            *reinterpret_cast<uint4*>(tile + TP_KG + off) = make_uint4(kgp[0], kgp[1], kgp[2], kgp[3]);
-            *reinterpret_cast<uint4*>(tile + TP_QG + off) = make_uint4(qgp[0], qgp[1], qgp[2], qgp[3]);
+            *reinterpret_cast<uint4*>(sm + SM_YS + (ch >> 3) * 8192 + j * 128 + (((ch & 7) ^ (j & 7)) << 4)) =
+                make_uint4(o4[0], o4[1], o4[2], o4[3]);
         }
-        for (int d = tid - 136; d < DK; d += INTRA_THREADS - 136)
-            reinterpret_cast<float*>(tile + TP_DECAY)[d] = fast_exp2(s.G[BT - 1][d]);
     }
+    umma::fence_before_sync();
     __syncthreads();
 
-    // ---- 4. Akk = (I + L)^-1 by forward substitution, one column per thread (64 threads) ----
-    if (tid < BT) {
-        float x[BT];
+    // ---- 5. Akk = (I + L)^-1: 16x16 diagonal blocks by substitution, then 16->32->64 block merges ----
+    if (tid < 64) {
+        const int b = tid >> 4, cc = tid & 15;
+        float x[16];
 #pragma unroll
-        for (int i = 0; i < BT; ++i) {
-            float acc = (i == tid) ? 1.f : 0.f;
+        for (int i = 0; i < 16; ++i) {
+            float acc = (i == cc) ? 1.f : 0.f;
 #pragma unroll
-            for (int j = 0; j < i; ++j) acc = fmaf(-s.L[i][j], x[j], acc);
+            for (int j = 0; j < i; ++j) acc = fmaf(-sL[(16 * b + i) * LROW + 16 * b + j], x[j], acc);
             x[i] = acc;
         }
 #pragma unroll
-        for (int i = 0; i < BT; ++i) s.A[i][tid] = x[i];
-    } else {
-        // Aqk (fp16) into the pack
-        for (int it = tid - BT; it < BT * 8; it += INTRA_THREADS - BT) {
-            int row = it >> 3, ch = it & 7;
-            uint32_t pk[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) pk[e] = pack_f16(s.P[row][ch * 8 + 2 * e], s.P[row][ch * 8 + 2 * e + 1]);
-            *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, ch * 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        }
+        for (int i = 0; i < 16; ++i) sAi[(16 * b + i) * LROW + 16 * b + cc] = x[i];
     }
     __syncthreads();
+    {   // level 1: blocks (1,0) and (3,2):  X = -D2inv * (C * D1inv)
+        const int pr = tid >> 7, i = (tid >> 3) & 15, j0 = (tid & 7) * 2;
+        const int r0 = 32 * pr + 16, c0 = 32 * pr;
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float cv = sL[(r0 + i) * LROW + c0 + k];
+            a0 = fmaf(cv, sAi[(c0 + k) * LROW + c0 + j0], a0);
+            a1 = fmaf(cv, sAi[(c0 + k) * LROW + c0 + j0 + 1], a1);
+        }
+        sT[(16 * pr + i) * TROW + j0] = a0;
+        sT[(16 * pr + i) * TROW + j0 + 1] = a1;
+        __syncthreads();
+        a0 = a1 = 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float dv = sAi[(r0 + i) * LROW + r0 + k];
+            a0 = fmaf(dv, sT[(16 * pr + k) * TROW + j0], a0);
+            a1 = fmaf(dv, sT[(16 * pr + k) * TROW + j0 + 1], a1);
+        }
+        sAi[(r0 + i) * LROW + c0 + j0] = -a0;
+        sAi[(r0 + i) * LROW + c0 + j0 + 1] = -a1;
+    }
+    __syncthreads();
+    {   // level 2: block rows 32..63 x cols 0..31:  X = -A2inv * (C * A1inv)
+        const int i = tid >> 3, j0 = (tid & 7) * 4;
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k = j0; k < 32; ++k) {      // A1inv is lower triangular: rows k < j0 contribute nothing
+            const float cv = sL[(32 + i) * LROW + k];
+            const float4 av = *reinterpret_cast<const float4*>(sAi + k * LROW + j0);
+            a[0] = fmaf(cv, av.x, a[0]);
+            a[1] = fmaf(cv, (k >= j0 + 1) ? av.y : 0.f, a[1]);
+            a[2] = fmaf(cv, (k >= j0 + 2) ? av.z : 0.f, a[2]);
+            a[3] = fmaf(cv, (k >= j0 + 3) ? av.w : 0.f, a[3]);
+        }
+        *reinterpret_cast<float4*>(sT + i * TROW + j0) = make_float4(a[0], a[1], a[2], a[3]);
+        __syncthreads();
+        a[0] = a[1] = a[2] = a[3] = 0.f;
+        for (int k = 0; k <= i; ++k) {       // A2inv is lower triangular
+            const float dv = sAi[(32 + i) * LROW + 32 + k];
+            const float4 tv = *reinterpret_cast<const float4*>(sT + k * TROW + j0);
+            a[0] = fmaf(dv, tv.x, a[0]);
+            a[1] = fmaf(dv, tv.y, a[1]);
+            a[2] = fmaf(dv, tv.z, a[2]);
+            a[3] = fmaf(dv, tv.w, a[3]);
+        }
+        *reinterpret_cast<float4*>(sAi + (32 + i) * LROW + j0) = make_float4(-a[0], -a[1], -a[2], -a[3]);
+    }
+    __syncthreads();
+    {   // Akk -> fp16 K-major operand (and fp32 to HBM when the backward pass wants it)
+        const int row = tid >> 2, c16 = (tid & 3) * 16;
+        float v[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const int j = c16 + e;
+            v[e] = (j <= row) ? sAi[row * LROW + j] : 0.f;
+        }
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+            const int ch = (c16 >> 3) + hc;
+            *reinterpret_cast<uint4*>(sm + SM_AKK16 + row * 128 + ((ch ^ (row & 7)) << 4)) =
+                make_uint4(pack_f16(v[8 * hc], v[8 * hc + 1]), pack_f16(v[8 * hc + 2], v[8 * hc + 3]),
+                           pack_f16(v[8 * hc + 4], v[8 * hc + 5]), pack_f16(v[8 * hc + 6], v[8 * hc + 7]));
+        }
+        if (p.akk_out) {
+            float* ao = p.akk_out + ((size_t)c * p.H + h) * BT * BT + row * BT + c16;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<float4*>(ao + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+        }
+    }
+    fence_proxy_async();
+    umma::fence_before_sync();
+    __syncthreads();
 
-    // ---- 5. w = Akk X (threads 0..127, one key channel each), u = Akk Y (threads 128..255) ----
+    // ---- 6. w^T = X^T Akk^T (TMEM columns 0..63), u^T = Y^T Akk^T (columns 64..127) ----
+    if (tid == 0) {
+        umma::fence_after_sync();
+        const uint32_t idesc = umma::make_idesc(umma::FMT_F16, 128, 64, true, false);
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint64_t ad = sdesc_sw128(sm_u32 + (which ? SM_YS : SM_XS) + ks * 2048, 8192, 1024);
+                const uint64_t bd = sdesc_sw128(sm_u32 + SM_AKK16 + ks * 32, 16, 1024);
+                umma::mma_f16(tmem + 64 * which, ad, bd, idesc, ks != 0);
+            }
+        }
+        umma::commit(&bars[2]);
+    }
+    if (!mbar_wait(&bars[2], 0)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+    umma::fence_after_sync();
+
+    // ---- 7. epilogue: lane = channel, columns = tokens; fp16 into the swizzled tile pack ----
     {
-        const int col = tid & 127, is_u = tid >> 7;
-        float x[BT];
-        if (is_u) {
-            const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(p.v);
+        const int qd = warp & 3, which = warp >> 2, d = 32 * qd + lane;
+        const uint32_t taddr = tmem + ((uint32_t)(32 * qd) << 16) + 64 * which;
+        unsigned char* dst = which ? tile + (d < 64 ? TP_U0 : TP_U1) : tile + TP_W;
 #pragma unroll
-            for (int j = 0; j < BT; ++j)
-                x[j] = (j < ci.valid) ? s.beta[j] * __bfloat162float(vp[base + (size_t)j * tok_stride + col]) : 0.f;
-        } else {
+        for (int cg = 0; cg < 4; ++cg) {
+            uint32_t r[16];
+            umma::ld_32x32b_x16(taddr + 16 * cg, r);
+            umma::wait_ld();
 #pragma unroll
-            for (int j = 0; j < BT; ++j) x[j] = s.beta[j] * s.Kh[j][col] * fast_exp2(s.G[j][col]);
-        }
-        unsigned char* dst = is_u ? tile + (col < 64 ? TP_U0 : TP_U1) : tile + TP_W;
-#pragma unroll
-        for (int i = 0; i < BT; ++i) {
-            float acc = 0.f;
-#pragma unroll
-            for (int j = 0; j <= i; ++j) acc = fmaf(s.A[i][j], x[j], acc);
-            if (is_u) *reinterpret_cast<__half*>(dst + swz128(i, col & 63)) = __float2half_rn(acc);
-            else *reinterpret_cast<__half*>(dst + swz256(i, col)) = __float2half_rn(acc);
+            for (int e = 0; e < 16; ++e) {
+                const int tok = 16 * cg + e;
+                const __half hv = __float2half_rn(__uint_as_float(r[e]));
+                if (which) *reinterpret_cast<__half*>(dst + swz128(tok, d & 63)) = hv;
+                else *reinterpret_cast<__half*>(dst + swz256(tok, d)) = hv;
+            }
         }
     }
-    // ---- 6. optional: Akk for the backward pass, fp32 row-major ----
-    if (p.akk_out) {
-        float* ao = p.akk_out + ((size_t)c * p.H + h) * BT * BT;
-        for (int i = tid; i < BT * BT; i += INTRA_THREADS) ao[i] = (&s.A[0][0])[i];
-    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 256);
 }
 
 }  // namespace kda
 
-extern "C" int kda_fwd_intra_smem_bytes() { return (int)sizeof(kda::IntraSmem); }
+extern "C" int kda_fwd_intra_smem_bytes() { return kda::SM_TOTAL + 1024; }
 
 extern "C" int kda_launch_fwd_intra(const kda::IntraParams* p, int num_chunks, cudaStream_t stream) {
     using namespace kda;
-    static_assert(sizeof(IntraSmem) <= 227 * 1024, "smem budget");
     if (num_chunks <= 0) return 0;
-    cudaError_t e = cudaFuncSetAttribute(kda_fwd_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)sizeof(IntraSmem));
+    const int smem = SM_TOTAL + 1024;
+    cudaError_t e = cudaFuncSetAttribute(kda_fwd_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    kda_fwd_intra_kernel<<<num_chunks * p->H, INTRA_THREADS, sizeof(IntraSmem), stream>>>(*p);
+    kda_fwd_intra_kernel<<<num_chunks * p->H, INTRA_THREADS, smem, stream>>>(*p);
     return (int)cudaGetLastError();
 }

@@ -23,6 +23,7 @@ struct IntraParams {
     const int* chunk_indices; // [NT][2] or null (fixed length)
     unsigned char* tiles;     // [NT*H] tile packs
     float* akk_out;           // [NT*H][64][64] fp32 or null
+    int* status;              // device status word
     int T;                    // tokens per sequence when cu_seqlens is null
     int H;
     int g_fp32;

@@ -75,7 +75,7 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
         q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32),
         beta.data_ptr(), int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias),
         cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
-        float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), stream),
+        float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), _status_word(dev).data_ptr(), stream),
         "cula_kda_fwd_intra")
     final_state = torch.empty(n_seqs, H, K, v.shape[-1], dtype=torch.float32, device=dev) if output_final_state else None
     h = vnew = None

@@ -48,6 +48,7 @@ int cula_kda_fwd_scan_smem_bytes(void);
  * d_cu_seqlens [N+1] / d_chunk_indices [num_chunks][2] (sequence, chunk-in-sequence) are the tables of
  * prepare_chunk_indices; pass both NULL for a fixed-length batch of sequences of T tokens.
  * d_tiles: num_chunks*H tile packs (output). d_akk: optional [num_chunks*H][64][64] fp32 (I+L)^-1.
+ * d_status: one int the kernel sets non-zero if a bounded wait on a tensor-core completion barrier gave up.
  */
 int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* d_v,
                        const void* d_g, int g_is_fp32,
@@ -56,7 +57,7 @@ int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* d_v,
                        const int* d_cu_seqlens, const int* d_chunk_indices,
                        int num_chunks, int T, int H,
                        float scale, int use_qk_l2norm, int gate_mode, float lower_bound,
-                       void* d_tiles, float* d_akk, void* stream);
+                       void* d_tiles, float* d_akk, int* d_status, void* stream);
 
 /*
  * Sequential state scan fused with the output stage, one CTA per (sequence, head, value half).
