@@ -73,6 +73,35 @@ __device__ __forceinline__ float gate_activation(float graw, float alpha, float 
     return -alpha * (x > 20.f ? x : log1pf(__expf(x)));
 }
 
+// D(16x8) += A(16 x 8*KT) * B(8*KT x 8) with A, B fp32 in shared memory (row-major, strides lda/ldb),
+// evaluated as three TF32 MMAs per k-step on the hi/lo split of both operands.
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(x - __uint_as_float(hi)));
+}
+__device__ __forceinline__ void mma_tf32_16x8x8(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+template <int KT>
+__device__ __forceinline__ void mma_tile_3xtf32(const float* A, int lda, const float* B, int ldb, float (&acc)[4], int g, int t) {
+#pragma unroll
+    for (int ks = 0; ks < KT; ++ks) {
+        const float af[4] = {A[g * lda + 8 * ks + t], A[(g + 8) * lda + 8 * ks + t], A[g * lda + 8 * ks + t + 4],
+                             A[(g + 8) * lda + 8 * ks + t + 4]};
+        const float bf[2] = {B[(8 * ks + t) * ldb + g], B[(8 * ks + t + 4) * ldb + g]};
+        uint32_t ah[4], al[4], bh[2], bl[2];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split_tf32(af[e], ah[e], al[e]);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) split_tf32(bf[e], bh[e], bl[e]);
+        mma_tf32_16x8x8(acc, al, bh);
+        mma_tf32_16x8x8(acc, ah, bl);
+        mma_tf32_16x8x8(acc, ah, bh);
+    }
+}
+
 __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const IntraParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -85,11 +114,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     float* sHalf = reinterpret_cast<float*>(sm + SM_MISC + 512);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
-    const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
     const size_t tok_stride = (size_t)p.H * DK;
-    const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DK;
-    unsigned char* tile = p.tiles + ((size_t)c * p.H + h) * TP_BYTES;
+    const int l8 = tid & 7, rq = tid >> 3;
 
     if (tid == 0) {
         mbar_init(&bars[0], 1);
@@ -98,37 +124,28 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         fence_mbar_init();
     }
     if (warp == 0) umma::tmem_alloc(tmem_slot, 256);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
 
-    // ---- 1. gate activation + cumulative sum down the 64 rows (two half-columns per channel) ----
-    {
-        const int d = tid & 127, half = tid >> 7;
-        const float alpha = p.gate_mode != GATE_NONE ? __expf(p.A_log[h]) : 0.f;
-        const float bias = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + d] : 0.f;
-        float run = 0.f;
-#pragma unroll 8
-        for (int r = 0; r < 32; ++r) {
-            int row = half * 32 + r;
-            float a = 0.f;
-            if (row < ci.valid)
-                a = gate_activation(load_gate_raw(p.g, p.g_fp32, base + (size_t)row * tok_stride + d), alpha, bias,
-                                    p.gate_mode, p.lower_bound);
-            run = fmaf(a, RCP_LN2, run);
-            sG[row * DK + d] = run;
-        }
-        if (half == 0) sHalf[d] = run;
-    }
-    // ---- 2. q, k rows into registers, L2 norms. Thread (rq, l8): rows rq and rq+32, channels
-    //         32*grp + 4*l8 .. +3 for the four channel groups grp ----
-    const int l8 = tid & 7, rq = tid >> 3;
+    // persistent over (chunk, head) tiles; the completion barriers flip phase once per tile
+    for (int tile_id = blockIdx.x, iter = 0; tile_id < p.num_tiles; tile_id += gridDim.x, ++iter) {
+    const uint32_t par = iter & 1;
+    const int c = tile_id / p.H, h = tile_id - c * p.H;
+    const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
+    const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DK;
+    unsigned char* tile = p.tiles + ((size_t)c * p.H + h) * TP_BYTES;
+
+    // q, k rows of this tile into registers first, so their latency hides behind the gate pass.
+    // Thread (rq, l8): rows rq and rq+32, channels 32*grp + 4*l8 .. +3 for the four channel groups grp.
     uint2 qraw[2][4], kraw[2][4];
-    float rstd_q[2], rstd_k[2], bet[2];
     {
         const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q);
         const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(p.k);
 #pragma unroll
         for (int rs = 0; rs < 2; ++rs) {
             const int row = rq + 32 * rs;
-            float sq = 0.f, sk = 0.f;
 #pragma unroll
             for (int grp = 0; grp < 4; ++grp) {
                 uint2 qv = make_uint2(0, 0), kv = make_uint2(0, 0);
@@ -139,30 +156,120 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 }
                 qraw[rs][grp] = qv;
                 kraw[rs][grp] = kv;
-                float2 a = unpack_bf16(qv.x), b = unpack_bf16(qv.y);
-                sq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
-                a = unpack_bf16(kv.x); b = unpack_bf16(kv.y);
-                sk += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
             }
-            float b = 0.f;
-            if (row < ci.valid) {
-                size_t bi = (size_t)(ci.row0 + row) * p.H + h;
-                b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
-                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
-            }
-            bet[rs] = b;
-            if (l8 == 0) sBeta[row] = b;
-            if (p.use_l2norm) {
-#pragma unroll
-                for (int o = 1; o < 8; o <<= 1) {
-                    sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        }
+    }
+    {   // pull this tile's v rows and the next tile's inputs towards L2 (two 128-byte lines per row)
+        const int row = tid >> 2, part = tid & 3;
+        if (part < 2 && row < ci.valid)
+            prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.v) + base + (size_t)row * tok_stride + 64 * part);
+        const int nt = tile_id + gridDim.x;
+        if (nt < p.num_tiles) {
+            const int nc = nt / p.H, nh = nt - nc * p.H;
+            const ChunkInfo ni = chunk_info(nc, p.cu_seqlens, p.chunk_indices, p.T);
+            if (row < ni.valid) {
+                const size_t nb = (size_t)(ni.row0 + row) * tok_stride + (size_t)nh * DK + 64 * (part & 1);
+                if (part < 2) {
+                    prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.q) + nb);
+                    prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.k) + nb);
+                } else if (p.g_fp32) {
+                    prefetch_l2(reinterpret_cast<const float*>(p.g) + nb);
+                    prefetch_l2(reinterpret_cast<const float*>(p.g) + nb + 32);
+                } else {
+                    prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.g) + nb);
                 }
-                rstd_q[rs] = rsqrtf(sq + 1e-6f);
-                rstd_k[rs] = rsqrtf(sk + 1e-6f);
-            } else {
-                rstd_q[rs] = rstd_k[rs] = 1.f;
             }
+        }
+    }
+
+    // ---- 1a. gate activation with wide, coalesced loads: item (row, pc) covers channels 4pc..4pc+3 and
+    //          64+4pc..64+4pc+3; the activated log2 decay goes to sG (zero for padding rows) ----
+    {
+        const float alpha = p.gate_mode != GATE_NONE ? __expf(p.A_log[h]) : 0.f;
+        const int pc = tid & 15;
+        float bias[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            bias[e] = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] : 0.f;
+        float gv[4][8];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int row = (tid >> 4) + 16 * n;
+            const size_t off = base + (size_t)row * tok_stride + 4 * pc;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) gv[n][e] = 0.f;
+            if (row < ci.valid) {
+                if (p.g_fp32) {
+                    const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
+                    const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
+                    gv[n][0] = lo.x; gv[n][1] = lo.y; gv[n][2] = lo.z; gv[n][3] = lo.w;
+                    gv[n][4] = hi.x; gv[n][5] = hi.y; gv[n][6] = hi.z; gv[n][7] = hi.w;
+                } else {
+                    const uint2 lo = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off);
+                    const uint2 hi = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off + 64);
+                    float2 f;
+                    f = unpack_bf16(lo.x); gv[n][0] = f.x; gv[n][1] = f.y;
+                    f = unpack_bf16(lo.y); gv[n][2] = f.x; gv[n][3] = f.y;
+                    f = unpack_bf16(hi.x); gv[n][4] = f.x; gv[n][5] = f.y;
+                    f = unpack_bf16(hi.y); gv[n][6] = f.x; gv[n][7] = f.y;
+                }
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int row = (tid >> 4) + 16 * n;
+            float a[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                a[e] = (row < ci.valid) ? RCP_LN2 * gate_activation(gv[n][e], alpha, bias[e], p.gate_mode, p.lower_bound) : 0.f;
+            *reinterpret_cast<float4*>(sG + row * DK + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
+            *reinterpret_cast<float4*>(sG + row * DK + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
+        }
+    }
+    __syncthreads();
+    // ---- 1b. cumulative sum down the rows: thread (half, d) scans 32 rows in shared memory ----
+    {
+        const int d = tid & 127, half = tid >> 7;
+        float run = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const int row = half * 32 + r;
+            run += sG[row * DK + d];
+            sG[row * DK + d] = run;
+        }
+        if (half == 0) sHalf[d] = run;
+    }
+    // ---- 2. L2 norms from the rows held in registers, beta ----
+    float rstd_q[2], rstd_k[2], bet[2];
+#pragma unroll
+    for (int rs = 0; rs < 2; ++rs) {
+        const int row = rq + 32 * rs;
+        float sq = 0.f, sk = 0.f;
+#pragma unroll
+        for (int grp = 0; grp < 4; ++grp) {
+            float2 a = unpack_bf16(qraw[rs][grp].x), b = unpack_bf16(qraw[rs][grp].y);
+            sq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+            a = unpack_bf16(kraw[rs][grp].x); b = unpack_bf16(kraw[rs][grp].y);
+            sk += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+        }
+        float b = 0.f;
+        if (row < ci.valid) {
+            size_t bi = (size_t)(ci.row0 + row) * p.H + h;
+            b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
+                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
+        }
+        bet[rs] = b;
+        if (l8 == 0) sBeta[row] = b;
+        if (p.use_l2norm) {
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+            }
+            rstd_q[rs] = rsqrtf(sq + 1e-6f);
+            rstd_k[rs] = rsqrtf(sk + 1e-6f);
+        } else {
+            rstd_q[rs] = rstd_k[rs] = 1.f;
         }
     }
     __syncthreads();
@@ -194,15 +301,13 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     }
     if (tid < DK) reinterpret_cast<float*>(tile + TP_DECAY)[tid] = fast_exp2(sG[63 * DK + tid]);
     __syncthreads();
-    umma::fence_after_sync();
-    const uint32_t tmem = *tmem_slot;
 
     // ---- 3. operand generation + Gram MMAs, one 64-channel half at a time ----
     uint2 xpk[2][4];
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
         if (hf == 1) {   // operand buffers are reused: wait until the first half's MMAs have read them
-            if (!mbar_wait(&bars[0], 0)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+            if (!mbar_wait(&bars[0], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
             umma::fence_after_sync();
         }
 #pragma unroll
@@ -280,10 +385,11 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             umma::commit(&bars[hf]);
         }
     }
-    if (!mbar_wait(&bars[1], 0)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+    if (!mbar_wait(&bars[1], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
     umma::fence_after_sync();
 
-    // ---- 4. X into shared memory (all threads); warps 0-3: Gram epilogue; warps 4-7: Y = beta v ----
+    // ---- 4. X and Y = beta v into shared memory (all threads); Gram epilogue: warp w reads TMEM lane
+    //         quadrant w&3 and handles the 16-row block (w&1)*2 + (w>>2) living in its lower/upper half ----
 #pragma unroll
     for (int rs = 0; rs < 2; ++rs) {
         const int row = rq + 32 * rs;
@@ -297,42 +403,46 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     float* sL = reinterpret_cast<float*>(sm + SM_LF);
     float* sAi = reinterpret_cast<float*>(sm + SM_AINV);
     float* sT = reinterpret_cast<float*>(sm + SM_TM);
-    if (warp < 4) {
-        // TMEM lane = 32*warp + lane: lanes 0..63 are q rows (-> Aqk), 64..127 k rows (-> L)
-        const int row = (warp & 1) * 32 + lane;
-        const int I = row >> 4;
-        const bool is_q = warp < 2;
-        const float bi = sBeta[row];
-        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
+    {
+        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(p.v);
+        uint4 raw[4];
 #pragma unroll
-        for (int bsel = 0; bsel < 2; ++bsel) {
-            const int blk = (warp & 1) * 2 + bsel;          // the two 16-row blocks living in this warp
+        for (int n = 0; n < 4; ++n) {
+            const int idx = tid + 256 * n, j = idx >> 4, ch = idx & 15;
+            raw[n] = make_uint4(0, 0, 0, 0);
+            if (j < ci.valid) raw[n] = *reinterpret_cast<const uint4*>(vp + base + (size_t)j * tok_stride + 8 * ch);
+        }
+        {
+            const int qd = warp & 3, bsel = warp >> 2;
+            const int blk = (qd & 1) * 2 + bsel;            // 16-row block handled by this warp
+            const int row = (qd & 1) * 32 + lane;           // row of this lane inside the 64-row matrix
+            const bool mine = (row >> 4) == blk;
+            const bool is_q = qd < 2;                       // lanes 0..63 hold q rows (-> Aqk), 64..127 k rows (-> L)
+            const float bi = sBeta[row];
+            const uint32_t taddr = tmem + ((uint32_t)(qd * 32) << 16) + 8 * blk * (blk + 1);
 #pragma unroll
             for (int gcol = 0; gcol < 4; ++gcol) {
                 uint32_t r[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) r[e] = 0u;
                 if (gcol <= blk) {                           // warp-uniform
-                    umma::ld_32x32b_x16(taddr + 8 * blk * (blk + 1) + 16 * gcol, r);
+                    umma::ld_32x32b_x16(taddr + 16 * gcol, r);
                     umma::wait_ld();
                 }
-                if (I == blk) {
+                if (mine) {
                     float vals[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
                         const int j = 16 * gcol + e;
-                        float x = __uint_as_float(r[e]);
-                        if (is_q) x = (j <= row) ? p.scale * x : 0.f;
-                        else x = (j < row) ? bi * x : 0.f;
-                        vals[e] = x;
+                        const float x = __uint_as_float(r[e]);
+                        vals[e] = is_q ? ((j <= row) ? p.scale * x : 0.f) : ((j < row) ? bi * x : 0.f);
                     }
                     if (is_q) {
 #pragma unroll
-                        for (int hc = 0; hc < 2; ++hc) {
-                            uint4 pk = make_uint4(pack_f16(vals[8 * hc], vals[8 * hc + 1]), pack_f16(vals[8 * hc + 2], vals[8 * hc + 3]),
-                                                  pack_f16(vals[8 * hc + 4], vals[8 * hc + 5]), pack_f16(vals[8 * hc + 6], vals[8 * hc + 7]));
-                            *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol + 8 * hc)) = pk;
-                        }
+                        for (int hc = 0; hc < 2; ++hc)
+                            *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol + 8 * hc)) =
+                                make_uint4(pack_f16(vals[8 * hc], vals[8 * hc + 1]), pack_f16(vals[8 * hc + 2], vals[8 * hc + 3]),
+                                           pack_f16(vals[8 * hc + 4], vals[8 * hc + 5]), pack_f16(vals[8 * hc + 6], vals[8 * hc + 7]));
                     } else {
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4)
@@ -342,15 +452,11 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 }
             }
         }
-    } else {
-        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(p.v);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const int idx = (tid - 128) + 128 * n, j = idx >> 4, ch = idx & 15;
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (j < ci.valid) raw = *reinterpret_cast<const uint4*>(vp + base + (size_t)j * tok_stride + 8 * ch);
+        for (int n = 0; n < 4; ++n) {
+            const int idx = tid + 256 * n, j = idx >> 4, ch = idx & 15;
             const float b = sBeta[j];
-            const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+            const uint32_t w4[4] = {raw[n].x, raw[n].y, raw[n].z, raw[n].w};
             uint32_t o4[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -364,7 +470,9 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     umma::fence_before_sync();
     __syncthreads();
 
-    // ---- 5. Akk = (I + L)^-1: 16x16 diagonal blocks by substitution, then 16->32->64 block merges ----
+    // ---- 5. Akk = (I + L)^-1: 16x16 diagonal blocks by substitution (64 threads; the others clear the
+    //         blocks above the diagonal), then 16->32->64 block merges X = -D2inv (C D1inv) as split-TF32
+    //         mma.sync products (three MMAs per step recover fp32-level accuracy) ----
     if (tid < 64) {
         const int b = tid >> 4, cc = tid & 15;
         float x[16];
@@ -377,55 +485,49 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) sAi[(16 * b + i) * LROW + 16 * b + cc] = x[i];
+    } else if (tid < 192) {   // zero blocks (0,1) and (2,3): they are read as part of the 32x32 factors
+        const int t = tid - 64, pr = t >> 6, i = (t >> 2) & 15, j4 = (t & 3) * 4;
+        *reinterpret_cast<float4*>(sAi + (32 * pr + i) * LROW + 32 * pr + 16 + j4) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     __syncthreads();
-    {   // level 1: blocks (1,0) and (3,2):  X = -D2inv * (C * D1inv)
-        const int pr = tid >> 7, i = (tid >> 3) & 15, j0 = (tid & 7) * 2;
-        const int r0 = 32 * pr + 16, c0 = 32 * pr;
-        float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            const float cv = sL[(r0 + i) * LROW + c0 + k];
-            a0 = fmaf(cv, sAi[(c0 + k) * LROW + c0 + j0], a0);
-            a1 = fmaf(cv, sAi[(c0 + k) * LROW + c0 + j0 + 1], a1);
+    {
+        const int g8 = lane >> 2, t4 = lane & 3;
+        // level 1: pairs pr = 0,1 -> block (2pr+1, 2pr). T = C * D1inv, one 16x8 tile per warp 0..3
+        if (warp < 4) {
+            const int pr = warp >> 1, nt = warp & 1, r0 = 32 * pr + 16, c0 = 32 * pr;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_tile_3xtf32<2>(sL + r0 * LROW + c0, LROW, sAi + c0 * LROW + c0 + 8 * nt, LROW, acc, g8, t4);
+            float* td = sT + (16 * pr) * TROW + 8 * nt;
+            td[g8 * TROW + 2 * t4] = acc[0]; td[g8 * TROW + 2 * t4 + 1] = acc[1];
+            td[(g8 + 8) * TROW + 2 * t4] = acc[2]; td[(g8 + 8) * TROW + 2 * t4 + 1] = acc[3];
         }
-        sT[(16 * pr + i) * TROW + j0] = a0;
-        sT[(16 * pr + i) * TROW + j0 + 1] = a1;
         __syncthreads();
-        a0 = a1 = 0.f;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            const float dv = sAi[(r0 + i) * LROW + r0 + k];
-            a0 = fmaf(dv, sT[(16 * pr + k) * TROW + j0], a0);
-            a1 = fmaf(dv, sT[(16 * pr + k) * TROW + j0 + 1], a1);
+        if (warp < 4) {
+            const int pr = warp >> 1, nt = warp & 1, r0 = 32 * pr + 16, c0 = 32 * pr;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_tile_3xtf32<2>(sAi + r0 * LROW + r0, LROW, sT + (16 * pr) * TROW + 8 * nt, TROW, acc, g8, t4);
+            float* xd = sAi + r0 * LROW + c0 + 8 * nt;
+            xd[g8 * LROW + 2 * t4] = -acc[0]; xd[g8 * LROW + 2 * t4 + 1] = -acc[1];
+            xd[(g8 + 8) * LROW + 2 * t4] = -acc[2]; xd[(g8 + 8) * LROW + 2 * t4 + 1] = -acc[3];
         }
-        sAi[(r0 + i) * LROW + c0 + j0] = -a0;
-        sAi[(r0 + i) * LROW + c0 + j0 + 1] = -a1;
-    }
-    __syncthreads();
-    {   // level 2: block rows 32..63 x cols 0..31:  X = -A2inv * (C * A1inv)
-        const int i = tid >> 3, j0 = (tid & 7) * 4;
-        float a[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int k = j0; k < 32; ++k) {      // A1inv is lower triangular: rows k < j0 contribute nothing
-            const float cv = sL[(32 + i) * LROW + k];
-            const float4 av = *reinterpret_cast<const float4*>(sAi + k * LROW + j0);
-            a[0] = fmaf(cv, av.x, a[0]);
-            a[1] = fmaf(cv, (k >= j0 + 1) ? av.y : 0.f, a[1]);
-            a[2] = fmaf(cv, (k >= j0 + 2) ? av.z : 0.f, a[2]);
-            a[3] = fmaf(cv, (k >= j0 + 3) ? av.w : 0.f, a[3]);
-        }
-        *reinterpret_cast<float4*>(sT + i * TROW + j0) = make_float4(a[0], a[1], a[2], a[3]);
         __syncthreads();
-        a[0] = a[1] = a[2] = a[3] = 0.f;
-        for (int k = 0; k <= i; ++k) {       // A2inv is lower triangular
-            const float dv = sAi[(32 + i) * LROW + 32 + k];
-            const float4 tv = *reinterpret_cast<const float4*>(sT + k * TROW + j0);
-            a[0] = fmaf(dv, tv.x, a[0]);
-            a[1] = fmaf(dv, tv.y, a[1]);
-            a[2] = fmaf(dv, tv.z, a[2]);
-            a[3] = fmaf(dv, tv.w, a[3]);
+        // level 2: block rows 32..63 x cols 0..31. One 16x8 tile per warp (2 m-tiles x 4 n-tiles)
+        const int mt = warp >> 2, nt = warp & 3;
+        {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_tile_3xtf32<4>(sL + (32 + 16 * mt) * LROW, LROW, sAi + 8 * nt, LROW, acc, g8, t4);
+            float* td = sT + (16 * mt) * TROW + 8 * nt;
+            td[g8 * TROW + 2 * t4] = acc[0]; td[g8 * TROW + 2 * t4 + 1] = acc[1];
+            td[(g8 + 8) * TROW + 2 * t4] = acc[2]; td[(g8 + 8) * TROW + 2 * t4 + 1] = acc[3];
         }
-        *reinterpret_cast<float4*>(sAi + (32 + i) * LROW + j0) = make_float4(-a[0], -a[1], -a[2], -a[3]);
+        __syncthreads();
+        {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_tile_3xtf32<4>(sAi + (32 + 16 * mt) * LROW + 32, LROW, sT + 8 * nt, TROW, acc, g8, t4);
+            float* xd = sAi + (32 + 16 * mt) * LROW + 8 * nt;
+            xd[g8 * LROW + 2 * t4] = -acc[0]; xd[g8 * LROW + 2 * t4 + 1] = -acc[1];
+            xd[(g8 + 8) * LROW + 2 * t4] = -acc[2]; xd[(g8 + 8) * LROW + 2 * t4 + 1] = -acc[3];
+        }
     }
     __syncthreads();
     {   // Akk -> fp16 K-major operand (and fp32 to HBM when the backward pass wants it)
@@ -469,7 +571,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
         umma::commit(&bars[2]);
     }
-    if (!mbar_wait(&bars[2], 0)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+    if (!mbar_wait(&bars[2], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
     umma::fence_after_sync();
 
     // ---- 7. epilogue: lane = channel, columns = tokens; fp16 into the swizzled tile pack ----
@@ -492,7 +594,9 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
     }
     umma::fence_before_sync();
-    __syncthreads();
+    __syncthreads();      // TMEM columns and shared memory are free for the next tile
+    umma::fence_after_sync();
+    }  // tile loop
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
 }
 
@@ -506,6 +610,12 @@ extern "C" int kda_launch_fwd_intra(const kda::IntraParams* p, int num_chunks, c
     const int smem = SM_TOTAL + 1024;
     cudaError_t e = cudaFuncSetAttribute(kda_fwd_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    kda_fwd_intra_kernel<<<num_chunks * p->H, INTRA_THREADS, smem, stream>>>(*p);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    IntraParams q = *p;
+    q.num_tiles = num_chunks * p->H;
+    const int grid = q.num_tiles < 2 * sms ? q.num_tiles : 2 * sms;     // two resident CTAs per SM
+    kda_fwd_intra_kernel<<<grid, INTRA_THREADS, smem, stream>>>(q);
     return (int)cudaGetLastError();
 }

@@ -26,6 +26,7 @@ struct IntraParams {
     int* status;              // device status word
     int T;                    // tokens per sequence when cu_seqlens is null
     int H;
+    int num_tiles;            // num_chunks * H (filled in by the launcher)
     int g_fp32;
     int beta_fp32;
     int use_l2norm;
