@@ -5,6 +5,11 @@
 
 extern "C" int kda_launch_fwd_intra(const kda::IntraParams* p, int num_chunks, cudaStream_t stream);
 extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream);
+extern "C" int kda_launch_grad_scale(const void* d_o, size_t n_do, const float* dht, size_t n_dht, unsigned int* amax_bits,
+                                     float* gscale, cudaStream_t stream);
+extern "C" int kda_launch_bwd_scan(const kda::BwdScanParams* p, cudaStream_t stream);
+extern "C" int kda_launch_bwd_dense(const kda::BwdDenseParams* p, int num_chunks, cudaStream_t stream);
+extern "C" int kda_launch_bwd_gated(const kda::BwdGatedParams* p, int num_chunks, cudaStream_t stream);
 
 namespace {
 inline bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
@@ -21,14 +26,14 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
                                   const void* d_beta, int beta_is_fp32, const float* d_A_log, const float* d_dt_bias,
                                   const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H,
                                   float scale, int use_qk_l2norm, int gate_mode, float lower_bound, void* d_tiles,
-                                  float* d_akk, int* d_status, void* stream) {
+                                  float* d_akk, float* d_mkk, int* d_status, void* stream) {
     if (num_chunks == 0) return 0;
     if (!d_q || !d_k || !d_v || !d_g || !d_beta || !d_tiles || !d_status || num_chunks < 0 || H <= 0) return CULA_KDA_EINVAL;
     if (gate_mode < 0 || gate_mode > 2 || (gate_mode != 0 && !d_A_log)) return CULA_KDA_EINVAL;
     if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
     if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
     if (misaligned(d_q) || misaligned(d_k) || misaligned(d_v) || misaligned(d_g) || misaligned(d_tiles) ||
-        misaligned(d_akk))
+        misaligned(d_akk) || misaligned(d_mkk))
         return CULA_KDA_EALIGN;
     kda::IntraParams p{};
     p.q = d_q; p.k = d_k; p.v = d_v; p.g = d_g; p.beta = d_beta;
@@ -36,6 +41,7 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
     p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices;
     p.tiles = static_cast<unsigned char*>(d_tiles);
     p.akk_out = d_akk;
+    p.mkk_out = d_mkk;
     p.status = d_status;
     p.T = T; p.H = H; p.g_fp32 = g_is_fp32; p.beta_fp32 = beta_is_fp32;
     p.use_l2norm = use_qk_l2norm; p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
@@ -43,20 +49,91 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
 }
 
 extern "C" int cula_kda_fwd_scan(const void* d_tiles, const float* d_h0, void* d_o, float* d_ht, void* d_h_out,
-                                 void* d_vnew_out, const int* d_cu_seqlens, const int* d_chunk_offsets,
+                                 void* d_vnew_out, float* d_h32_out, const int* d_cu_seqlens, const int* d_chunk_offsets,
                                  const int* d_seq_order, int N, int T, int H, int* d_status, void* stream) {
     if (N == 0) return 0;
     if (!d_tiles || !d_o || !d_status || N < 0 || H <= 0) return CULA_KDA_EINVAL;
     if ((d_cu_seqlens == nullptr) != (d_chunk_offsets == nullptr)) return CULA_KDA_EINVAL;
     if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
-    if ((d_h_out == nullptr) != (d_vnew_out == nullptr)) return CULA_KDA_EINVAL;
+    if ((d_h_out || d_h32_out) && !d_vnew_out) return CULA_KDA_EINVAL;
     if (misaligned(d_tiles) || misaligned(d_o) || misaligned(d_h_out) || misaligned(d_vnew_out)) return CULA_KDA_EALIGN;
     kda::ScanParams p{};
     p.tiles = static_cast<const unsigned char*>(d_tiles);
-    p.h0 = d_h0; p.o = d_o; p.ht = d_ht; p.h_out = d_h_out; p.vnew_out = d_vnew_out;
+    p.h0 = d_h0; p.o = d_o; p.ht = d_ht; p.h_out = d_h_out; p.vnew_out = d_vnew_out; p.h32_out = d_h32_out;
     p.cu_seqlens = d_cu_seqlens; p.chunk_offsets = d_chunk_offsets; p.seq_order = d_seq_order;
     p.status = d_status; p.T = T; p.H = H; p.N = N;
     return kda_launch_fwd_scan(&p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_bwd_scratch_floats(void) { return kda::BWD_SCRATCH_FLOATS; }
+
+extern "C" int cula_kda_bwd_grad_scale(const void* d_do, long long n_do, const float* d_dht, long long n_dht,
+                                       unsigned int* d_amax, float* d_gscale, void* stream) {
+    if (!d_do || !d_amax || !d_gscale || n_do < 0 || n_dht < 0) return CULA_KDA_EINVAL;
+    return kda_launch_grad_scale(d_do, (size_t)n_do, d_dht, (size_t)n_dht, d_amax, d_gscale, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_bwd_scan(const void* d_tiles, const void* d_do, const float* d_dht, const float* d_gscale,
+                                 void* d_dvn_out, float* d_ds_out, float* d_dh0, const int* d_cu_seqlens,
+                                 const int* d_chunk_offsets, const int* d_seq_order, int N, int T, int H, int* d_status,
+                                 void* stream) {
+    if (N == 0) return 0;
+    if (!d_tiles || !d_do || !d_gscale || !d_dvn_out || !d_ds_out || !d_status || N < 0 || H <= 0) return CULA_KDA_EINVAL;
+    if ((d_cu_seqlens == nullptr) != (d_chunk_offsets == nullptr)) return CULA_KDA_EINVAL;
+    if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_tiles) || misaligned(d_do) || misaligned(d_dvn_out) || misaligned(d_ds_out)) return CULA_KDA_EALIGN;
+    kda::BwdScanParams p{};
+    p.tiles = static_cast<const unsigned char*>(d_tiles);
+    p.d_o = d_do; p.dht = d_dht; p.gscale = d_gscale; p.dvn_out = d_dvn_out; p.ds_out = d_ds_out; p.dh0 = d_dh0;
+    p.cu_seqlens = d_cu_seqlens; p.chunk_offsets = d_chunk_offsets; p.seq_order = d_seq_order;
+    p.status = d_status; p.T = T; p.H = H; p.N = N;
+    return kda_launch_bwd_scan(&p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_bwd_dense(const float* d_h32, const float* d_ds, const void* d_vnew, const void* d_dvn,
+                                  const void* d_do, const void* d_v, const void* d_beta, int beta_is_fp32,
+                                  const float* d_akk, const float* d_gscale, void* d_dv, float* d_scratch,
+                                  const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H,
+                                  void* stream) {
+    if (num_chunks == 0) return 0;
+    if (!d_h32 || !d_ds || !d_vnew || !d_dvn || !d_do || !d_v || !d_beta || !d_akk || !d_gscale || !d_dv || !d_scratch ||
+        num_chunks < 0 || H <= 0)
+        return CULA_KDA_EINVAL;
+    if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
+    if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_h32) || misaligned(d_ds) || misaligned(d_vnew) || misaligned(d_dvn) || misaligned(d_do) ||
+        misaligned(d_v) || misaligned(d_akk) || misaligned(d_dv) || misaligned(d_scratch))
+        return CULA_KDA_EALIGN;
+    kda::BwdDenseParams p{};
+    p.h32 = d_h32; p.ds = d_ds; p.vnew = d_vnew; p.dvn = d_dvn; p.d_o = d_do; p.v = d_v; p.beta = d_beta;
+    p.akk = d_akk; p.gscale = d_gscale; p.dv = d_dv; p.scratch = d_scratch;
+    p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices; p.T = T; p.H = H; p.beta_fp32 = beta_is_fp32;
+    return kda_launch_bwd_dense(&p, num_chunks, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_bwd_gated(const void* d_q, const void* d_k, const void* d_g, int g_is_fp32, const void* d_beta,
+                                  int beta_is_fp32, const float* d_A_log, const float* d_dt_bias, const float* d_akk,
+                                  const float* d_mkk, const float* d_scratch, const float* d_gscale, void* d_dq, void* d_dk,
+                                  void* d_dg, void* d_dbeta, float* d_dA_log, float* d_ddt_bias, const int* d_cu_seqlens,
+                                  const int* d_chunk_indices, int num_chunks, int T, int H, float scale, int use_qk_l2norm,
+                                  int gate_mode, float lower_bound, void* stream) {
+    if (num_chunks == 0) return 0;
+    if (!d_q || !d_k || !d_g || !d_beta || !d_akk || !d_mkk || !d_scratch || !d_gscale || !d_dq || !d_dk || !d_dg ||
+        !d_dbeta || num_chunks < 0 || H <= 0)
+        return CULA_KDA_EINVAL;
+    if (gate_mode < 0 || gate_mode > 2 || (gate_mode != 0 && !d_A_log)) return CULA_KDA_EINVAL;
+    if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
+    if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_q) || misaligned(d_k) || misaligned(d_g) || misaligned(d_akk) || misaligned(d_mkk) ||
+        misaligned(d_scratch) || misaligned(d_dq) || misaligned(d_dk) || misaligned(d_dg))
+        return CULA_KDA_EALIGN;
+    kda::BwdGatedParams p{};
+    p.q = d_q; p.k = d_k; p.g = d_g; p.beta = d_beta; p.A_log = d_A_log; p.dt_bias = d_dt_bias; p.akk = d_akk;
+    p.mkk = d_mkk; p.scratch = d_scratch; p.gscale = d_gscale; p.dq = d_dq; p.dk = d_dk; p.dg = d_dg; p.dbeta = d_dbeta;
+    p.dA_log = d_dA_log; p.ddt_bias = d_ddt_bias; p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices;
+    p.T = T; p.H = H; p.g_fp32 = g_is_fp32; p.beta_fp32 = beta_is_fp32; p.use_l2norm = use_qk_l2norm;
+    p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
+    return kda_launch_bwd_gated(&p, num_chunks, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" const char* cula_kda_strerror(int code) {

@@ -448,6 +448,19 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                         for (int q4 = 0; q4 < 4; ++q4)
                             *reinterpret_cast<float4*>(sL + row * LROW + 16 * gcol + 4 * q4) =
                                 make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
+                        if (p.mkk_out) {     // the same Gram entries without beta, for the backward pass
+                            float* mo = p.mkk_out + ((size_t)c * p.H + h) * BT * BT + row * BT + 16 * gcol;
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                float mv[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int j = 16 * gcol + 4 * q4 + e;
+                                    mv[e] = (j < row) ? __uint_as_float(r[4 * q4 + e]) : 0.f;
+                                }
+                                *reinterpret_cast<float4*>(mo + 4 * q4) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+                            }
+                        }
                     }
                 }
             }

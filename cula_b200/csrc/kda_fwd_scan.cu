@@ -132,23 +132,37 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
             sa[ks][3] = pack_f16(S[2 * ks + 1][2] * s_up, S[2 * ks + 1][3] * s_up);
         }
         if (STORE_HV) {
-            // incoming state of this chunk, bf16 [128 k][128 v]; this warp owns a 32-byte column slice
+            if (p.h_out) {
+                // incoming state of this chunk, bf16 [128 k][128 v]; this warp owns a 32-byte column slice
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                int krow = 8 * (2 * ks + (m >> 1)) + r;
-                stsm_x4_t(stg_u32 + krow * 32 + (m & 1) * 16,
-                          pack_bf16(S[2 * ks][0], S[2 * ks][1]), pack_bf16(S[2 * ks][2], S[2 * ks][3]),
-                          pack_bf16(S[2 * ks + 1][0], S[2 * ks + 1][1]), pack_bf16(S[2 * ks + 1][2], S[2 * ks + 1][3]));
-            }
-            __syncwarp();
-            unsigned char* hg = reinterpret_cast<unsigned char*>(p.h_out) + tile_idx * (size_t)(DK * DV * 2);
+                for (int ks = 0; ks < 8; ++ks) {
+                    int krow = 8 * (2 * ks + (m >> 1)) + r;
+                    stsm_x4_t(stg_u32 + krow * 32 + (m & 1) * 16,
+                              pack_bf16(S[2 * ks][0], S[2 * ks][1]), pack_bf16(S[2 * ks][2], S[2 * ks][3]),
+                              pack_bf16(S[2 * ks + 1][0], S[2 * ks + 1][1]), pack_bf16(S[2 * ks + 1][2], S[2 * ks + 1][3]));
+                }
+                __syncwarp();
+                unsigned char* hg = reinterpret_cast<unsigned char*>(p.h_out) + tile_idx * (size_t)(DK * DV * 2);
 #pragma unroll
-            for (int it = 0; it < 8; ++it) {
-                int row = it * 16 + (lane >> 1), hf = lane & 1;
-                uint4 val = *reinterpret_cast<const uint4*>(stg + row * 32 + hf * 16);
-                *reinterpret_cast<uint4*>(hg + (size_t)row * 256 + vb * 2 + hf * 16) = val;
+                for (int it = 0; it < 8; ++it) {
+                    int row = it * 16 + (lane >> 1), hf = lane & 1;
+                    uint4 val = *reinterpret_cast<const uint4*>(stg + row * 32 + hf * 16);
+                    *reinterpret_cast<uint4*>(hg + (size_t)row * 256 + vb * 2 + hf * 16) = val;
+                }
+                __syncwarp();
             }
-            __syncwarp();
+            if (p.h32_out) {
+                // the same state in fp32 [128 k][128 v] for the backward pass
+                float* hg = p.h32_out + tile_idx * (size_t)(DK * DV);
+#pragma unroll
+                for (int jt = 0; jt < 16; ++jt) {
+                    int k0 = 8 * jt + 2 * t;
+                    hg[(size_t)k0 * DV + vb + g] = S[jt][0];
+                    hg[(size_t)(k0 + 1) * DV + vb + g] = S[jt][1];
+                    hg[(size_t)k0 * DV + vb + g + 8] = S[jt][2];
+                    hg[(size_t)(k0 + 1) * DV + vb + g + 8] = S[jt][3];
+                }
+            }
         }
 
         // ---- acc = S^T w^T : [16 v] x [64 tokens], contraction over 128 key channels ----
@@ -301,7 +315,7 @@ extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream
     if (p->N <= 0) return 0;
     dim3 grid(2, p->H, p->N);
     cudaError_t e;
-    if (p->h_out) {
+    if (p->vnew_out) {
         e = cudaFuncSetAttribute(kda_fwd_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
         if (e != cudaSuccess) return (int)e;
         kda_fwd_scan_kernel<true><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);

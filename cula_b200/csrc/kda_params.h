@@ -23,6 +23,7 @@ struct IntraParams {
     const int* chunk_indices; // [NT][2] or null (fixed length)
     unsigned char* tiles;     // [NT*H] tile packs
     float* akk_out;           // [NT*H][64][64] fp32 or null
+    float* mkk_out;           // [NT*H][64][64] fp32 strict-lower gated k k^T Gram matrix, or null
     int* status;              // device status word
     int T;                    // tokens per sequence when cu_seqlens is null
     int H;
@@ -41,6 +42,7 @@ struct ScanParams {
     void* o;                      // [B*T, H, 128] bf16
     float* ht;                    // [N, H, 128, 128] fp32 or null
     void* h_out;                  // per-chunk incoming state, bf16, or null
+    float* h32_out;               // per-chunk incoming state, fp32, or null
     void* vnew_out;               // per-chunk v_new, fp16, or null
     const int* cu_seqlens;        // [N+1] or null
     const int* chunk_offsets;     // [N+1] first global chunk of each sequence, or null
@@ -49,6 +51,81 @@ struct ScanParams {
     int T;
     int H;
     int N;                        // number of sequences
+};
+
+struct BwdScanParams {
+    const unsigned char* tiles;   // [NT*H] forward tile packs
+    const void* d_o;              // [B*T, H, 128] bf16 upstream gradient
+    const float* dht;             // [N, H, 128, 128] fp32 or null
+    const float* gscale;          // device: {s, 1/s}; all gradient-like operands are carried in units of s
+    void* dvn_out;                // [NT*H][64][128] fp16, gradient w.r.t. v_new (units of s)
+    float* ds_out;                // [NT*H][128][128] fp32, gradient w.r.t. the state leaving each chunk (units of s)
+    float* dh0;                   // [N, H, 128, 128] fp32 or null (true units)
+    const int* cu_seqlens;
+    const int* chunk_offsets;
+    const int* seq_order;
+    int* status;
+    int T;
+    int H;
+    int N;
+};
+
+// fp32 scratch record written per (chunk, head) by the dense backward stage, read by the gated stage
+constexpr int SCR_DQG = 0;            // [64][128] gradient w.r.t. qg = scale q 2^g
+constexpr int SCR_DW = 8192;          // [64][128] gradient w.r.t. w
+constexpr int SCR_DKG = 16384;        // [64][128] gradient w.r.t. kg
+constexpr int SCR_DPS = 24576;        // [64][64]  gradient w.r.t. Aqk (lower triangle incl. diagonal)
+constexpr int SCR_DAU = 28672;        // [64][64]  stril(dVn (beta V)^T): the u-part of the gradient w.r.t. Akk
+constexpr int SCR_DBU = 32768;        // [64]      rowsum(Zu * V)
+constexpr int SCR_DD = 32832;         // [128]     sum_v S dS'
+constexpr int BWD_SCRATCH_FLOATS = 32960;
+
+struct BwdDenseParams {
+    const float* h32;             // [NT*H][128][128] state entering each chunk
+    const float* ds;              // [NT*H][128][128] gradient w.r.t. the state leaving each chunk (units of s)
+    const void* vnew;             // [NT*H][64][128] fp16
+    const void* dvn;              // [NT*H][64][128] fp16 (units of s)
+    const void* d_o;              // [B*T, H, 128] bf16
+    const void* v;                // [B*T, H, 128] bf16
+    const void* beta;
+    const float* akk;             // [NT*H][64][64] fp32
+    const float* gscale;
+    void* dv;                     // [B*T, H, 128] bf16 (output)
+    float* scratch;               // [NT*H][BWD_SCRATCH_FLOATS]
+    const int* cu_seqlens;
+    const int* chunk_indices;
+    int T;
+    int H;
+    int beta_fp32;
+};
+
+struct BwdGatedParams {
+    const void* q;
+    const void* k;
+    const void* g;
+    const void* beta;
+    const float* A_log;
+    const float* dt_bias;
+    const float* akk;             // [NT*H][64][64] fp32
+    const float* mkk;             // [NT*H][64][64] fp32: strict-lower sum_d k_i k_j 2^(g_i-g_j)
+    const float* scratch;         // [NT*H][BWD_SCRATCH_FLOATS]
+    const float* gscale;
+    void* dq;                     // [B*T, H, 128] bf16
+    void* dk;                     // [B*T, H, 128] bf16
+    void* dg;                     // [B*T, H, 128] dtype of g
+    void* dbeta;                  // [B*T, H] dtype of beta
+    float* dA_log;                // [H] fp32, accumulated with atomics (zero it first) or null
+    float* ddt_bias;              // [H*128] fp32, accumulated with atomics, or null
+    const int* cu_seqlens;
+    const int* chunk_indices;
+    int T;
+    int H;
+    int g_fp32;
+    int beta_fp32;
+    int use_l2norm;
+    int gate_mode;
+    float lower_bound;
+    float scale;
 };
 
 }  // namespace kda

@@ -48,7 +48,7 @@ def _gate_mode(use_gate_in_kernel, safe_gate, lower_bound):
 
 def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
                   use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias,
-                  store_states=False, store_akk=False):
+                  store_states=False, store_akk=False, store_for_backward=False):
     """Forward orchestration (the role of cula/kda/chunk_fwd.py:39-152): the chunk-parallel stage
     writes one tile pack per (chunk, head); the scan consumes them, carries the fp32 state and
     writes ``o``. Returns a dict with o, final_state and the intermediates kept for backward."""
@@ -69,23 +69,86 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
         cu_p = ci_p = co_p = so_p = None
         o = torch.empty_like(v)
     tiles = torch.empty(num_chunks * H * lib.cula_kda_tile_pack_bytes(), dtype=torch.uint8, device=dev)
-    akk = torch.empty(num_chunks * H, CHUNK, CHUNK, dtype=torch.float32, device=dev) if store_akk else None
+    akk = (torch.empty(num_chunks * H, CHUNK, CHUNK, dtype=torch.float32, device=dev)
+           if (store_akk or store_for_backward) else None)
+    mkk = torch.empty(num_chunks * H, CHUNK, CHUNK, dtype=torch.float32, device=dev) if store_for_backward else None
     gate_mode = _gate_mode(use_gate_in_kernel, safe_gate, lower_bound)
     _native.check(lib.cula_kda_fwd_intra(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32),
         beta.data_ptr(), int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias),
         cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
-        float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), _status_word(dev).data_ptr(), stream),
+        float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), _ptr(mkk), _status_word(dev).data_ptr(), stream),
         "cula_kda_fwd_intra")
     final_state = torch.empty(n_seqs, H, K, v.shape[-1], dtype=torch.float32, device=dev) if output_final_state else None
-    h = vnew = None
+    h = vnew = h32 = None
     if store_states:
         h = torch.empty(num_chunks * H, K, v.shape[-1], dtype=torch.bfloat16, device=dev)
+    if store_for_backward:
+        h32 = torch.empty(num_chunks * H, K, v.shape[-1], dtype=torch.float32, device=dev)
+    if store_states or store_for_backward:
         vnew = torch.empty(num_chunks * H, CHUNK, v.shape[-1], dtype=torch.float16, device=dev)
     _native.check(lib.cula_kda_fwd_scan(
-        tiles.data_ptr(), _ptr(initial_state), o.data_ptr(), _ptr(final_state), _ptr(h), _ptr(vnew),
+        tiles.data_ptr(), _ptr(initial_state), o.data_ptr(), _ptr(final_state), _ptr(h), _ptr(vnew), _ptr(h32),
         cu_p, co_p, so_p, n_seqs, T, H, _status_word(dev).data_ptr(), stream), "cula_kda_fwd_scan")
-    return dict(o=o, final_state=final_state, tiles=tiles, akk=akk, h=h, vnew=vnew, num_chunks=num_chunks)
+    return dict(o=o, final_state=final_state, tiles=tiles, akk=akk, mkk=mkk, h=h, h32=h32, vnew=vnew,
+                num_chunks=num_chunks)
+
+
+def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, cu_seqlens_cpu,
+                  use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias, saved=None):
+    """Backward orchestration (the role of cula/kda/chunk_bwd.py:432-604). ``saved`` holds the forward
+    intermediates (tiles, akk, mkk, h32, vnew) when they were kept; otherwise they are recomputed here, as the
+    reference does by default (cula/kda/chunk_bwd.py:459-500)."""
+    lib = _native.lib()
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    dev = q.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    if saved is None:
+        saved = chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, False, cu_seqlens, cu_seqlens_cpu,
+                              use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias,
+                              store_for_backward=True)
+    if cu_seqlens is not None:
+        tab = get_varlen_tables(cu_seqlens, cu_seqlens_cpu)
+        n_seqs, num_chunks = tab.n_seqs, tab.num_chunks
+        cu_p, ci_p, co_p, so_p = (tab.cu_seqlens.data_ptr(), tab.chunk_indices.data_ptr(),
+                                  tab.chunk_offsets.data_ptr(), tab.seq_order.data_ptr())
+        zeros = torch.zeros
+    else:
+        n_seqs, num_chunks = B, B * ((T + CHUNK - 1) // CHUNK)
+        cu_p = ci_p = co_p = so_p = None
+        zeros = torch.empty
+    status = _status_word(dev).data_ptr()
+    gate_mode = _gate_mode(use_gate_in_kernel, safe_gate, lower_bound)
+    do = do.contiguous()
+    if dht is not None:
+        dht = dht.float().contiguous()
+    work = torch.zeros(4, dtype=torch.float32, device=dev)          # [0:2] = {s, 1/s}, [2] = running max (as bits)
+    _native.check(lib.cula_kda_bwd_grad_scale(do.data_ptr(), do.numel(), _ptr(dht), 0 if dht is None else dht.numel(),
+                                              work[2:].data_ptr(), work.data_ptr(), stream), "cula_kda_bwd_grad_scale")
+    dvn = torch.empty(num_chunks * H, CHUNK, V, dtype=torch.float16, device=dev)
+    ds = torch.empty(num_chunks * H, K, V, dtype=torch.float32, device=dev)
+    dh0 = torch.empty(n_seqs, H, K, V, dtype=torch.float32, device=dev) if initial_state is not None else None
+    _native.check(lib.cula_kda_bwd_scan(saved["tiles"].data_ptr(), do.data_ptr(), _ptr(dht), work.data_ptr(),
+                                        dvn.data_ptr(), ds.data_ptr(), _ptr(dh0), cu_p, co_p, so_p, n_seqs, T, H, status,
+                                        stream), "cula_kda_bwd_scan")
+    dv = zeros(v.shape, dtype=v.dtype, device=dev)
+    scratch = torch.empty(num_chunks * H, lib.cula_kda_bwd_scratch_floats(), dtype=torch.float32, device=dev)
+    _native.check(lib.cula_kda_bwd_dense(saved["h32"].data_ptr(), ds.data_ptr(), saved["vnew"].data_ptr(), dvn.data_ptr(),
+                                         do.data_ptr(), v.data_ptr(), beta.data_ptr(), int(beta.dtype == torch.float32),
+                                         saved["akk"].data_ptr(), work.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
+                                         cu_p, ci_p, num_chunks, T, H, stream), "cula_kda_bwd_dense")
+    dq, dk = zeros(q.shape, dtype=q.dtype, device=dev), zeros(k.shape, dtype=k.dtype, device=dev)
+    dg, dbeta = zeros(g.shape, dtype=g.dtype, device=dev), zeros(beta.shape, dtype=beta.dtype, device=dev)
+    dA = torch.zeros(H, dtype=torch.float32, device=dev) if use_gate_in_kernel else None
+    dbias = torch.zeros(H * K, dtype=torch.float32, device=dev) if (use_gate_in_kernel and dt_bias is not None) else None
+    _native.check(lib.cula_kda_bwd_gated(
+        q.data_ptr(), k.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32), beta.data_ptr(),
+        int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias), saved["akk"].data_ptr(), saved["mkk"].data_ptr(),
+        scratch.data_ptr(), work.data_ptr(), dq.data_ptr(), dk.data_ptr(), dg.data_ptr(), dbeta.data_ptr(), _ptr(dA),
+        _ptr(dbias), cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
+        float(lower_bound if lower_bound is not None else 0.0), stream), "cula_kda_bwd_gated")
+    return dq, dk, dv, dg, dbeta, dA, dbias, dh0
 
 
 class ChunkKDAFunction(torch.autograd.Function):
@@ -105,7 +168,8 @@ class ChunkKDAFunction(torch.autograd.Function):
         with torch.cuda.device(q.device):
             out = chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                                 cu_seqlens_cpu, use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound,
-                                A_log, dt_bias, store_states=return_intermediate_states)
+                                A_log, dt_bias, store_states=return_intermediate_states,
+                                store_for_backward=bool(disable_recompute) and torch.is_grad_enabled())
         if return_intermediate_states:
             assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
             assert disable_recompute is False, "return_intermediate_states must be used with disable_recompute=False"
@@ -117,6 +181,10 @@ class ChunkKDAFunction(torch.autograd.Function):
                 h = h.unsqueeze(0)
             return out["o"], out["final_state"], h
         ctx.save_for_backward(q, k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens)
+        # disable_recompute keeps the forward intermediates alive for backward (cula/kda/chunk_fwd.py:144-151 drops
+        # them otherwise); they are internal buffers nobody else can modify, so they ride on ctx directly
+        ctx.kept = ({n: out[n] for n in ("tiles", "akk", "mkk", "h32", "vnew")}
+                    if out["h32"] is not None else None)
         ctx.cu_seqlens_cpu = cu_seqlens_cpu
         ctx.scale = scale
         ctx.flags = (use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound)
@@ -124,7 +192,18 @@ class ChunkKDAFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do, dht):
-        raise NotImplementedError("chunk_kda backward kernels are not built yet")
+        q, k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens = ctx.saved_tensors
+        l2, gate_in, safe_gate, lower_bound = ctx.flags
+        with torch.cuda.device(q.device):
+            dq, dk, dv, dg, dbeta, dA, dbias, dh0 = chunk_kda_bwd(
+                q, k, v, g, beta, ctx.scale, initial_state, do, dht, cu_seqlens, ctx.cu_seqlens_cpu, l2, gate_in,
+                safe_gate, lower_bound, A_log, dt_bias, saved=ctx.kept)
+        if dA is not None and A_log is not None:
+            dA = dA.to(A_log.dtype).view_as(A_log)
+        if dbias is not None and dt_bias is not None:
+            dbias = dbias.to(dt_bias.dtype).view_as(dt_bias)
+        # gradients for: q, k, v, g, beta, A_log, dt_bias, scale, initial_state, then 9 non-tensor arguments
+        return (dq, dk, dv, dg, dbeta, dA, dbias, None, dh0) + (None,) * 9
 
 
 @torch.compiler.disable

@@ -47,7 +47,8 @@ int cula_kda_fwd_scan_smem_bytes(void);
  *                                                                 csrc/api/kda_sm100.cu:70-120
  * d_cu_seqlens [N+1] / d_chunk_indices [num_chunks][2] (sequence, chunk-in-sequence) are the tables of
  * prepare_chunk_indices; pass both NULL for a fixed-length batch of sequences of T tokens.
- * d_tiles: num_chunks*H tile packs (output). d_akk: optional [num_chunks*H][64][64] fp32 (I+L)^-1.
+ * d_tiles: num_chunks*H tile packs (output). d_akk: optional [num_chunks*H][64][64] fp32 (I+L)^-1;
+ * d_mkk: optional [num_chunks*H][64][64] fp32 strictly-lower gated k k^T Gram matrix (both kept for backward).
  * d_status: one int the kernel sets non-zero if a bounded wait on a tensor-core completion barrier gave up.
  */
 int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* d_v,
@@ -57,7 +58,7 @@ int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* d_v,
                        const int* d_cu_seqlens, const int* d_chunk_indices,
                        int num_chunks, int T, int H,
                        float scale, int use_qk_l2norm, int gate_mode, float lower_bound,
-                       void* d_tiles, float* d_akk, int* d_status, void* stream);
+                       void* d_tiles, float* d_akk, float* d_mkk, int* d_status, void* stream);
 
 /*
  * Sequential state scan fused with the output stage, one CTA per (sequence, head, value half).
@@ -66,15 +67,60 @@ int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* d_v,
  *   chunk_gla_fwd_o(q, v_new, g, A=Aqk, h, o, scale, ...) (cula/ops/fwd_o.py:1755-1852, chunk_fwd.py:131-143).
  * d_h0 / d_ht: [N, H, 128, 128] fp32 or NULL. d_o: [B*T, H, 128] bf16; only rows of real tokens are written.
  * d_h_out (bf16 [num_chunks*H][128][128], state entering each chunk) and d_vnew_out (fp16
- * [num_chunks*H][64][128]) are both given or both NULL.
+ * [num_chunks*H][64][128]) and d_h32_out (the same states in fp32, for the backward pass) are optional;
+ * d_vnew_out must be given whenever a state output is.
  * d_chunk_offsets [N+1]: first global chunk of each sequence (prepare_chunk_offsets);
  * d_seq_order [N]: optional launch order of the sequences (longest first balances a ragged batch).
  * d_status: one int the kernel sets non-zero if a bounded pipeline wait gave up (never in a healthy run).
  */
 int cula_kda_fwd_scan(const void* d_tiles, const float* d_h0, void* d_o, float* d_ht,
-                      void* d_h_out, void* d_vnew_out,
+                      void* d_h_out, void* d_vnew_out, float* d_h32_out,
                       const int* d_cu_seqlens, const int* d_chunk_offsets, const int* d_seq_order,
                       int N, int T, int H, int* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Backward pass. The reference's backward is all Triton / flash-linear-attention kernels plus a recompute of
+ * its forward intermediates (cula/kda/chunk_bwd.py:432-604); here it is four launches after re-running the two
+ * forward launches with d_akk, d_mkk, d_h32_out and d_vnew_out set.
+ * All gradient-like intermediates are carried in units of a power-of-two scale s (d_gscale = {s, 1/s}).
+ * ------------------------------------------------------------------------------------------------------------ */
+
+/* floats per (chunk, head) of the scratch record passed from cula_kda_bwd_dense to cula_kda_bwd_gated */
+int cula_kda_bwd_scratch_floats(void);
+
+/* s = 2^k with max(|dO|, |dht|) * s in [4, 8). d_amax: one uint32 of workspace. No counterpart in the reference
+ * (its bf16 intermediates need no range management; ours are fp16). */
+int cula_kda_bwd_grad_scale(const void* d_do, long long n_do, const float* d_dht, long long n_dht,
+                            unsigned int* d_amax, float* d_gscale, void* stream);
+
+/* Reverse state scan: d_dvn_out (fp16 [num_chunks*H][64][128], gradient w.r.t. v_new), d_ds_out (fp32
+ * [num_chunks*H][128][128], gradient w.r.t. the state leaving each chunk), d_dh0 ([N,H,128,128] fp32 or NULL).
+ * Replaces chunk_gated_delta_rule_bwd_dhu (fla/ops/common/chunk_delta_h.py:659-718, cula/kda/chunk_bwd.py:541-555)
+ * and the dv half of chunk_kda_bwd_dAv (cula/kda/chunk_bwd.py:510-520). */
+int cula_kda_bwd_scan(const void* d_tiles, const void* d_do, const float* d_dht, const float* d_gscale,
+                      void* d_dvn_out, float* d_ds_out, float* d_dh0,
+                      const int* d_cu_seqlens, const int* d_chunk_offsets, const int* d_seq_order,
+                      int N, int T, int H, int* d_status, void* stream);
+
+/* Chunk-parallel dense products with the carried states; writes d_dv (bf16, final) and the scratch record.
+ * Replaces the state-dependent half of chunk_kda_bwd_wy_dqkg_fused (cula/kda/chunk_bwd.py:557-574) and the dAqk
+ * half of chunk_kda_bwd_dAv. */
+int cula_kda_bwd_dense(const float* d_h32, const float* d_ds, const void* d_vnew, const void* d_dvn,
+                       const void* d_do, const void* d_v, const void* d_beta, int beta_is_fp32,
+                       const float* d_akk, const float* d_gscale, void* d_dv, float* d_scratch,
+                       const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H, void* stream);
+
+/* Chunk-parallel gated part: Akk / Gram-matrix VJPs, reverse cumulative sum, gate and L2-norm VJPs.
+ * Writes d_dq, d_dk (bf16), d_dg (dtype of g), d_dbeta (dtype of beta); accumulates d_dA_log [H] and
+ * d_ddt_bias [H*128] with atomics (caller zeroes them). Replaces the rest of chunk_kda_bwd_wy_dqkg_fused,
+ * chunk_kda_bwd_intra (cula/kda/chunk_intra.py:796-860), chunk_local_cumsum(reverse) + kda_gate_bwd
+ * (cula/kda/chunk_bwd.py:594-602) and l2norm_bwd (cula/kda/chunk.py:190-192). */
+int cula_kda_bwd_gated(const void* d_q, const void* d_k, const void* d_g, int g_is_fp32,
+                       const void* d_beta, int beta_is_fp32, const float* d_A_log, const float* d_dt_bias,
+                       const float* d_akk, const float* d_mkk, const float* d_scratch, const float* d_gscale,
+                       void* d_dq, void* d_dk, void* d_dg, void* d_dbeta, float* d_dA_log, float* d_ddt_bias,
+                       const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H,
+                       float scale, int use_qk_l2norm, int gate_mode, float lower_bound, void* stream);
 
 /* Human-readable text for a return value of the functions above. */
 const char* cula_kda_strerror(int code);
