@@ -26,8 +26,8 @@ constexpr int BG_QK = BG_ACC3 + 8192;          // q raw, k raw as bf16 [64][128]
 constexpr int BG_A = BG_QK + 8192;             // A [64][68]
 constexpr int BG_C1 = BG_A + 64 * AR;          // T1, later cP = scale * dPs          [64][68]
 constexpr int BG_C2 = BG_C1 + 64 * AR;         // dA, later cR = beta_i * dL          [64][68]
-constexpr int BG_MISC = BG_C2 + 64 * AR;       // rstd_q[64] rstd_k[64] beta[64] dbeta[64] half[128] red[16]
-constexpr int BG_FLOATS = BG_MISC + 64 * 4 + 128 + 16;
+constexpr int BG_MISC = BG_C2 + 64 * AR;       // rstd_q[64] rstd_k[64] beta[64] dbeta[64] half[128] red[16] partial[256]
+constexpr int BG_FLOATS = BG_MISC + 64 * 4 + 128 + 16 + 256;
 constexpr int BG_SMEM = BG_FLOATS * 4;
 
 __device__ __forceinline__ float bg_gate_raw(const void* g, int g_fp32, size_t idx) {
@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     float* sDbeta = sBeta + 64;
     float* sHalf = sDbeta + 64;
     float* sRed = sHalf + 128;
+    float* c1z = sHalf + 144;                      // [4][64] per-warp partial row sums
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
@@ -250,12 +251,13 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
             float zb = zw * kplus;
 #pragma unroll
             for (int o = 16; o; o >>= 1) zb += __shfl_xor_sync(0xffffffffu, zb, o);
-            if (lane == 0) atomicAdd(&sDbeta[i], zb);
+            if (lane == 0) c1z[warp * 64 + i] = zb;          // per-warp partials, summed in a fixed order below
             acc3[i * DK + d] = dG;
         }
         acc3[63 * DK + d] += dgl;
     }
     __syncthreads();
+    if (tid < 64) sDbeta[tid] += (c1z[tid] + c1z[64 + tid]) + (c1z[128 + tid] + c1z[192 + tid]);
 
     // ---- 6. pairwise gated VJPs. Thread (d, par): channel d, rows of parity par inside every 16x16 block ----
     {
@@ -299,12 +301,19 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
                 acc3[i * DK + d] += qi * aq + ki * ar;
             }
             __syncthreads();       // row updates of this block are visible before the column updates below
+            // the two row-parity threads of a channel add their column sums one after the other: fixed order,
+            // so the result does not depend on scheduling
+#pragma unroll 1
+            for (int turn = 0; turn < 2; ++turn) {
+                if (par == turn) {
 #pragma unroll
-            for (int y = 0; y < 16; ++y) {
-                atomicAdd(&acc2[(16 * J + y) * DK + d], aj[y]);
-                atomicAdd(&acc3[(16 * J + y) * DK + d], -kj[y] * aj[y]);
+                    for (int y = 0; y < 16; ++y) {
+                        acc2[(16 * J + y) * DK + d] += aj[y];
+                        acc3[(16 * J + y) * DK + d] -= kj[y] * aj[y];
+                    }
+                }
+                __syncthreads();
             }
-            __syncthreads();
         }
     }
 

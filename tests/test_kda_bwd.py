@@ -1,0 +1,172 @@
+"""GPU parity of the chunk_kda backward path (autograd through the C ABI) against autograd of the CPU oracle
+and against the golden gradients. Tolerances (relative RMS): 5e-3 for dq, dk, dv, dg, dbeta, dh0 on the headline
+distributions, the reference's own 8e-3 / 2e-2 bounds (tests/test_kda.py:147-155) elsewhere; max-abs <= 2e-2
+relative to the largest reference entry."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from conftest import GOLDEN_CASES, load_golden
+from oracle.naive_kda import chunk_kda_oracle, err_ratio, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+GRADS = ("q", "k", "v", "g", "beta", "A_log", "dt_bias", "initial_state")
+
+
+def run_both(inp, do, dht, cu_seqlens=None, l2=True, gate=True, safe=True, lower_bound=-5.0, **kw):
+    from cula_b200.kda import check_status, chunk_kda
+    names = [n for n in GRADS if inp.get(n) is not None and (gate or n not in ("A_log", "dt_bias"))]
+    # oracle
+    ref_in = {n: inp[n].detach().float().clone().requires_grad_(True) for n in names}
+    o, ht = chunk_kda_oracle(ref_in["q"], ref_in["k"], ref_in["v"], ref_in["g"], ref_in["beta"],
+                             initial_state=ref_in.get("initial_state"), output_final_state=True,
+                             use_qk_l2norm_in_kernel=l2, use_gate_in_kernel=gate, cu_seqlens=cu_seqlens,
+                             safe_gate=safe, lower_bound=lower_bound if (gate and safe) else None,
+                             A_log=ref_in.get("A_log"), dt_bias=ref_in.get("dt_bias"))
+    ((o * do.float()).sum() + (ht * dht).sum()).backward()
+    ref = {n: t.grad for n, t in ref_in.items()}
+    # CUDA path
+    dev_in = {n: inp[n].detach().cuda().requires_grad_(True) for n in names}
+    extra = dict(A_log=dev_in.get("A_log"), dt_bias=dev_in.get("dt_bias")) if gate else {}
+    o2, ht2 = chunk_kda(dev_in["q"], dev_in["k"], dev_in["v"], dev_in["g"], dev_in["beta"],
+                        initial_state=dev_in.get("initial_state"), output_final_state=True,
+                        use_qk_l2norm_in_kernel=l2, use_gate_in_kernel=gate, safe_gate=safe,
+                        lower_bound=lower_bound if (gate and safe) else None,
+                        cu_seqlens=None if cu_seqlens is None else cu_seqlens.cuda(), **extra, **kw)
+    ((o2.float() * do.cuda().float()).sum() + (ht2 * dht.cuda()).sum()).backward()
+    torch.cuda.synchronize()
+    check_status()
+    got = {n: t.grad.float().cpu() for n, t in dev_in.items()}
+    for n in names:
+        assert got[n].shape == ref[n].shape and dev_in[n].grad.dtype == dev_in[n].dtype, n
+    return ref, got
+
+
+def assert_grads(ref, got, tol, tag=""):
+    msgs = []
+    for n in ref:
+        e = err_ratio(ref[n], got[n])
+        mx = float((ref[n] - got[n]).abs().max() / (ref[n].abs().max() + 1e-30))
+        t = tol.get(n, tol["default"])
+        if not (e <= t and mx <= 2e-2 and torch.isfinite(got[n]).all()):
+            msgs.append(f"d{n}: rel {e:.2e} (tol {t}) maxabs/max {mx:.2e}")
+    assert not msgs, f"{tag}: " + "; ".join(msgs)
+
+
+HEADLINE_TOL = {"default": 5e-3}
+SUITE_TOL = {"default": 8e-3, "g": 2e-2, "beta": 2e-2}
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_backward_matches_golden(name):
+    from cula_b200.kda import chunk_kda
+    case, inp, exp = load_golden(name)
+    names = [n for n in ("q", "k", "v", "g", "beta", "A_log", "dt_bias", "h0") if n in inp]
+    dev = {n: inp[n].detach().cuda().requires_grad_(True) for n in names}
+    extra = dict(A_log=dev.get("A_log"), dt_bias=dev.get("dt_bias")) if case["use_gate_in_kernel"] else {}
+    o, ht = chunk_kda(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], initial_state=dev.get("h0"),
+                      output_final_state=True, use_qk_l2norm_in_kernel=case["use_l2norm"],
+                      use_gate_in_kernel=case["use_gate_in_kernel"], safe_gate=case["safe_gate"],
+                      lower_bound=case["lower_bound"],
+                      cu_seqlens=None if case["cu_seqlens"] is None else case["cu_seqlens"].cuda(), **extra)
+    ((o.float() * inp["do"].cuda().float()).sum() + (ht * inp["dht"].cuda()).sum()).backward()
+    torch.cuda.synchronize()
+    ref = {n: exp["d" + n] for n in names}
+    got = {n: dev[n].grad.float().cpu() for n in names}
+    assert_grads(ref, got, SUITE_TOL, name)
+
+
+def test_backward_headline_distribution():
+    """B=1, T=512, H=4 with the headline input distributions, N(0,1) upstream gradient, 0.1*N(0,1) initial state."""
+    inp = make_inputs(1, 512, 4, seed=0, h0_std=0.1)
+    gen = torch.Generator().manual_seed(5)
+    do = torch.randn(1, 512, 4, 128, generator=gen).to(torch.bfloat16)
+    dht = torch.zeros(1, 4, 128, 128)
+    ref, got = run_both(inp, do, dht)
+    assert_grads(ref, got, HEADLINE_TOL, "headline")
+
+
+@pytest.mark.parametrize("B,T,H,gate_offset,recompute", [
+    (1, 63, 1, -6.0, True), (2, 500, 3, -8.0, False), (2, 300, 2, 0.0, True), (1, 1, 2, -8.0, True), (1, 65, 2, -3.0, False),
+])
+def test_backward_shapes(B, T, H, gate_offset, recompute):
+    inp = make_inputs(B, T, H, seed=42, gate_offset=gate_offset, h0_std=1.0)
+    inp["A_log"] = inp["A_log"] + 0.1
+    gen = torch.Generator().manual_seed(7)
+    inp["dt_bias"] = 0.1 * torch.randn(H * 128, generator=gen)
+    do = torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16)
+    dht = torch.randn(B, H, 128, 128, generator=gen)
+    ref, got = run_both(inp, do, dht, disable_recompute=not recompute)
+    assert_grads(ref, got, SUITE_TOL, f"B{B}T{T}H{H}")
+
+
+@pytest.mark.parametrize("beta_dtype,g_fp32,safe", [(torch.float32, True, True), (torch.bfloat16, False, False)])
+def test_backward_pre_gated_softplus_and_dtypes(beta_dtype, g_fp32, safe):
+    """use_gate_in_kernel=False with an fp32 log-decay and fp32 beta; and the softplus gate (safe_gate=False)."""
+    B, T, H = 2, 200, 2
+    gen = torch.Generator().manual_seed(11)
+    if g_fp32:
+        inp = make_inputs(B, T, H, seed=5, h0_std=1.0, beta_dtype=beta_dtype)
+        inp["g"] = (F.logsigmoid(torch.randn(B, T, H, 128, generator=gen)) / 4.0).clamp(-5, 0)
+        inp["q"] = F.normalize(inp["q"].float(), dim=-1).to(torch.bfloat16)
+        inp["k"] = F.normalize(inp["k"].float(), dim=-1).to(torch.bfloat16)
+        kw = dict(l2=False, gate=False)
+    else:
+        inp = make_inputs(B, T, H, seed=5, gate_offset=-4.0, h0_std=1.0, beta_dtype=beta_dtype)
+        inp["dt_bias"] = 0.2 * torch.randn(H * 128, generator=gen)
+        kw = dict(safe=False)
+    do = torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16)
+    dht = torch.randn(B, H, 128, 128, generator=gen)
+    ref, got = run_both(inp, do, dht, **kw)
+    assert_grads(ref, got, SUITE_TOL, "dtypes")
+
+
+@pytest.mark.parametrize("lens", [[15], [1, 63, 65], [100, 300, 56], [33, 128, 200, 95]])
+def test_backward_varlen(lens):
+    H, T = 2, sum(lens)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    inp = make_inputs(1, T, H, seed=9, gate_offset=-7.0)
+    gen = torch.Generator().manual_seed(1)
+    inp["initial_state"] = torch.randn(len(lens), H, 128, 128, generator=gen)
+    do = torch.randn(1, T, H, 128, generator=gen).to(torch.bfloat16)
+    dht = torch.randn(len(lens), H, 128, 128, generator=gen)
+    ref, got = run_both(inp, do, dht, cu_seqlens=cu)
+    assert_grads(ref, got, SUITE_TOL, f"varlen{lens}")
+
+
+def test_backward_small_upstream_gradient_and_no_state():
+    """dO of order 1e-6 (mean-reduced losses): the power-of-two gradient scale keeps fp16 operands in range.
+    Also covers initial_state=None / no final-state gradient."""
+    from cula_b200.kda import chunk_kda
+    B, T, H = 1, 256, 2
+    inp = make_inputs(B, T, H, seed=3, gate_offset=-6.0)
+    gen = torch.Generator().manual_seed(2)
+    do = (1e-6 * torch.randn(B, T, H, 128, generator=gen)).to(torch.bfloat16)
+    names = ("q", "k", "v", "g", "beta", "A_log", "dt_bias")
+    ref_in = {n: inp[n].detach().float().clone().requires_grad_(True) for n in names}
+    o, _ = chunk_kda_oracle(ref_in["q"], ref_in["k"], ref_in["v"], ref_in["g"], ref_in["beta"],
+                            use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+                            A_log=ref_in["A_log"], dt_bias=ref_in["dt_bias"])
+    (o * do.float()).sum().backward()
+    dev = {n: inp[n].detach().cuda().requires_grad_(True) for n in names}
+    o2, ht2 = chunk_kda(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], use_qk_l2norm_in_kernel=True,
+                        use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=dev["A_log"], dt_bias=dev["dt_bias"])
+    assert ht2 is None
+    (o2.float() * do.cuda().float()).sum().backward()
+    torch.cuda.synchronize()
+    ref = {n: ref_in[n].grad for n in names}
+    got = {n: dev[n].grad.float().cpu() for n in names}
+    assert_grads(ref, got, SUITE_TOL, "tiny dO")
+
+
+def test_backward_is_deterministic_except_atomics():
+    """dq, dk, dv, dg, dbeta, dh0 are bit-identical across runs (dA_log / d dt_bias are atomic sums)."""
+    inp = make_inputs(2, 300, 2, seed=1, gate_offset=-8.0, h0_std=1.0)
+    gen = torch.Generator().manual_seed(3)
+    do = torch.randn(2, 300, 2, 128, generator=gen).to(torch.bfloat16)
+    dht = torch.randn(2, 2, 128, 128, generator=gen)
+    runs = [run_both(inp, do, dht)[1] for _ in range(2)]
+    for n in ("q", "k", "v", "g", "beta", "initial_state"):
+        assert torch.equal(runs[0][n], runs[1][n]), n
