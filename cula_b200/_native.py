@@ -26,6 +26,9 @@ SIGNATURES = {
     "cula_kda_bwd_dense": (_i, [_fp, _fp, _vp, _vp, _vp, _vp, _vp, _i, _fp, _fp, _vp, _fp, _ip, _ip, _i, _i, _i, _vp]),
     "cula_kda_bwd_gated": (_i, [_vp, _vp, _vp, _i, _vp, _i, _fp, _fp, _fp, _fp, _fp, _fp, _vp, _vp, _vp, _vp, _fp, _fp,
                                 _ip, _ip, _i, _i, _i, _f, _i, _i, _f, _vp]),
+    "cula_kda_noalloc_max_tiles": (_i, []),
+    "cula_kda_fwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _fp, _fp, _fp, _vp, _fp, _ip, _ip, _ip,
+                                  _i, _i, _i, _i, _f, _i, _i, _f, _ip, _vp]),
     "cula_kda_strerror": (ctypes.c_char_p, [_i]),
 }
 

@@ -140,6 +140,7 @@ extern "C" const char* cula_kda_strerror(int code) {
     if (code == 0) return "ok";
     if (code == CULA_KDA_EINVAL) return "invalid argument (null pointer, non-positive size or bad enum)";
     if (code == CULA_KDA_EALIGN) return "pointer is not 16-byte aligned";
+    if (code == CULA_KDA_ETOOBIG) return "num_chunks * H exceeds the fixed capacity of cula_kda_fwd_noalloc (256 tiles)";
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
     return "unknown error";
 }

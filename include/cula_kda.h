@@ -23,6 +23,9 @@ extern "C" {
 
 #define CULA_KDA_EINVAL (-1)   /* null pointer / non-positive size / bad enum */
 #define CULA_KDA_EALIGN (-2)   /* a pointer is not 16-byte aligned */
+#define CULA_KDA_ETOOBIG (-3)  /* problem exceeds the fixed capacity of cula_kda_fwd_noalloc */
+
+#define CULA_KDA_NOALLOC_MAX_TILES 256   /* capacity of cula_kda_fwd_noalloc: num_chunks * H */
 
 #define CULA_KDA_GATE_NONE 0         /* g already holds the natural-log decay (use_gate_in_kernel=False) */
 #define CULA_KDA_GATE_SOFTPLUS 1     /* a = -exp(A_log[h]) * softplus(g + dt_bias[h,:]) */
@@ -121,6 +124,27 @@ int cula_kda_bwd_gated(const void* d_q, const void* d_k, const void* d_g, int g_
                        void* d_dq, void* d_dk, void* d_dg, void* d_dbeta, float* d_dA_log, float* d_ddt_bias,
                        const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H,
                        float scale, int use_qk_l2norm, int gate_mode, float lower_bound, void* stream);
+
+/*
+ * Whole forward pass (both launches above) for callers that cannot allocate device memory themselves -- a runtime
+ * that has given all device memory to its own pool, a plugin inside a foreign memory manager, a path where
+ * cudaMalloc's device-wide synchronisation is unacceptable. It has no counterpart in the reference, whose Python
+ * layer allocates every workspace with torch. The tile packs live in a fixed 18.1 MiB array inside the library's
+ * device image (held by every GPU that loads the library until the process exits), so:
+ *   - num_chunks * H must not exceed CULA_KDA_NOALLOC_MAX_TILES (= 256), else CULA_KDA_ETOOBIG is returned;
+ *   - all calls on a device share that array: calls that can overlap on the GPU race, serialise them;
+ *   - the first call on a device resolves the array's address; make it before any stream capture on that device.
+ * Arguments as in cula_kda_fwd_intra / cula_kda_fwd_scan (d_chunk_offsets/d_chunk_indices/d_cu_seqlens all NULL for
+ * a fixed-length batch, where num_chunks must equal N * ceil(T/64)). Never calls cudaMalloc or cudaFree.
+ */
+int cula_kda_noalloc_max_tiles(void);
+int cula_kda_fwd_noalloc(const void* d_q, const void* d_k, const void* d_v, const void* d_g, int g_is_fp32,
+                         const void* d_beta, int beta_is_fp32, const float* d_A_log, const float* d_dt_bias,
+                         const float* d_h0, void* d_o, float* d_ht,
+                         const int* d_cu_seqlens, const int* d_chunk_indices, const int* d_chunk_offsets,
+                         int num_chunks, int N, int T, int H,
+                         float scale, int use_qk_l2norm, int gate_mode, float lower_bound,
+                         int* d_status, void* stream);
 
 /* Human-readable text for a return value of the functions above. */
 const char* cula_kda_strerror(int code);
