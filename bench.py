@@ -241,11 +241,11 @@ def main():
         _native.check(lib.cula_kda_fwd_intra(d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), d["g"].data_ptr(), 0,
                                              d["beta"].data_ptr(), 0, d["A_log"].data_ptr(), d["dt_bias"].data_ptr(),
                                              None, None, nchunks, T, H, 128 ** -0.5, 1, 2, -5.0, tiles.data_ptr(), None,
-                                             status.data_ptr(), stream), "intra")
+                                             None, status.data_ptr(), stream), "intra")
 
     def k_scan():
         _native.check(lib.cula_kda_fwd_scan(tiles.data_ptr(), None, o_buf.data_ptr(), ht_buf.data_ptr(), None, None,
-                                            None, None, None, B, T, H, status.data_ptr(), stream), "scan")
+                                            None, None, None, None, B, T, H, status.data_ptr(), stream), "scan")
 
     ms_intra = timed(k_intra, args.steps, 3)
     ms_scan = timed(k_scan, args.steps, 3)
