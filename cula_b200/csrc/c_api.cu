@@ -5,6 +5,9 @@
 
 extern "C" int kda_launch_fwd_intra(const kda::IntraParams* p, int num_chunks, cudaStream_t stream);
 extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream);
+extern "C" int kda_launch_fwd_transition(const kda::ScanParams* p, cudaStream_t stream);
+extern "C" int kda_launch_cp_fold(const float* c_all, const float* m_all, const float* h0, float* s_in, int n_prev, int H,
+                                  cudaStream_t stream);
 extern "C" int kda_launch_grad_scale(const void* d_o, size_t n_do, const float* dht, size_t n_dht, unsigned int* amax_bits,
                                      float* gscale, cudaStream_t stream);
 extern "C" int kda_launch_bwd_scan(const kda::BwdScanParams* p, cudaStream_t stream);
@@ -63,6 +66,27 @@ extern "C" int cula_kda_fwd_scan(const void* d_tiles, const float* d_h0, void* d
     p.cu_seqlens = d_cu_seqlens; p.chunk_offsets = d_chunk_offsets; p.seq_order = d_seq_order;
     p.status = d_status; p.T = T; p.H = H; p.N = N;
     return kda_launch_fwd_scan(&p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_cp_transition(const void* d_tiles, float* d_c_out, float* d_m_out, const int* d_cu_seqlens,
+                                      const int* d_chunk_offsets, int N, int T, int H, int* d_status, void* stream) {
+    if (N == 0) return 0;
+    if (!d_tiles || !d_c_out || !d_m_out || !d_status || N < 0 || H <= 0) return CULA_KDA_EINVAL;
+    if ((d_cu_seqlens == nullptr) != (d_chunk_offsets == nullptr)) return CULA_KDA_EINVAL;
+    if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_tiles)) return CULA_KDA_EALIGN;
+    kda::ScanParams p{};
+    p.tiles = static_cast<const unsigned char*>(d_tiles);
+    p.ht = d_c_out; p.m_out = d_m_out; p.cu_seqlens = d_cu_seqlens; p.chunk_offsets = d_chunk_offsets;
+    p.status = d_status; p.T = T; p.H = H; p.N = N;
+    return kda_launch_fwd_transition(&p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, const float* d_h0, float* d_s_in, int n_prev,
+                                int H, void* stream) {
+    if (!d_s_in || n_prev < 0 || H <= 0 || (n_prev > 0 && (!d_c_all || !d_m_all))) return CULA_KDA_EINVAL;
+    if (misaligned(d_m_all)) return CULA_KDA_EALIGN;
+    return kda_launch_cp_fold(d_c_all, d_m_all, d_h0, d_s_in, n_prev, H, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cula_kda_bwd_scratch_floats(void) { return kda::BWD_SCRATCH_FLOATS; }

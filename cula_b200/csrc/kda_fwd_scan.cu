@@ -25,13 +25,18 @@ constexpr int SCAN_THREADS = (SCAN_CONSUMERS + 1) * 32;
 constexpr int SCAN_SMEM = SCAN_STAGES * SCAN_STAGE_BYTES + SCAN_CONSUMERS * SCAN_STG_BYTES + 64;
 constexpr int ST_U = TP_HEAD_BYTES;                      // offset of the U half inside a stage
 
-template <bool STORE_HV>
+// TRANSITION: the affine action of a whole shard on the state, S_out = M S_in + C, from the same recurrence with
+// four column groups per (sequence, head): groups 0,1 carry C (zero start, normal u; written to p.ht) and groups
+// 2,3 carry the K x K matrix M = prod_c (D_c - kg_c^T w_c) (identity start, u = 0; written to p.m_out). No output
+// rows are produced. Used by context parallelism.
+template <bool STORE_HV, bool TRANSITION>
 __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const ScanParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + SCAN_STAGES * SCAN_STAGE_BYTES + SCAN_CONSUMERS * SCAN_STG_BYTES);
     uint64_t* empty = full + SCAN_STAGES;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int vh = blockIdx.x, h = blockIdx.y;
+    const bool is_m = TRANSITION && blockIdx.x >= 2;     // this CTA carries columns of M
+    const int vh = blockIdx.x & 1, h = blockIdx.y;
     const int n = p.seq_order ? p.seq_order[blockIdx.z] : blockIdx.z;
     int bos, len, chunk0;
     if (p.cu_seqlens) {
@@ -65,9 +70,14 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
                 }
                 const unsigned char* tile = p.tiles + ((size_t)(chunk0 + c) * p.H + h) * TP_BYTES;
                 unsigned char* dst = smem + s * SCAN_STAGE_BYTES;
-                mbar_arrive_expect_tx(&full[s], SCAN_STAGE_BYTES);
-                bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
-                bulk_g2s(dst + ST_U, tile + (vh ? TP_U1 : TP_U0), 8192, &full[s]);
+                if (is_m) {
+                    mbar_arrive_expect_tx(&full[s], TP_HEAD_BYTES);
+                    bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
+                } else {
+                    mbar_arrive_expect_tx(&full[s], SCAN_STAGE_BYTES);
+                    bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
+                    bulk_g2s(dst + ST_U, tile + (vh ? TP_U1 : TP_U0), 8192, &full[s]);
+                }
             }
         }
         return;
@@ -81,7 +91,16 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
     const uint32_t stg_u32 = smem_u32(stg);
 
     float S[16][4];
-    if (p.h0) {
+    if (is_m) {
+#pragma unroll
+        for (int jt = 0; jt < 16; ++jt) {
+            const int k0 = 8 * jt + 2 * t;
+            S[jt][0] = (k0 == vb + g) ? 1.f : 0.f;
+            S[jt][1] = (k0 + 1 == vb + g) ? 1.f : 0.f;
+            S[jt][2] = (k0 == vb + g + 8) ? 1.f : 0.f;
+            S[jt][3] = (k0 + 1 == vb + g + 8) ? 1.f : 0.f;
+        }
+    } else if (!TRANSITION && p.h0) {
         const float* h0 = p.h0 + ((size_t)n * p.H + h) * DK * DV;
 #pragma unroll
         for (int jt = 0; jt < 16; ++jt) {
@@ -179,7 +198,13 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
                 mma_f16(acc[nt], sa[2 * kp + 1], b2, b3);
             }
         }
-        // ---- v_new^T = u^T - acc ----
+        // ---- v_new^T = u^T - acc  (u = 0 for the transition matrix) ----
+        if (is_m) {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                acc[nt][0] *= -s_down; acc[nt][1] *= -s_down; acc[nt][2] *= -s_down; acc[nt][3] *= -s_down;
+            }
+        } else {
 #pragma unroll
         for (int np = 0; np < 4; ++np) {
             uint32_t r0, r1, r2, r3;
@@ -190,6 +215,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
             f = unpack_f16(r1); acc[2 * np][2] = fmaf(-s_down, acc[2 * np][2], f.x); acc[2 * np][3] = fmaf(-s_down, acc[2 * np][3], f.y);
             f = unpack_f16(r2); acc[2 * np + 1][0] = fmaf(-s_down, acc[2 * np + 1][0], f.x); acc[2 * np + 1][1] = fmaf(-s_down, acc[2 * np + 1][1], f.y);
             f = unpack_f16(r3); acc[2 * np + 1][2] = fmaf(-s_down, acc[2 * np + 1][2], f.x); acc[2 * np + 1][3] = fmaf(-s_down, acc[2 * np + 1][3], f.y);
+        }
         }
         uint32_t va[4][4];   // v_new^T as fp16 A fragments (4 k-steps over the 64 tokens)
 #pragma unroll
@@ -218,7 +244,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
         }
 
         // ---- o^T = S^T qg^T + v_new^T Aqk^T ----
-        {
+        if (!TRANSITION) {
             float oacc[8][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) oacc[nt][0] = oacc[nt][1] = oacc[nt][2] = oacc[nt][3] = 0.f;
@@ -293,8 +319,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
         if (lane == 0) mbar_arrive(&empty[s]);
     }
 
-    if (p.ht) {
-        float* ht = p.ht + ((size_t)n * p.H + h) * DK * DV;
+    float* final_dst = is_m ? p.m_out : p.ht;
+    if (final_dst) {
+        float* ht = final_dst + ((size_t)n * p.H + h) * DK * DV;
 #pragma unroll
         for (int jt = 0; jt < 16; ++jt) {
             int k0 = 8 * jt + 2 * t;
@@ -316,13 +343,24 @@ extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream
     dim3 grid(2, p->H, p->N);
     cudaError_t e;
     if (p->vnew_out) {
-        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
         if (e != cudaSuccess) return (int)e;
-        kda_fwd_scan_kernel<true><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+        kda_fwd_scan_kernel<true, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
     } else {
-        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
         if (e != cudaSuccess) return (int)e;
-        kda_fwd_scan_kernel<false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+        kda_fwd_scan_kernel<false, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
     }
+    return (int)cudaGetLastError();
+}
+
+// Affine shard transitions of every (sequence, head): p->ht receives C, p->m_out receives M; p->o / p->h0 unused.
+extern "C" int kda_launch_fwd_transition(const kda::ScanParams* p, cudaStream_t stream) {
+    using namespace kda;
+    if (p->N <= 0) return 0;
+    dim3 grid(4, p->H, p->N);
+    cudaError_t e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    kda_fwd_scan_kernel<false, true><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
     return (int)cudaGetLastError();
 }

@@ -43,6 +43,7 @@ struct ScanParams {
     float* ht;                    // [N, H, 128, 128] fp32 or null
     void* h_out;                  // per-chunk incoming state, bf16, or null
     float* h32_out;               // per-chunk incoming state, fp32, or null
+    float* m_out;                 // [N, H, 128, 128] shard transition matrices (transition launch only)
     void* vnew_out;               // per-chunk v_new, fp16, or null
     const int* cu_seqlens;        // [N+1] or null
     const int* chunk_offsets;     // [N+1] first global chunk of each sequence, or null

@@ -125,6 +125,24 @@ int cula_kda_bwd_gated(const void* d_q, const void* d_k, const void* d_g, int g_
                        const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H,
                        float scale, int use_qk_l2norm, int gate_mode, float lower_bound, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * Context parallelism (one long sequence split into contiguous shards, one per GPU). The reference reaches this
+ * through flash-linear-attention's cp_context (cula/kda/chunk_fwd.py:99-109,122-127; fla/ops/cp/chunk_delta_h.py).
+ * A shard acts on the carried state as S_out = M S_in + C.
+ * ------------------------------------------------------------------------------------------------------------ */
+
+/* Per (sequence, head): d_c_out [N,H,128,128] = final state of the shard started from zero, d_m_out [N,H,128,128] =
+ * transition matrix. Same tile packs and tables as cula_kda_fwd_scan. Replaces
+ * chunk_gated_delta_rule_fwd_h_pre_process (fla/ops/cp/chunk_delta_h.py:736-795). */
+int cula_kda_cp_transition(const void* d_tiles, float* d_c_out, float* d_m_out,
+                           const int* d_cu_seqlens, const int* d_chunk_offsets, int N, int T, int H,
+                           int* d_status, void* stream);
+
+/* d_s_in [H,128,128] = fold of the first n_prev gathered transitions (d_c_all, d_m_all: [W,H,128,128], in this GPU's
+ * own memory) applied to d_h0 (or zero when NULL). Replaces the merge step (fla/ops/cp/chunk_delta_h.py:797-817). */
+int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, const float* d_h0, float* d_s_in, int n_prev, int H,
+                     void* stream);
+
 /*
  * Whole forward pass (both launches above) for callers that cannot allocate device memory themselves -- a runtime
  * that has given all device memory to its own pool, a plugin inside a foreign memory manager, a path where

@@ -1,0 +1,90 @@
+"""Context-parallel kernels on the GPU. With one device the W ranks are emulated one after the other in this
+process (the gather is a stack), which exercises the transition launch, the fold kernel and the scan from a folded
+state; with two or more devices a real NCCL run is launched through torch.distributed.run."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from oracle import c_oracle
+from oracle.naive_kda import err_ratio, make_inputs
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _oracle(inp):
+    f = lambda x: None if x is None else x.float().numpy()
+    o, ht = c_oracle.naive_kda_fwd(f(inp["q"]), f(inp["k"]), f(inp["v"]), f(inp["g"]), f(inp["beta"]), f(inp["A_log"]),
+                                   f(inp["dt_bias"]), f(inp["initial_state"]), use_l2norm=True, gate_mode=2, lower_bound=-5.0)
+    return torch.from_numpy(o), torch.from_numpy(ht)
+
+
+@pytest.mark.parametrize("world,T,gate_offset", [(2, 256, -8.0), (4, 1024, -8.0), (3, 64 * 5 + 17, -6.0), (4, 512, 0.0)])
+def test_cp_emulated_ranks_match_oracle(world, T, gate_offset):
+    from cula_b200.kda import check_status
+    from cula_b200.kda.cp import CudaBackend, cp_forward
+    H = 4
+    inp = make_inputs(1, T, H, seed=2, gate_offset=gate_offset, h0_std=0.5)
+    per = (T // world) // 64 * 64
+    bounds = [r * per for r in range(world)] + [T]
+    backends = []
+    for r in range(world):
+        sl = slice(bounds[r], bounds[r + 1])
+        backends.append(CudaBackend(inp["q"][:, sl].cuda(), inp["k"][:, sl].cuda(), inp["v"][:, sl].cuda(),
+                                    inp["g"][:, sl].cuda(), inp["beta"][:, sl].cuda(), 128 ** -0.5, True, True, True, -5.0,
+                                    inp["A_log"].cuda(), inp["dt_bias"].cuda()))
+    trans = [b.zeros_transition() if r == world - 1 else b.transition() for r, b in enumerate(backends)]
+    stacked = {"C": torch.stack([t[0] for t in trans]), "M": torch.stack([t[1] for t in trans])}
+
+    class Replay:                       # the emulated collective: every rank sees the same stacked tensors
+        def __init__(self):
+            self.calls = 0
+
+        def __call__(self, x):
+            self.calls += 1
+            return stacked["C"] if self.calls % 2 == 1 else stacked["M"]
+
+    outs, final = [], None
+    for r, b in enumerate(backends):
+        b.transition = lambda t=trans[r]: t           # already computed above
+        o, ht = cp_forward(b, Replay(), r, world, inp["initial_state"].cuda(), True)
+        outs.append(o)
+        final = ht if ht is not None else final
+    torch.cuda.synchronize()
+    check_status()
+    o = torch.cat(outs, dim=1).float().cpu()
+    o_ref, ht_ref = _oracle(inp)
+    assert err_ratio(o_ref, o) <= 5e-3 and float((o_ref - o).abs().max()) <= 2e-2
+    assert err_ratio(ht_ref, final.cpu()) <= 2e-3
+
+
+def test_cp_transition_is_the_affine_map_of_the_shard():
+    """S_out = M S_in + C must reproduce the final state of a scan started from a random state."""
+    from cula_b200.kda import chunk_kda
+    from cula_b200.kda.cp import CudaBackend
+    T, H = 320, 2
+    inp = make_inputs(1, T, H, seed=4, gate_offset=-8.0, h0_std=1.0)
+    d = {k: v.cuda() for k, v in inp.items()}
+    b = CudaBackend(d["q"], d["k"], d["v"], d["g"], d["beta"], 128 ** -0.5, True, True, True, -5.0, d["A_log"], d["dt_bias"])
+    C, M = b.transition()
+    _, ht = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
+                      initial_state=d["initial_state"], output_final_state=True, use_qk_l2norm_in_kernel=True,
+                      use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
+    pred = torch.matmul(M.double(), d["initial_state"][0].double()) + C.double()
+    assert err_ratio(ht[0].double().cpu(), pred.cpu()) <= 2e-3
+    folded = b.fold(C[None], M[None], d["initial_state"], 1)
+    assert err_ratio(pred.cpu(), folded.double().cpu()) <= 1e-5
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_cp_two_gpus_nccl(tmp_path):
+    script = os.path.join(ROOT, "tests", "cp_nccl_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29611", script, str(tmp_path)],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "CP_OK" in out.stdout
