@@ -33,6 +33,32 @@ WORKLOADS = {
     "fwd_B4_T8192_H32": (4, 8192, 32),
     "fwd_B1_T512_H4": (1, 512, 4),
 }
+# Secondary workloads (selected with --workload; not the headline line): forward+backward, the packed varlen
+# forward, and the context-parallel forward of one long sequence split over the ranks (strong scaling).
+EXTRA_WORKLOADS = {
+    "fwdbwd_B4_T8192_H32": dict(kind="fwdbwd", B=4, T=8192, H=32),
+    "fwdbwd_B2_T2048_H32": dict(kind="fwdbwd", B=2, T=2048, H=32),
+    "varlen_64seq_65536_H32": dict(kind="varlen", n_seqs=64, total=65536, H=32),
+    "cp_T262144_H32": dict(kind="cp", T=262144, H=32),
+    "cp_T32768_H32": dict(kind="cp", T=32768, H=32),
+}
+
+
+def varlen_lengths(n_seqs=64, total=65536, seed=0):
+    """Seeded lognormal lengths (median 512, sigma 1, clipped to [63, 8192]) adjusted to sum to `total`."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    lens = np.clip(np.round(rng.lognormal(np.log(512.0), 1.0, n_seqs)), 63, 8192).astype(np.int64)
+    diff = int(total - lens.sum())
+    order = np.argsort(-lens)
+    i = 0
+    while diff != 0:
+        j = order[i % n_seqs]
+        step = max(-int(lens[j] - 63), min(int(8192 - lens[j]), diff))
+        lens[j] += step
+        diff -= step
+        i += 1
+    return lens.tolist()
 FLOP_PER_TOKEN_HEAD = 180224          # dense-tile convention, forward
 BYTES_PER_TOKEN_HEAD = 1282           # compulsory forward traffic: q,k,v,g bf16 + beta + o
 TILE_PACK_BYTES = 74240
@@ -58,7 +84,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
@@ -142,13 +168,115 @@ def run_reference(args, rank, world):
     }), flush=True)
 
 
+def run_extra(args, rank, world, local_rank):
+    """Secondary workloads: same timing rules as the headline (warm-up, L2 flush before every timed step, CUDA
+    events, max over ranks); one JSON line from rank 0."""
+    import torch.distributed as dist
+    from cula_b200 import _native
+    from cula_b200.kda import check_status, chunk_kda
+    from cula_b200.kda.cp import chunk_kda_cp
+    from cula_b200.synthetic import make_inputs
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm is timed on the headline workload only"}))
+        return
+    w = EXTRA_WORKLOADS[args.workload]
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 or w["kind"] == "cp":
+        if not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29577")
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    _native.lib()
+    kw = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
+    H = w["H"]
+    scaling, launches = "weak", 2
+    if w["kind"] == "fwdbwd":
+        B, T = w["B"], w["T"]
+        inp = make_inputs(B, T, H, seed=rank, h0_std=0.1)
+        d = {k: v.to(dev).requires_grad_(True) for k, v in inp.items()}
+        do = torch.randn(B, T, H, 128, device=dev).to(torch.bfloat16)
+
+        def step():
+            for t in d.values():
+                t.grad = None
+            o, _ = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
+                             initial_state=d["initial_state"], output_final_state=True, **kw)
+            o.backward(do)
+        tokens, metric, launches = B * T * world, "chunk_kda forward+backward tokens/s", 9
+        cfg = {"B_per_gpu": B, "T": T, "sharding": "batch x head shards, one per rank, no collective"}
+    elif w["kind"] == "varlen":
+        lens = varlen_lengths(w["n_seqs"], w["total"], seed=rank)
+        T = sum(lens)
+        cu = torch.tensor([0] + list(__import__("itertools").accumulate(lens)), dtype=torch.int32, device=dev)
+        inp = make_inputs(1, T, H, seed=rank)
+        d = {k: v.to(dev) for k, v in inp.items() if v is not None}
+        step = lambda: chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
+                                 cu_seqlens=cu, output_final_state=True, **kw)
+        tokens, metric = T * world, "chunk_kda varlen forward tokens/s"
+        cfg = {"sequences_per_gpu": len(lens), "tokens_per_gpu": T, "min_len": min(lens), "max_len": max(lens)}
+    else:   # context parallel: ONE sequence of T tokens split over the ranks
+        T = w["T"]
+        per = T // world
+        inp = make_inputs(1, per, H, seed=100 + rank)       # this rank's shard
+        d = {k: v.to(dev) for k, v in inp.items() if v is not None}
+        step = lambda: chunk_kda_cp(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
+                                    output_final_state=True, **kw)
+        tokens, metric, scaling, launches = T, "chunk_kda context-parallel forward tokens/s", "strong", (4 if world > 1 else 2)
+        cfg = {"T_total": T, "T_per_gpu": per, "exchange": "all-gather of (C|M) [H,128,256] fp32 per rank over NCCL"}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.5)
+    evs = []
+    for _ in range(args.steps):
+        flush.zero_()
+        if w["kind"] == "cp" and world > 1:
+            dist.barrier()                      # ranks enter every step together; the collective is inside the timed region
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        evs.append((e0, e1))
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    check_status(dev)
+    ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({
+            "metric": metric, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict({"workload": args.workload, "H": H, "K": 128, "V": 128,
+                            "l2": "256 MB flush buffer written before every timed step"}, **cfg),
+            "gpu_launches": launches * args.steps, "clocks": clocks}), flush=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="fwd_B2_T2048_H32", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="fwd_B2_T2048_H32", choices=sorted(WORKLOADS) + sorted(EXTRA_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -156,6 +284,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload in EXTRA_WORKLOADS:
+        return run_extra(args, rank, world, local_rank)
     if args.impl == "reference":
         return run_reference(args, rank, world)
 
@@ -206,11 +336,13 @@ def main():
         return total_ms / steps
 
     # ---- device-resident throughput ("value") ----
+    # the clock sampler runs from before the warm-up to the end of the last timed loop (the timed region of the
+    # headline number alone lasts only a few milliseconds, shorter than one nvidia-smi sampling period)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.5)
     ms = timed(lambda: fwd(d), args.steps, args.warmup)
-    clocks = sampler.stop() if rank == 0 else None
     check_status(dev)
     tokens = B * T * world
 
@@ -249,6 +381,7 @@ def main():
 
     ms_intra = timed(k_intra, args.steps, 3)
     ms_scan = timed(k_scan, args.steps, 3)
+    clocks = sampler.stop() if rank == 0 else None
     th = B * T * H
     kernels = {
         "kda_fwd_intra_kernel": dict(ms=ms_intra, bytes=th * (1282 - 256) + nchunks * H * TILE_PACK_BYTES),
