@@ -219,9 +219,19 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         for (int n = 0; n < 4; ++n) {
             const int row = (tid >> 4) + 16 * n;
             float a[8];
+            if (p.gate_mode == GATE_LOWER_BOUND) {
+                // lower_bound * sigmoid(alpha x) / ln2 with one ex2 and one rcp (flush-to-zero approximations)
+                const float c0 = -alpha * RCP_LN2, c1 = p.lower_bound * RCP_LN2;
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-                a[e] = (row < ci.valid) ? RCP_LN2 * gate_activation(gv[n][e], alpha, bias[e], p.gate_mode, p.lower_bound) : 0.f;
+                for (int e = 0; e < 8; ++e) a[e] = c1 * fast_rcp(1.f + fast_exp2(c0 * (gv[n][e] + bias[e])));
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = RCP_LN2 * gate_activation(gv[n][e], alpha, bias[e], p.gate_mode, p.lower_bound);
+            }
+            if (row >= ci.valid) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = 0.f;
+            }
             *reinterpret_cast<float4*>(sG + row * DK + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
             *reinterpret_cast<float4*>(sG + row * DK + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
         }
