@@ -1,15 +1,20 @@
 // Chunk-parallel backward, gated part: per (chunk, head), from the scratch record of the dense stage,
 //   dA  = dAu + stril(dW X^T),  dL = -stril(A^T dA A^T),  Zw = A^T dW  (gradient w.r.t. X = beta k 2^g)
-//   VJPs of the two gated Gram matrices (Aqk and L) with the exact pairwise factors 2^(g_i - g_j), j <= i
-//   chain rule to q-hat, k-hat and the cumulative gate; reverse cumulative sum; gate activation VJP
-//   (dg, dA_log, d dt_bias); L2-norm VJP; dq, dk, dg, dbeta to HBM.
+//   VJPs of the two gated Gram matrices (Aqk and L), chain rule to q-hat, k-hat and the cumulative gate,
+//   reverse cumulative sum, gate activation VJP (dg, dA_log, d dt_bias), L2-norm VJP; dq, dk, dg, dbeta to HBM.
 //
 // Covers the gate-dependent half of chunk_kda_bwd_kernel_wy_dqkg_fused (cula/kda/chunk_bwd.py:145-313),
 // chunk_kda_bwd_kernel_intra (cula/kda/chunk_intra.py:367-627), the reverse chunk_local_cumsum and
 // kda_gate_bwd (cula/kda/chunk_bwd.py:594-602) and l2norm_bwd (cula/kda/chunk.py:190-192).
 //
-// This first version evaluates the pairwise part on CUDA cores in fp32 (exponents G_i - G_j <= 0 are formed
-// directly, so no anchoring is needed); the tensor-core formulation with per-block anchors is future work.
+// All contractions run as TF32 mma.sync (m16n8k8) on fp32 operands in shared memory. The Gram-matrix VJPs
+//     dq_i += sum_{j<=i} cP_ij k_j 2^(g_i-g_j)        dk_i += sum_{j<i} cR_ij k_j 2^(g_i-g_j)
+//     dk_j += sum_{i>=j} (cP_ij q_i + cR_ij k_i) 2^(g_i-g_j)
+// never form 2^(g_i-g_j) pairwise: for the rows of a 16-row block I the column operand is k_j 2^(r_I-g_j)
+// (r_I = g at the first row of the block, generated on the fly inside the B fragments) and the result is
+// rescaled by 2^(g_i-r_I); for the columns of block J the row operands are q_i, k_i times 2^(g_i-s_J)
+// (s_J = g at the last row of the block) and the result is rescaled by 2^(s_J-g_j). Every factor is either
+// <= 1 or bounded by 2^(15*5*log2 e) ~ 2^108 under the safe gate, and the large ones only meet zero coefficients.
 #include "kda_common.cuh"
 #include "kda_params.h"
 
@@ -17,21 +22,47 @@ namespace kda {
 
 constexpr int BG_THREADS = 256;
 constexpr int AR = 68;                         // padded row of the 64x64 fp32 matrices
+constexpr int AS = 132;                        // padded row of the 64x128 fp32 matrices
 // shared memory map (floats)
 constexpr int BG_G = 0;                        // G    [64][128] log2 cumulative gate
-constexpr int BG_ACC1 = BG_G + 8192;           // dW, later dq-hat accumulator
-constexpr int BG_ACC2 = BG_ACC1 + 8192;        // dk-hat accumulator
-constexpr int BG_ACC3 = BG_ACC2 + 8192;        // X, later dG accumulator
-constexpr int BG_QK = BG_ACC3 + 8192;          // q raw, k raw as bf16 [64][128] each (8192 floats total)
+constexpr int BG_ACC1 = BG_G + 8192;           // dW, later dq-hat accumulator            [64][132]
+constexpr int BG_ACC2 = BG_ACC1 + 64 * AS;     // dk-hat accumulator
+constexpr int BG_ACC3 = BG_ACC2 + 64 * AS;     // X, later dG accumulator
+constexpr int BG_QK = BG_ACC3 + 64 * AS;       // q raw, k raw as bf16 [64][128] each (8192 floats total)
 constexpr int BG_A = BG_QK + 8192;             // A [64][68]
 constexpr int BG_C1 = BG_A + 64 * AR;          // T1, later cP = scale * dPs          [64][68]
 constexpr int BG_C2 = BG_C1 + 64 * AR;         // dA, later cR = beta_i * dL          [64][68]
-constexpr int BG_MISC = BG_C2 + 64 * AR;       // rstd_q[64] rstd_k[64] beta[64] dbeta[64] half[128] red[16] partial[256]
-constexpr int BG_FLOATS = BG_MISC + 64 * 4 + 128 + 16 + 256;
+constexpr int BG_MISC = BG_C2 + 64 * AR;
+constexpr int MS_RSTDQ = 0, MS_RSTDK = 64, MS_BETA = 128, MS_DBETA = 192, MS_HALF = 256, MS_RED = 384,
+              MS_PBETA = 400 /* [2][64] */, MS_PGL = 528 /* [4][128] */, MS_COL = 1040 /* [128] */, MS_END = 1168;
+constexpr int BG_FLOATS = BG_MISC + MS_END;
 constexpr int BG_SMEM = BG_FLOATS * 4;
 
-__device__ __forceinline__ float bg_gate_raw(const void* g, int g_fp32, size_t idx) {
-    return g_fp32 ? reinterpret_cast<const float*>(g)[idx] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g)[idx]);
+__device__ __forceinline__ float bg_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void bg_mma(float (&d)[4], const float (&a)[4], float b0, float b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])), "r"(__float_as_uint(a[3])),
+                   "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+// The same with the B operand carried as a tf32 hi/lo pair (two MMAs): B is then exact to ~2^-22. Used for the Gram
+// VJPs, where every pair (i, j) adds +x to the gate gradient of row i and -x to that of row j through two different
+// products; the reverse cumulative sum relies on those two cancelling, so they must agree far better than tf32.
+__device__ __forceinline__ void bg_mma_split(float (&d)[4], const float (&a)[4], float b0, float b1) {
+    const float h0 = bg_tf32(b0), h1 = bg_tf32(b1);
+    bg_mma(d, a, bg_tf32(b0 - h0), bg_tf32(b1 - h1));
+    bg_mma(d, a, h0, h1);
+}
+// natural-log decay a(x) of one raw gate value and (optionally) da/dx and the A_log-gradient integrand
+__device__ __forceinline__ float bg_gate(float graw, float bias, float alpha, int mode, float lb) {
+    if (mode == GATE_NONE) return graw;
+    const float x = graw + bias;
+    if (mode == GATE_LOWER_BOUND) return lb * fast_rcp(1.f + fast_exp2(-alpha * RCP_LN2 * x));
+    return -alpha * (x > 20.f ? x : log1pf(__expf(x)));
 }
 
 __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdGatedParams p) {
@@ -45,15 +76,19 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     float* sA = sm + BG_A;
     float* c1 = sm + BG_C1;
     float* c2 = sm + BG_C2;
-    float* rstd_q = sm + BG_MISC;
-    float* rstd_k = rstd_q + 64;
-    float* sBeta = rstd_k + 64;
-    float* sDbeta = sBeta + 64;
-    float* sHalf = sDbeta + 64;
-    float* sRed = sHalf + 128;
-    float* c1z = sHalf + 144;                      // [4][64] per-warp partial row sums
+    float* misc = sm + BG_MISC;
+    float* rstd_q = misc + MS_RSTDQ;
+    float* rstd_k = misc + MS_RSTDK;
+    float* sBeta = misc + MS_BETA;
+    float* sDbeta = misc + MS_DBETA;
+    float* sHalf = misc + MS_HALF;
+    float* sRed = misc + MS_RED;
+    float* pBeta = misc + MS_PBETA;
+    float* pGl = misc + MS_PGL;
+    float* sCol = misc + MS_COL;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g8 = lane >> 2, t4 = lane & 3;
     const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
     const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
     const size_t tile_idx = (size_t)c * p.H + h;
@@ -62,51 +97,70 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     const float* scr = p.scratch + tile_idx * (size_t)BWD_SCRATCH_FLOATS;
     const float gs_inv = p.gscale[1];
     const float alpha = p.gate_mode != GATE_NONE ? __expf(p.A_log[h]) : 0.f;
-
-    // ---- 1. gate activation (log2 domain) + cumulative sum; q, k rows; norms; beta ----
-    {
-        const int d = tid & 127, half = tid >> 7;
-        const float bias = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + d] : 0.f;
-        float run = 0.f;
-#pragma unroll 4
-        for (int r = 0; r < 32; ++r) {
-            const int row = half * 32 + r;
-            float a = 0.f;
-            if (row < ci.valid) {
-                const float x = bg_gate_raw(p.g, p.g_fp32, base + (size_t)row * tok_stride + d);
-                if (p.gate_mode == GATE_NONE) a = x;
-                else if (p.gate_mode == GATE_LOWER_BOUND) a = __fdividef(p.lower_bound, 1.f + __expf(-alpha * (x + bias)));
-                else { const float y = x + bias; a = -alpha * (y > 20.f ? y : log1pf(__expf(y))); }
-            }
-            run = fmaf(a, RCP_LN2, run);
-            sG[row * DK + d] = run;
-        }
-        if (half == 0) sHalf[d] = run;
-    }
-    for (int r = 0; r < 8; ++r) {
-        const int row = warp * 8 + r;
-        uint2 qr = make_uint2(0, 0), kr = make_uint2(0, 0);
-        if (row < ci.valid) {
-            qr = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + base + (size_t)row * tok_stride + lane * 4);
-            kr = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + base + (size_t)row * tok_stride + lane * 4);
-        }
-        *reinterpret_cast<uint2*>(sQ + row * DK + lane * 4) = qr;
-        *reinterpret_cast<uint2*>(sK + row * DK + lane * 4) = kr;
-        float rq = 1.f, rk = 1.f;
-        if (p.use_l2norm) {
-            float2 a = unpack_bf16(qr.x), b = unpack_bf16(qr.y);
-            float sq = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
-            a = unpack_bf16(kr.x); b = unpack_bf16(kr.y);
-            float sk = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+    const int pc = tid & 15;
+    float bias[8];
 #pragma unroll
-            for (int o = 16; o; o >>= 1) {
-                sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+    for (int e = 0; e < 8; ++e)
+        bias[e] = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] : 0.f;
+
+    // ---- 1a. wide loads: gate activation -> sG (log2 domain, zero for padding rows); q, k -> bf16 copies + norms ----
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+        const int row = (tid >> 4) + 16 * n;
+        const size_t off = base + (size_t)row * tok_stride + 4 * pc;
+        float gv[8];
+        uint2 q0 = make_uint2(0, 0), q1 = q0, k0 = q0, k1 = q0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) gv[e] = 0.f;
+        if (row < ci.valid) {
+            if (p.g_fp32) {
+                const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
+                const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
+                gv[0] = lo.x; gv[1] = lo.y; gv[2] = lo.z; gv[3] = lo.w; gv[4] = hi.x; gv[5] = hi.y; gv[6] = hi.z; gv[7] = hi.w;
+            } else {
+                const uint2 lo = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off);
+                const uint2 hi = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off + 64);
+                float2 f;
+                f = unpack_bf16(lo.x); gv[0] = f.x; gv[1] = f.y;
+                f = unpack_bf16(lo.y); gv[2] = f.x; gv[3] = f.y;
+                f = unpack_bf16(hi.x); gv[4] = f.x; gv[5] = f.y;
+                f = unpack_bf16(hi.y); gv[6] = f.x; gv[7] = f.y;
             }
-            rq = rsqrtf(sq + 1e-6f);
-            rk = rsqrtf(sk + 1e-6f);
+            q0 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off);
+            q1 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off + 64);
+            k0 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + off);
+            k1 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + off + 64);
         }
-        if (lane == 0) { rstd_q[row] = rq; rstd_k[row] = rk; }
+        float a[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            a[e] = (row < ci.valid) ? RCP_LN2 * bg_gate(gv[e], bias[e], alpha, p.gate_mode, p.lower_bound) : 0.f;
+        *reinterpret_cast<float4*>(sG + row * DK + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<float4*>(sG + row * DK + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
+        *reinterpret_cast<uint2*>(sQ + row * DK + 4 * pc) = q0;
+        *reinterpret_cast<uint2*>(sQ + row * DK + 64 + 4 * pc) = q1;
+        *reinterpret_cast<uint2*>(sK + row * DK + 4 * pc) = k0;
+        *reinterpret_cast<uint2*>(sK + row * DK + 64 + 4 * pc) = k1;
+        float sq = 0.f, sk = 0.f;
+        {
+            const uint32_t qw[4] = {q0.x, q0.y, q1.x, q1.y}, kw[4] = {k0.x, k0.y, k1.x, k1.y};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float2 f = unpack_bf16(qw[e]);
+                sq += f.x * f.x + f.y * f.y;
+                f = unpack_bf16(kw[e]);
+                sk += f.x * f.x + f.y * f.y;
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) {
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        }
+        if (pc == 0) {
+            rstd_q[row] = p.use_l2norm ? rsqrtf(sq + 1e-6f) : 1.f;
+            rstd_k[row] = p.use_l2norm ? rsqrtf(sk + 1e-6f) : 1.f;
+        }
     }
     if (tid < 64) {
         float b = 0.f;
@@ -118,243 +172,412 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         sBeta[tid] = b;
         sDbeta[tid] = scr[SCR_DBU + tid];
     }
+    if (tid < 128) sCol[tid] = 0.f;
     for (int i = tid; i < 64 * 16; i += BG_THREADS) {
         const int row = i >> 4, c4 = (i & 15) * 4;
-        *reinterpret_cast<float4*>(sA + row * AR + c4) = *reinterpret_cast<const float4*>(p.akk + tile_idx * 4096 + row * 64 + c4);
+        const float4 a = *reinterpret_cast<const float4*>(p.akk + tile_idx * 4096 + row * 64 + c4);
+        *reinterpret_cast<float4*>(sA + row * AR + c4) = make_float4(bg_tf32(a.x), bg_tf32(a.y), bg_tf32(a.z), bg_tf32(a.w));
     }
     __syncthreads();
-    if (tid >= 128) {
-        const int d = tid & 127;
-        const float t0 = sHalf[d];
+    // ---- 1b. cumulative sum down the rows (two halves per channel, then the second half adds the first's total) ----
+    {
+        const int d = tid & 127, half = tid >> 7;
+        float run = 0.f;
 #pragma unroll 8
-        for (int r = 32; r < 64; ++r) sG[r * DK + d] += t0;
+        for (int r = 0; r < 32; ++r) {
+            const int row = half * 32 + r;
+            run += sG[row * DK + d];
+            sG[row * DK + d] = run;
+        }
+        if (half == 0) sHalf[d] = run;
+        __syncthreads();
+        if (half == 1) {
+            const float t0 = sHalf[d];
+#pragma unroll 8
+            for (int r = 32; r < 64; ++r) sG[r * DK + d] += t0;
+        }
     }
     __syncthreads();
 
-    // ---- 2. stage dW (acc1) and X = beta k-hat 2^G (acc3) ----
+    // ---- 2. stage dW (acc1) and X = beta k-hat 2^G (acc3), both rounded to tf32 ----
     for (int i = tid; i < 64 * 32; i += BG_THREADS) {
         const int row = i >> 5, c4 = (i & 31) * 4;
-        *reinterpret_cast<float4*>(acc1 + row * DK + c4) = *reinterpret_cast<const float4*>(scr + SCR_DW + row * DK + c4);
+        const float4 w = *reinterpret_cast<const float4*>(scr + SCR_DW + row * DK + c4);
+        *reinterpret_cast<float4*>(acc1 + row * AS + c4) = make_float4(bg_tf32(w.x), bg_tf32(w.y), bg_tf32(w.z), bg_tf32(w.w));
         const float bk = sBeta[row] * rstd_k[row];
         float x[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) x[e] = bk * __bfloat162float(sK[row * DK + c4 + e]) * fast_exp2(sG[row * DK + c4 + e]);
-        *reinterpret_cast<float4*>(acc3 + row * DK + c4) = make_float4(x[0], x[1], x[2], x[3]);
+        for (int e = 0; e < 4; ++e)
+            x[e] = bg_tf32(bk * __bfloat162float(sK[row * DK + c4 + e]) * fast_exp2(sG[row * DK + c4 + e]));
+        *reinterpret_cast<float4*>(acc3 + row * AS + c4) = make_float4(x[0], x[1], x[2], x[3]);
     }
     __syncthreads();
 
-    // ---- 3. dA = dAu + stril(dW X^T) on the 136 lower-triangular 4x4 blocks -> c2 (zero elsewhere) ----
-    for (int i = tid; i < 64 * AR; i += BG_THREADS) c2[i] = 0.f;
-    __syncthreads();
-    if (tid < 136) {
-        int bi = (int)((sqrtf(8.f * tid + 1.f) - 1.f) * 0.5f);
-        while ((bi + 1) * (bi + 2) / 2 <= tid) ++bi;
-        while (bi * (bi + 1) / 2 > tid) --bi;
-        const int bj = tid - bi * (bi + 1) / 2;
-        float a[4][4];
-#pragma unroll
-        for (int x = 0; x < 4; ++x)
-#pragma unroll
-            for (int y = 0; y < 4; ++y) a[x][y] = 0.f;
-        for (int dd = 0; dd < DK; ++dd) {
-            const int d = (dd + lane) & (DK - 1);
-            float wv[4], xv[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                wv[x] = acc1[(4 * bi + x) * DK + d];
-                xv[x] = acc3[(4 * bj + x) * DK + d];
-            }
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-#pragma unroll
-                for (int y = 0; y < 4; ++y) a[x][y] = fmaf(wv[x], xv[y], a[x][y]);
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x)
-#pragma unroll
-            for (int y = 0; y < 4; ++y) {
-                const int i = 4 * bi + x, j = 4 * bj + y;
-                if (j < i) c2[i * AR + j] = a[x][y] + scr[SCR_DAU + i * BT + j];
-            }
-    }
-    __syncthreads();
-    // ---- 4. T1 = dA A^T -> c1 ;  dL = -stril(A^T T1) -> c2 (then scaled by beta_i into cR) ----
-    {
-        const int i = tid >> 2, m0 = (tid & 3) * 16;
-        float t1[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) t1[e] = 0.f;
-        for (int j = 0; j < i; ++j) {
-            const float dv = c2[i * AR + j];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) t1[e] = fmaf(dv, sA[(m0 + e) * AR + j], t1[e]);     // A[m][j] = 0 for j > m
-        }
-#pragma unroll
-        for (int e = 0; e < 16; ++e) c1[i * AR + m0 + e] = t1[e];
-    }
-    __syncthreads();
-    {
-        const int i = tid >> 2, j0 = (tid & 3) * 16;
-        float dl[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) dl[e] = 0.f;
-        for (int mm = i; mm < 64; ++mm) {                 // A[mm][i] = 0 for mm < i
-            const float av = sA[mm * AR + i];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) dl[e] = fmaf(av, c1[mm * AR + j0 + e], dl[e]);
-        }
-        __syncthreads();                                   // everyone is done reading dA (c2) and T1 (c1)
-        float dbl = 0.f;
-        const float bi = sBeta[i];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const int j = j0 + e;
-            const float v = (j < i) ? -dl[e] : 0.f;
-            if (j < i) dbl = fmaf(v, p.mkk[tile_idx * 4096 + i * BT + j], dbl);
-            c2[i * AR + j] = bi * v;                       // cR
-        }
-        dbl += __shfl_xor_sync(0xffffffffu, dbl, 1);
-        dbl += __shfl_xor_sync(0xffffffffu, dbl, 2);
-        if ((tid & 3) == 0) sDbeta[i] += dbl;
-        // cP = scale * dPs
-        for (int x = tid; x < 64 * 16; x += BG_THREADS) {
-            const int row = x >> 4, c4 = (x & 15) * 4;
-            const float4 v = *reinterpret_cast<const float4*>(scr + SCR_DPS + row * BT + c4);
-            *reinterpret_cast<float4*>(c1 + row * AR + c4) = make_float4(p.scale * v.x, p.scale * v.y, p.scale * v.z, p.scale * v.w);
-        }
-    }
-    __syncthreads();
+    const int mt = warp & 3, nh = warp >> 2;     // 16-row tile and column half of this warp in the GEMM phases
+    const int r0 = 16 * mt + g8, r1 = r0 + 8;
 
-    // ---- 5. per key channel d (threads 0..127): Zw = A^T dW, accumulator initialisation ----
-    if (tid < 128) {
-        const int d = tid;
-        float dw[64];
-#pragma unroll
-        for (int mm = 0; mm < 64; ++mm) dw[mm] = acc1[mm * DK + d];
-        const float glast = sG[63 * DK + d];
-        float dgl = fast_exp2(glast) * scr[SCR_DD + d];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-            float zw = 0.f;
-#pragma unroll
-            for (int mm = i; mm < 64; ++mm) zw = fmaf(sA[mm * AR + i], dw[mm], zw);
-            const float gi = sG[i * DK + d];
-            const float eg = fast_exp2(gi), ekg = fast_exp2(glast - gi);
-            const float qh = __bfloat162float(sQ[i * DK + d]) * rstd_q[i], kh = __bfloat162float(sK[i * DK + d]) * rstd_k[i];
-            const float dqg = scr[SCR_DQG + i * DK + d], dkg = scr[SCR_DKG + i * DK + d];
-            const float dkp = sBeta[i] * zw, kplus = kh * eg, kgv = kh * ekg, qgv = p.scale * qh * eg;
-            acc1[i * DK + d] = p.scale * dqg * eg;                         // dq-hat
-            acc2[i * DK + d] = dkp * eg + dkg * ekg;                       // dk-hat
-            float dG = dqg * qgv + dkp * kplus - dkg * kgv;
-            dgl = fmaf(dkg, kgv, dgl);
-            // rowsum(Zw * K+) for dbeta: reduce over the 128 channel threads via warp shuffles + shared atomics
-            float zb = zw * kplus;
-#pragma unroll
-            for (int o = 16; o; o >>= 1) zb += __shfl_xor_sync(0xffffffffu, zb, o);
-            if (lane == 0) c1z[warp * 64 + i] = zb;          // per-warp partials, summed in a fixed order below
-            acc3[i * DK + d] = dG;
-        }
-        acc3[63 * DK + d] += dgl;
-    }
-    __syncthreads();
-    if (tid < 64) sDbeta[tid] += (c1z[tid] + c1z[64 + tid]) + (c1z[128 + tid] + c1z[192 + tid]);
-
-    // ---- 6. pairwise gated VJPs. Thread (d, par): channel d, rows of parity par inside every 16x16 block ----
+    // ---- 3. dA = dAu + stril(dW X^T) -> c2 (zero on and above the diagonal) ----
     {
-        const int d = tid & 127, par = tid >> 7;
-#pragma unroll 1
-        for (int blk = 0; blk < 10; ++blk) {
-            // lower-triangular block list (I, J), J <= I
-            const int I = (blk < 1) ? 0 : (blk < 3) ? 1 : (blk < 6) ? 2 : 3;
-            const int J = blk - (I * (I + 1)) / 2;
-            float kj[16], gj[16], aj[16];
+        float acc[4][4];
 #pragma unroll
-            for (int y = 0; y < 16; ++y) {
-                kj[y] = __bfloat162float(sK[(16 * J + y) * DK + d]) * rstd_k[16 * J + y];
-                gj[y] = sG[(16 * J + y) * DK + d];
-                aj[y] = 0.f;
-            }
-#pragma unroll 1
-            for (int x = par; x < 16; x += 2) {
-                const int i = 16 * I + x;
-                const float gi = sG[i * DK + d];
-                const float qi = __bfloat162float(sQ[i * DK + d]) * rstd_q[i], ki = __bfloat162float(sK[i * DK + d]) * rstd_k[i];
-                float aq = 0.f, ar = 0.f;
+        for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        if (32 * nh <= 16 * mt + 15) {
+#pragma unroll 4
+            for (int ks = 0; ks < 16; ++ks) {
+                const int k0 = 8 * ks;
+                const float fa[4] = {acc1[r0 * AS + k0 + t4], acc1[r1 * AS + k0 + t4], acc1[r0 * AS + k0 + t4 + 4], acc1[r1 * AS + k0 + t4 + 4]};
 #pragma unroll
-                for (int y4 = 0; y4 < 4; ++y4) {
-                    const float4 cp4 = *reinterpret_cast<const float4*>(c1 + i * AR + 16 * J + 4 * y4);
-                    const float4 cr4 = *reinterpret_cast<const float4*>(c2 + i * AR + 16 * J + 4 * y4);
-                    const float cp[4] = {cp4.x, cp4.y, cp4.z, cp4.w}, cr[4] = {cr4.x, cr4.y, cr4.z, cr4.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int y = 4 * y4 + e;
-                        // entries with j > i carry zero coefficients; the exponent clamp keeps them finite
-                        const float E = fast_exp2(fminf(gi - gj[y], 0.f));
-                        const float t1 = E * kj[y];
-                        aq = fmaf(cp[e], t1, aq);
-                        ar = fmaf(cr[e], t1, ar);
-                        aj[y] = fmaf(E, fmaf(cp[e], qi, cr[e] * ki), aj[y]);
-                    }
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int j = 32 * nh + 8 * nt + g8;
+                    bg_mma(acc[nt], fa, acc3[j * AS + k0 + t4], acc3[j * AS + k0 + t4 + 4]);
                 }
-                acc1[i * DK + d] += aq;
-                acc2[i * DK + d] += ar;
-                acc3[i * DK + d] += qi * aq + ki * ar;
             }
-            __syncthreads();       // row updates of this block are visible before the column updates below
-            // the two row-parity threads of a channel add their column sums one after the other: fixed order,
-            // so the result does not depend on scheduling
-#pragma unroll 1
-            for (int turn = 0; turn < 2; ++turn) {
-                if (par == turn) {
+        }
 #pragma unroll
-                    for (int y = 0; y < 16; ++y) {
-                        acc2[(16 * J + y) * DK + d] += aj[y];
-                        acc3[(16 * J + y) * DK + d] -= kj[y] * aj[y];
-                    }
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = 32 * nh + 8 * nt + 2 * t4;
+            const float2 u0 = *reinterpret_cast<const float2*>(scr + SCR_DAU + r0 * BT + col);
+            const float2 u1 = *reinterpret_cast<const float2*>(scr + SCR_DAU + r1 * BT + col);
+            c2[r0 * AR + col] = (col < r0) ? bg_tf32(acc[nt][0] + u0.x) : 0.f;
+            c2[r0 * AR + col + 1] = (col + 1 < r0) ? bg_tf32(acc[nt][1] + u0.y) : 0.f;
+            c2[r1 * AR + col] = (col < r1) ? bg_tf32(acc[nt][2] + u1.x) : 0.f;
+            c2[r1 * AR + col + 1] = (col + 1 < r1) ? bg_tf32(acc[nt][3] + u1.y) : 0.f;
+        }
+    }
+    __syncthreads();
+    // ---- 4a. T1 = dA A^T -> c1 ----
+    {
+        float acc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        for (int ks = 0; ks < 2 * mt + 2; ++ks) {          // dA[i][j] = 0 for j >= i: later k-steps contribute nothing
+            const int k0 = 8 * ks;
+            const float fa[4] = {c2[r0 * AR + k0 + t4], c2[r1 * AR + k0 + t4], c2[r0 * AR + k0 + t4 + 4], c2[r1 * AR + k0 + t4 + 4]};
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int mm = 32 * nh + 8 * nt + g8;
+                bg_mma(acc[nt], fa, sA[mm * AR + k0 + t4], sA[mm * AR + k0 + t4 + 4]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = 32 * nh + 8 * nt + 2 * t4;
+            c1[r0 * AR + col] = bg_tf32(acc[nt][0]);
+            c1[r0 * AR + col + 1] = bg_tf32(acc[nt][1]);
+            c1[r1 * AR + col] = bg_tf32(acc[nt][2]);
+            c1[r1 * AR + col + 1] = bg_tf32(acc[nt][3]);
+        }
+    }
+    __syncthreads();
+    // ---- 4b. dL = -stril(A^T T1); dbeta += rowsum(dL * M); cR = beta_i dL -> c2 ----
+    {
+        float acc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        for (int ks = 2 * mt; ks < 8; ++ks) {              // A[m][i] = 0 for m < i
+            const int k0 = 8 * ks;
+            const float fa[4] = {sA[(k0 + t4) * AR + r0], sA[(k0 + t4) * AR + r1], sA[(k0 + t4 + 4) * AR + r0], sA[(k0 + t4 + 4) * AR + r1]};
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int j = 32 * nh + 8 * nt + g8;
+                bg_mma(acc[nt], fa, c1[(k0 + t4) * AR + j], c1[(k0 + t4 + 4) * AR + j]);
+            }
+        }
+        const float b0 = sBeta[r0], b1 = sBeta[r1];
+        const float* mk = p.mkk + tile_idx * 4096;
+        float db0 = 0.f, db1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = 32 * nh + 8 * nt + 2 * t4;
+            const float2 m0 = *reinterpret_cast<const float2*>(mk + r0 * BT + col);
+            const float2 m1 = *reinterpret_cast<const float2*>(mk + r1 * BT + col);
+            const float v00 = (col < r0) ? -acc[nt][0] : 0.f, v01 = (col + 1 < r0) ? -acc[nt][1] : 0.f;
+            const float v10 = (col < r1) ? -acc[nt][2] : 0.f, v11 = (col + 1 < r1) ? -acc[nt][3] : 0.f;
+            db0 += v00 * m0.x + v01 * m0.y;
+            db1 += v10 * m1.x + v11 * m1.y;
+            c2[r0 * AR + col] = bg_tf32(b0 * v00);
+            c2[r0 * AR + col + 1] = bg_tf32(b0 * v01);
+            c2[r1 * AR + col] = bg_tf32(b1 * v10);
+            c2[r1 * AR + col + 1] = bg_tf32(b1 * v11);
+        }
+        db0 += __shfl_xor_sync(0xffffffffu, db0, 1); db0 += __shfl_xor_sync(0xffffffffu, db0, 2);
+        db1 += __shfl_xor_sync(0xffffffffu, db1, 1); db1 += __shfl_xor_sync(0xffffffffu, db1, 2);
+        if (t4 == 0) {
+            pBeta[nh * 64 + r0] = db0;
+            pBeta[nh * 64 + r1] = db1;
+        }
+    }
+    __syncthreads();
+    if (tid < 64) sDbeta[tid] += pBeta[tid] + pBeta[64 + tid];
+    for (int x = tid; x < 64 * 16; x += BG_THREADS) {      // cP = scale * dPs -> c1 (T1 is no longer needed)
+        const int row = x >> 4, c4 = (x & 15) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(scr + SCR_DPS + row * BT + c4);
+        *reinterpret_cast<float4*>(c1 + row * AR + c4) =
+            make_float4(bg_tf32(p.scale * v.x), bg_tf32(p.scale * v.y), bg_tf32(p.scale * v.z), bg_tf32(p.scale * v.w));
+    }
+
+    // ---- 5. Zw = A^T dW (gradient w.r.t. X); initial values of the dq-hat, dk-hat and dG accumulators ----
+    {
+        float zw[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) zw[nt][0] = zw[nt][1] = zw[nt][2] = zw[nt][3] = 0.f;
+        for (int ks = 2 * mt; ks < 8; ++ks) {
+            const int k0 = 8 * ks;
+            const float fa[4] = {sA[(k0 + t4) * AR + r0], sA[(k0 + t4) * AR + r1], sA[(k0 + t4 + 4) * AR + r0], sA[(k0 + t4 + 4) * AR + r1]};
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const int d = 64 * nh + 8 * nt + g8;
+                bg_mma(zw[nt], fa, acc1[(k0 + t4) * AS + d], acc1[(k0 + t4 + 4) * AS + d]);
+            }
+        }
+        __syncthreads();                                   // every warp has finished reading dW from acc1
+        const float bb[2] = {sBeta[r0], sBeta[r1]};
+        const float rq[2] = {rstd_q[r0], rstd_q[r1]}, rk[2] = {rstd_k[r0], rstd_k[r1]};
+        float dbw[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int col = 64 * nh + 8 * nt + 2 * t4;
+            const float2 gl = *reinterpret_cast<const float2*>(sG + 63 * DK + col);
+            float cs0 = 0.f, cs1 = 0.f;                    // column sums of dKg * Kg over this thread's two rows
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = rr ? r1 : r0;
+                const float2 gi = *reinterpret_cast<const float2*>(sG + row * DK + col);
+                const float2 dqg = *reinterpret_cast<const float2*>(scr + SCR_DQG + row * DK + col);
+                const float2 dkg = *reinterpret_cast<const float2*>(scr + SCR_DKG + row * DK + col);
+                const float2 qf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + row * DK + col));
+                const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * DK + col));
+                const float gg[2] = {gi.x, gi.y}, gls[2] = {gl.x, gl.y}, dq2[2] = {dqg.x, dqg.y}, dk2[2] = {dkg.x, dkg.y};
+                const float qh[2] = {qf.x * rq[rr], qf.y * rq[rr]}, kh[2] = {kf.x * rk[rr], kf.y * rk[rr]};
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float z = zw[nt][2 * rr + e];
+                    const float eg = fast_exp2(gg[e]), ekg = fast_exp2(gls[e] - gg[e]);
+                    const float dkp = bb[rr] * z, kplus = kh[e] * eg, kgv = kh[e] * ekg, qgv = p.scale * qh[e] * eg;
+                    acc1[row * AS + col + e] = p.scale * dq2[e] * eg;
+                    acc2[row * AS + col + e] = dkp * eg + dk2[e] * ekg;
+                    acc3[row * AS + col + e] = dq2[e] * qgv + dkp * kplus - dk2[e] * kgv;
+                    dbw[rr] = fmaf(z, kplus, dbw[rr]);
+                    if (e == 0) cs0 = fmaf(dk2[e], kgv, cs0); else cs1 = fmaf(dk2[e], kgv, cs1);
                 }
-                __syncthreads();
+            }
+            // sum over the 8 row pairs of this warp (lanes with equal t4): columns col, col+1
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                cs0 += __shfl_xor_sync(0xffffffffu, cs0, o);
+                cs1 += __shfl_xor_sync(0xffffffffu, cs1, o);
+            }
+            if (g8 == 0) {
+                pGl[mt * 128 + col] = cs0;
+                pGl[mt * 128 + col + 1] = cs1;
+            }
+        }
+        dbw[0] += __shfl_xor_sync(0xffffffffu, dbw[0], 1); dbw[0] += __shfl_xor_sync(0xffffffffu, dbw[0], 2);
+        dbw[1] += __shfl_xor_sync(0xffffffffu, dbw[1], 1); dbw[1] += __shfl_xor_sync(0xffffffffu, dbw[1], 2);
+        if (t4 == 0) {
+            pBeta[nh * 64 + r0] = dbw[0];
+            pBeta[nh * 64 + r1] = dbw[1];
+        }
+    }
+    __syncthreads();
+    if (tid < 64) sDbeta[tid] += pBeta[tid] + pBeta[64 + tid];
+    if (tid < 128) {   // g_last sits in row 63 (padding rows repeat the last real value): fold its gradient in there
+        const float dgl = (pGl[tid] + pGl[128 + tid]) + (pGl[256 + tid] + pGl[384 + tid]) +
+                          fast_exp2(sG[63 * DK + tid]) * scr[SCR_DD + tid];
+        acc3[63 * AS + tid] += dgl;
+    }
+    __syncthreads();
+
+    // ---- 6. VJPs of the gated Gram matrices. Warp w owns key channels 16w..16w+15 for all 64 rows; the same
+    //         thread owns the same (row, channel) cells in the row-side and column-side updates: no synchronisation ----
+    {
+        const int dB0 = 16 * warp + g8;                   // channel of this lane's B-fragment column (n-tile 0; +8 for n-tile 1)
+#pragma unroll 1
+        for (int I = 0; I < 4; ++I) {                     // row side: rows of block I against columns j < 16(I+1)
+            float accP[2][4], accR[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) accP[nt][e] = accR[nt][e] = 0.f;
+            const int i0 = 16 * I + g8, i1 = i0 + 8;
+            const float rI0 = sG[16 * I * DK + dB0], rI1 = sG[16 * I * DK + dB0 + 8];
+            for (int ks = 0; ks < 2 * I + 2; ++ks) {
+                const int j0 = 8 * ks + t4, j1 = j0 + 4;
+                const float aP[4] = {c1[i0 * AR + j0], c1[i1 * AR + j0], c1[i0 * AR + j1], c1[i1 * AR + j1]};
+                const float aR[4] = {c2[i0 * AR + j0], c2[i1 * AR + j0], c2[i0 * AR + j1], c2[i1 * AR + j1]};
+                const float k0s = rstd_k[j0], k1s = rstd_k[j1];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int d = dB0 + 8 * nt;
+                    const float rI = nt ? rI1 : rI0;
+                    const float b0 = __bfloat162float(sK[j0 * DK + d]) * k0s * fast_exp2(fminf(rI - sG[j0 * DK + d], 120.f));
+                    const float b1 = __bfloat162float(sK[j1 * DK + d]) * k1s * fast_exp2(fminf(rI - sG[j1 * DK + d], 120.f));
+                    const float h0 = bg_tf32(b0), h1 = bg_tf32(b1), l0 = bg_tf32(b0 - h0), l1 = bg_tf32(b1 - h1);
+                    bg_mma(accP[nt], aP, l0, l1);
+                    bg_mma(accP[nt], aP, h0, h1);
+                    bg_mma(accR[nt], aR, l0, l1);
+                    bg_mma(accR[nt], aR, h0, h1);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int col = 16 * warp + 8 * nt + 2 * t4;
+                const float2 rI = *reinterpret_cast<const float2*>(sG + 16 * I * DK + col);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int row = rr ? i1 : i0;
+                    const float2 gi = *reinterpret_cast<const float2*>(sG + row * DK + col);
+                    const float2 qf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + row * DK + col));
+                    const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * DK + col));
+                    const float f0 = fast_exp2(gi.x - rI.x), f1 = fast_exp2(gi.y - rI.y);
+                    const float dq0 = f0 * accP[nt][2 * rr], dq1 = f1 * accP[nt][2 * rr + 1];
+                    const float dk0 = f0 * accR[nt][2 * rr], dk1 = f1 * accR[nt][2 * rr + 1];
+                    acc1[row * AS + col] += dq0;
+                    acc1[row * AS + col + 1] += dq1;
+                    acc2[row * AS + col] += dk0;
+                    acc2[row * AS + col + 1] += dk1;
+                    acc3[row * AS + col] += rstd_q[row] * qf.x * dq0 + rstd_k[row] * kf.x * dk0;
+                    acc3[row * AS + col + 1] += rstd_q[row] * qf.y * dq1 + rstd_k[row] * kf.y * dk1;
+                }
+            }
+        }
+#pragma unroll 1
+        for (int J = 0; J < 4; ++J) {                     // column side: columns of block J against rows i >= 16J
+            float accC[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) accC[nt][e] = 0.f;
+            const int jc0 = 16 * J + g8, jc1 = jc0 + 8;
+            const float sJ0 = sG[(16 * J + 15) * DK + dB0], sJ1 = sG[(16 * J + 15) * DK + dB0 + 8];
+            for (int ks = 2 * J; ks < 8; ++ks) {
+                const int ia = 8 * ks + t4, ib = ia + 4;
+                const float aP[4] = {c1[ia * AR + jc0], c1[ia * AR + jc1], c1[ib * AR + jc0], c1[ib * AR + jc1]};
+                const float aR[4] = {c2[ia * AR + jc0], c2[ia * AR + jc1], c2[ib * AR + jc0], c2[ib * AR + jc1]};
+                const float qa = rstd_q[ia], qb = rstd_q[ib], ka = rstd_k[ia], kb = rstd_k[ib];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int d = dB0 + 8 * nt;
+                    const float sJ = nt ? sJ1 : sJ0;
+                    const float ea = fast_exp2(fminf(sG[ia * DK + d] - sJ, 120.f)), eb = fast_exp2(fminf(sG[ib * DK + d] - sJ, 120.f));
+                    bg_mma_split(accC[nt], aP, __bfloat162float(sQ[ia * DK + d]) * qa * ea, __bfloat162float(sQ[ib * DK + d]) * qb * eb);
+                    bg_mma_split(accC[nt], aR, __bfloat162float(sK[ia * DK + d]) * ka * ea, __bfloat162float(sK[ib * DK + d]) * kb * eb);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int col = 16 * warp + 8 * nt + 2 * t4;
+                const float2 sJ = *reinterpret_cast<const float2*>(sG + (16 * J + 15) * DK + col);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int row = rr ? jc1 : jc0;
+                    const float2 gj = *reinterpret_cast<const float2*>(sG + row * DK + col);
+                    const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * DK + col));
+                    const float d0 = fast_exp2(sJ.x - gj.x) * accC[nt][2 * rr], d1 = fast_exp2(sJ.y - gj.y) * accC[nt][2 * rr + 1];
+                    acc2[row * AS + col] += d0;
+                    acc2[row * AS + col + 1] += d1;
+                    acc3[row * AS + col] -= rstd_k[row] * kf.x * d0;
+                    acc3[row * AS + col + 1] -= rstd_k[row] * kf.y * d1;
+                }
             }
         }
     }
+    __syncthreads();
 
-    // ---- 7. reverse cumulative sum of dG down the rows, gate VJP, dg / dA_log / d dt_bias ----
+    // ---- 7a. reverse cumulative sum of dG down the rows, in place (two halves per channel) ----
+    {
+        const int d = tid & 127, half = tid >> 7;
+        float run = 0.f;
+#pragma unroll 8
+        for (int r = 31; r >= 0; --r) {
+            const int row = half * 32 + r;
+            run += acc3[row * AS + d];
+            acc3[row * AS + d] = run;
+        }
+        if (half == 1) sHalf[d] = run;
+        __syncthreads();
+        if (half == 0) {
+            const float t1 = sHalf[d];
+#pragma unroll 8
+            for (int r = 0; r < 32; ++r) acc3[r * AS + d] += t1;
+        }
+    }
+    __syncthreads();
+    // ---- 7b. gate VJP with wide accesses: dg, per-channel sums for d dt_bias, the A_log sum ----
     float dA_part = 0.f;
-    if (tid < 128) {
-        const int d = tid;
-        const float bias = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + d] : 0.f;
-        float run = 0.f, dbias = 0.f;
-        for (int i = 63; i >= 0; --i) {
-            run += acc3[i * DK + d];
-            if (i < ci.valid) {
-                const size_t gi = base + (size_t)i * tok_stride + d;
-                const float da = run * gs_inv;          // gradient w.r.t. the natural-log decay a_i[d]
-                float dx = da;
-                if (p.gate_mode != GATE_NONE) {
-                    const float x = bg_gate_raw(p.g, p.g_fp32, gi) + bias;
-                    if (p.gate_mode == GATE_LOWER_BOUND) {
-                        const float sg = __fdividef(1.f, 1.f + __expf(-alpha * x));
-                        dx = da * p.lower_bound * sg * (1.f - sg) * alpha;
-                        dA_part = fmaf(dx, x, dA_part);
-                    } else {
-                        const float sg = __fdividef(1.f, 1.f + __expf(-x));
-                        const float sp = x > 20.f ? x : log1pf(__expf(x));
-                        dx = -da * alpha * sg;
-                        dA_part = fmaf(da, -alpha * sp, dA_part);
-                    }
-                    dbias += dx;
+    {
+        float colsum[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) colsum[e] = 0.f;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int row = (tid >> 4) + 16 * n;
+            if (row >= ci.valid) continue;
+            const size_t off = base + (size_t)row * tok_stride + 4 * pc;
+            float gv[8], dx[8];
+            if (p.g_fp32) {
+                const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
+                const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
+                gv[0] = lo.x; gv[1] = lo.y; gv[2] = lo.z; gv[3] = lo.w; gv[4] = hi.x; gv[5] = hi.y; gv[6] = hi.z; gv[7] = hi.w;
+            } else {
+                const uint2 lo = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off);
+                const uint2 hi = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off + 64);
+                float2 f;
+                f = unpack_bf16(lo.x); gv[0] = f.x; gv[1] = f.y;
+                f = unpack_bf16(lo.y); gv[2] = f.x; gv[3] = f.y;
+                f = unpack_bf16(hi.x); gv[4] = f.x; gv[5] = f.y;
+                f = unpack_bf16(hi.y); gv[6] = f.x; gv[7] = f.y;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int d = 64 * (e >> 2) + 4 * pc + (e & 3);
+                const float da = acc3[row * AS + d] * gs_inv;       // gradient w.r.t. the natural-log decay a_row[d]
+                float v = da;
+                if (p.gate_mode == GATE_LOWER_BOUND) {
+                    const float x = gv[e] + bias[e];
+                    const float sg = fast_rcp(1.f + fast_exp2(-alpha * RCP_LN2 * x));
+                    v = da * p.lower_bound * sg * (1.f - sg) * alpha;
+                    dA_part = fmaf(v, x, dA_part);
+                    colsum[e] += v;
+                } else if (p.gate_mode == GATE_SOFTPLUS) {
+                    const float x = gv[e] + bias[e];
+                    const float sg = __fdividef(1.f, 1.f + __expf(-x));
+                    const float sp = x > 20.f ? x : log1pf(__expf(x));
+                    v = -da * alpha * sg;
+                    dA_part = fmaf(da, -alpha * sp, dA_part);
+                    colsum[e] += v;
                 }
-                if (p.g_fp32) reinterpret_cast<float*>(p.dg)[gi] = dx;
-                else reinterpret_cast<__nv_bfloat16*>(p.dg)[gi] = __float2bfloat16_rn(dx);
+                dx[e] = v;
+            }
+            if (p.g_fp32) {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dg) + off) = make_float4(dx[0], dx[1], dx[2], dx[3]);
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dg) + off + 64) = make_float4(dx[4], dx[5], dx[6], dx[7]);
+            } else {
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.dg) + off) =
+                    make_uint2(pack_bf16(dx[0], dx[1]), pack_bf16(dx[2], dx[3]));
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.dg) + off + 64) =
+                    make_uint2(pack_bf16(dx[4], dx[5]), pack_bf16(dx[6], dx[7]));
             }
         }
-        if (p.gate_mode != GATE_NONE && p.ddt_bias) atomicAdd(&p.ddt_bias[h * DK + d], dbias);
+        if (p.gate_mode != GATE_NONE && p.ddt_bias) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                // lanes l and l+16 hold the same channels: combine them, then one shared-memory atomic per channel and warp
+                float v = colsum[e] + __shfl_xor_sync(0xffffffffu, colsum[e], 16);
+                if (lane < 16) atomicAdd(&sCol[64 * (e >> 2) + 4 * pc + (e & 3)], v);
+            }
+        }
     }
     if (p.gate_mode != GATE_NONE && p.dA_log) {
 #pragma unroll
         for (int o = 16; o; o >>= 1) dA_part += __shfl_xor_sync(0xffffffffu, dA_part, o);
         if (lane == 0) sRed[warp] = dA_part;
-        __syncthreads();
-        if (tid == 0) atomicAdd(&p.dA_log[h], sRed[0] + sRed[1] + sRed[2] + sRed[3]);
+    }
+    __syncthreads();
+    if (p.gate_mode != GATE_NONE) {
+        if (p.ddt_bias && tid < 128) atomicAdd(&p.ddt_bias[h * DK + tid], sCol[tid]);
+        if (p.dA_log && tid == 0)
+            atomicAdd(&p.dA_log[h], ((sRed[0] + sRed[1]) + (sRed[2] + sRed[3])) + ((sRed[4] + sRed[5]) + (sRed[6] + sRed[7])));
     }
 
     // ---- 8. L2-norm VJP and stores of dq, dk (a warp per row); dbeta ----
@@ -363,13 +586,19 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         if (row >= ci.valid) continue;
         float dq[4], dk[4], qh[4], kh[4];
         float sq = 0.f, sk = 0.f;
+        const float4 a1 = *reinterpret_cast<const float4*>(acc1 + row * AS + lane * 4);
+        const float4 a2 = *reinterpret_cast<const float4*>(acc2 + row * AS + lane * 4);
+        const uint2 qr = *reinterpret_cast<const uint2*>(sQ + row * DK + lane * 4);
+        const uint2 kr = *reinterpret_cast<const uint2*>(sK + row * DK + lane * 4);
+        dq[0] = a1.x * gs_inv; dq[1] = a1.y * gs_inv; dq[2] = a1.z * gs_inv; dq[3] = a1.w * gs_inv;
+        dk[0] = a2.x * gs_inv; dk[1] = a2.y * gs_inv; dk[2] = a2.z * gs_inv; dk[3] = a2.w * gs_inv;
+        float2 f;
+        f = unpack_bf16(qr.x); qh[0] = f.x * rstd_q[row]; qh[1] = f.y * rstd_q[row];
+        f = unpack_bf16(qr.y); qh[2] = f.x * rstd_q[row]; qh[3] = f.y * rstd_q[row];
+        f = unpack_bf16(kr.x); kh[0] = f.x * rstd_k[row]; kh[1] = f.y * rstd_k[row];
+        f = unpack_bf16(kr.y); kh[2] = f.x * rstd_k[row]; kh[3] = f.y * rstd_k[row];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int d = lane * 4 + e;
-            dq[e] = acc1[row * DK + d] * gs_inv;
-            dk[e] = acc2[row * DK + d] * gs_inv;
-            qh[e] = __bfloat162float(sQ[row * DK + d]) * rstd_q[row];
-            kh[e] = __bfloat162float(sK[row * DK + d]) * rstd_k[row];
             sq = fmaf(dq[e], qh[e], sq);
             sk = fmaf(dk[e], kh[e], sk);
         }
@@ -401,6 +630,7 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
 
 extern "C" int kda_launch_bwd_gated(const kda::BwdGatedParams* p, int num_chunks, cudaStream_t stream) {
     using namespace kda;
+    static_assert(BG_SMEM <= 227 * 1024, "shared memory budget");
     if (num_chunks <= 0) return 0;
     cudaError_t e = cudaFuncSetAttribute(kda_bwd_gated_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BG_SMEM);
     if (e != cudaSuccess) return (int)e;
