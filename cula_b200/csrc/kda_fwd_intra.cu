@@ -26,7 +26,12 @@
 
 namespace kda {
 
-constexpr int INTRA_THREADS = 256;
+constexpr int INTRA_THREADS = 256;              // 256 or 512 (the thread mappings below follow it)
+constexpr int NWARPS = INTRA_THREADS / 32;
+constexpr int RS = 512 / INTRA_THREADS;          // 64-row slots per thread in the (row, 8-lane) mapping
+constexpr int RSTEP = INTRA_THREADS / 8;         // row distance between a thread's slots
+constexpr int NIT = 1024 / INTRA_THREADS;        // (row, 16-lane) items per thread
+constexpr int NPART = INTRA_THREADS / 128;       // row segments of the column scan
 
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr int SM_OPA = 0;                 // A operand of one 64-channel half: [2 k-atoms][128 rows][128 B], SW128
@@ -34,7 +39,7 @@ constexpr int SM_OPB = 32768;             // B operand: [2 k-atoms][160 rows][12
 constexpr int SM_G = 73728;               // G [64][128] fp32
 constexpr int SM_TAB = 106496;            // 10 x [128] fp32 anchor tables
 constexpr int SM_MISC = 111616;           // beta[64], barriers, tmem base, half totals
-constexpr int SM_TOTAL = 112640;
+constexpr int SM_TOTAL = 113664;
 constexpr int KATOM_A = 16384, KATOM_B = 20480;
 // regions reused once the Gram MMAs have completed
 constexpr int SM_XS = SM_OPA;             // X = beta k 2^g, fp16 [2 mn-atoms][64 tokens][128 B], SW128 (MN-major A operand)
@@ -66,7 +71,8 @@ __device__ __forceinline__ float load_gate_raw(const void* g, int g_fp32, size_t
     return g_fp32 ? reinterpret_cast<const float*>(g)[idx]
                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g)[idx]);
 }
-__device__ __forceinline__ float gate_activation(float graw, float alpha, float bias, int gate_mode, float lower_bound) {
+// kept out of line: it is instantiated per element group and the softplus path is long (instruction-cache footprint)
+__device__ __noinline__ float gate_activation(float graw, float alpha, float bias, int gate_mode, float lower_bound) {
     if (gate_mode == GATE_NONE) return graw;
     float x = graw + bias;
     if (gate_mode == GATE_LOWER_BOUND) return __fdividef(lower_bound, 1.f + __expf(-alpha * x));
@@ -86,7 +92,7 @@ __device__ __forceinline__ void mma_tf32_16x8x8(float (&d)[4], const uint32_t (&
 }
 template <int KT>
 __device__ __forceinline__ void mma_tile_3xtf32(const float* A, int lda, const float* B, int ldb, float (&acc)[4], int g, int t) {
-#pragma unroll
+#pragma unroll 1
     for (int ks = 0; ks < KT; ++ks) {
         const float af[4] = {A[g * lda + 8 * ks + t], A[(g + 8) * lda + 8 * ks + t], A[g * lda + 8 * ks + t + 4],
                              A[(g + 8) * lda + 8 * ks + t + 4]};
@@ -111,7 +117,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     float* sBeta = reinterpret_cast<float*>(sm + SM_MISC);
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SM_MISC + 256);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + SM_MISC + 288);
-    float* sHalf = reinterpret_cast<float*>(sm + SM_MISC + 512);
+    float* sHalf = reinterpret_cast<float*>(sm + SM_MISC + 512);      // [NPART][128] segment totals
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t tok_stride = (size_t)p.H * DK;
@@ -139,13 +145,13 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 
     // q, k rows of this tile into registers first, so their latency hides behind the gate pass.
     // Thread (rq, l8): rows rq and rq+32, channels 32*grp + 4*l8 .. +3 for the four channel groups grp.
-    uint2 qraw[2][4], kraw[2][4];
+    uint2 qraw[RS][4], kraw[RS][4];
     {
         const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q);
         const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(p.k);
 #pragma unroll
-        for (int rs = 0; rs < 2; ++rs) {
-            const int row = rq + 32 * rs;
+        for (int rs = 0; rs < RS; ++rs) {
+            const int row = rq + RSTEP * rs;
 #pragma unroll
             for (int grp = 0; grp < 4; ++grp) {
                 uint2 qv = make_uint2(0, 0), kv = make_uint2(0, 0);
@@ -159,7 +165,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             }
         }
     }
-    {   // pull this tile's v rows and the next tile's inputs towards L2 (two 128-byte lines per row)
+    if (tid < 256) {   // pull this tile's v rows and the next tile's inputs towards L2 (two 128-byte lines per row)
         const int row = tid >> 2, part = tid & 3;
         if (part < 2 && row < ci.valid)
             prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.v) + base + (size_t)row * tok_stride + 64 * part);
@@ -191,10 +197,10 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
         for (int e = 0; e < 8; ++e)
             bias[e] = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] : 0.f;
-        float gv[4][8];
+        float gv[NIT][8];
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int row = (tid >> 4) + 16 * n;
+        for (int n = 0; n < NIT; ++n) {
+            const int row = (tid >> 4) + (INTRA_THREADS / 16) * n;
             const size_t off = base + (size_t)row * tok_stride + 4 * pc;
 #pragma unroll
             for (int e = 0; e < 8; ++e) gv[n][e] = 0.f;
@@ -216,8 +222,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             }
         }
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int row = (tid >> 4) + 16 * n;
+        for (int n = 0; n < NIT; ++n) {
+            const int row = (tid >> 4) + (INTRA_THREADS / 16) * n;
             float a[8];
             if (p.gate_mode == GATE_LOWER_BOUND) {
                 // lower_bound * sigmoid(alpha x) / ln2 with one ex2 and one rcp (flush-to-zero approximations)
@@ -225,7 +231,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
                 for (int e = 0; e < 8; ++e) a[e] = c1 * fast_rcp(1.f + fast_exp2(c0 * (gv[n][e] + bias[e])));
             } else {
-#pragma unroll
+#pragma unroll 1
                 for (int e = 0; e < 8; ++e) a[e] = RCP_LN2 * gate_activation(gv[n][e], alpha, bias[e], p.gate_mode, p.lower_bound);
             }
             if (row >= ci.valid) {
@@ -237,23 +243,23 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
     }
     __syncthreads();
-    // ---- 1b. cumulative sum down the rows: thread (half, d) scans 32 rows in shared memory ----
+    // ---- 1b. cumulative sum down the rows: thread (part, d) scans its 64/NPART rows in shared memory ----
     {
-        const int d = tid & 127, half = tid >> 7;
+        const int d = tid & 127, part = tid >> 7;
         float run = 0.f;
 #pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const int row = half * 32 + r;
+        for (int r = 0; r < 64 / NPART; ++r) {
+            const int row = part * (64 / NPART) + r;
             run += sG[row * DK + d];
             sG[row * DK + d] = run;
         }
-        if (half == 0) sHalf[d] = run;
+        sHalf[part * DK + d] = run;
     }
     // ---- 2. L2 norms from the rows held in registers, beta ----
-    float rstd_q[2], rstd_k[2], bet[2];
+    float rstd_q[RS], rstd_k[RS], bet[RS];
 #pragma unroll
-    for (int rs = 0; rs < 2; ++rs) {
-        const int row = rq + 32 * rs;
+    for (int rs = 0; rs < RS; ++rs) {
+        const int row = rq + RSTEP * rs;
         float sq = 0.f, sk = 0.f;
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
@@ -283,11 +289,12 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
     }
     __syncthreads();
-    if (tid >= 128) {   // second half of every column adds the first half's total
-        const int d = tid & 127;
-        const float t0 = sHalf[d];
+    if (tid >= 128) {   // later row segments add the totals of the earlier ones
+        const int d = tid & 127, part = tid >> 7;
+        float t0 = 0.f;
+        for (int q = 0; q < part; ++q) t0 += sHalf[q * DK + d];
 #pragma unroll 8
-        for (int r = 32; r < 64; ++r) sG[r * DK + d] += t0;
+        for (int r = 0; r < 64 / NPART; ++r) sG[(part * (64 / NPART) + r) * DK + d] += t0;
     }
     __syncthreads();
     // ---- anchor tables (r_I = G[16 I], g_last = G[63]) ----
@@ -313,16 +320,16 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     __syncthreads();
 
     // ---- 3. operand generation + Gram MMAs, one 64-channel half at a time ----
-    uint2 xpk[2][4];
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
+    uint2 xpk[RS][4];
+#pragma unroll 1
+    for (int hf = 0; hf < 2; ++hf) {       // rolled: register arrays are picked with selects on static indices
         if (hf == 1) {   // operand buffers are reused: wait until the first half's MMAs have read them
             if (!mbar_wait(&bars[0], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
             umma::fence_after_sync();
         }
 #pragma unroll
-        for (int rs = 0; rs < 2; ++rs) {
-            const int row = rq + 32 * rs, I = row >> 4, r7 = row & 7;
+        for (int rs = 0; rs < RS; ++rs) {
+            const int row = rq + RSTEP * rs, I = row >> 4, r7 = row & 7;
             const int rowN = (I < 3) ? 16 * (I + 1) : 63;
 #pragma unroll
             for (int it = 0; it < 2; ++it) {
@@ -338,9 +345,11 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 const float tt1[4] = {t1.x, t1.y, t1.z, t1.w};
                 float qv[4], kv[4];
                 {
-                    float2 a = unpack_bf16(qraw[rs][grp].x), b = unpack_bf16(qraw[rs][grp].y);
+                    const uint2 qsel = hf ? qraw[rs][2 + it] : qraw[rs][it];
+                    const uint2 ksel = hf ? kraw[rs][2 + it] : kraw[rs][it];
+                    float2 a = unpack_bf16(qsel.x), b = unpack_bf16(qsel.y);
                     qv[0] = a.x * rstd_q[rs]; qv[1] = a.y * rstd_q[rs]; qv[2] = b.x * rstd_q[rs]; qv[3] = b.y * rstd_q[rs];
-                    a = unpack_bf16(kraw[rs][grp].x); b = unpack_bf16(kraw[rs][grp].y);
+                    a = unpack_bf16(ksel.x); b = unpack_bf16(ksel.y);
                     kv[0] = a.x * rstd_k[rs]; kv[1] = a.y * rstd_k[rs]; kv[2] = b.x * rstd_k[rs]; kv[3] = b.y * rstd_k[rs];
                 }
                 float qa[4], ka[4], kown[4], kend[4], kg[4], qg[4], xx[4];
@@ -377,7 +386,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 const int goff = swz256(row, d0);
                 *reinterpret_cast<uint2*>(tile + TP_KG + goff) = make_uint2(pack_f16(kg[0], kg[1]), pack_f16(kg[2], kg[3]));
                 *reinterpret_cast<uint2*>(tile + TP_QG + goff) = make_uint2(pack_f16(qg[0], qg[1]), pack_f16(qg[2], qg[3]));
-                xpk[rs][grp] = make_uint2(pack_f16(xx[0], xx[1]), pack_f16(xx[2], xx[3]));
+                const uint2 xv = make_uint2(pack_f16(xx[0], xx[1]), pack_f16(xx[2], xx[3]));
+                if (hf) xpk[rs][2 + it] = xv; else xpk[rs][it] = xv;
             }
         }
         fence_proxy_async();
@@ -401,8 +411,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     // ---- 4. X and Y = beta v into shared memory (all threads); Gram epilogue: warp w reads TMEM lane
     //         quadrant w&3 and handles the 16-row block (w&1)*2 + (w>>2) living in its lower/upper half ----
 #pragma unroll
-    for (int rs = 0; rs < 2; ++rs) {
-        const int row = rq + 32 * rs;
+    for (int rs = 0; rs < RS; ++rs) {
+        const int row = rq + RSTEP * rs;
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
             const int chunk = 4 * (grp & 1) + (l8 >> 1);
@@ -415,23 +425,23 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     float* sT = reinterpret_cast<float*>(sm + SM_TM);
     {
         const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(p.v);
-        uint4 raw[4];
+        uint4 raw[NIT];
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int idx = tid + 256 * n, j = idx >> 4, ch = idx & 15;
+        for (int n = 0; n < NIT; ++n) {
+            const int idx = tid + INTRA_THREADS * n, j = idx >> 4, ch = idx & 15;
             raw[n] = make_uint4(0, 0, 0, 0);
             if (j < ci.valid) raw[n] = *reinterpret_cast<const uint4*>(vp + base + (size_t)j * tok_stride + 8 * ch);
         }
         {
-            const int qd = warp & 3, bsel = warp >> 2;
+            const int qd = warp & 3, bsel = (warp >> 2) & 1, gpar = warp >> 3;   // gpar splits the column groups (16 warps)
             const int blk = (qd & 1) * 2 + bsel;            // 16-row block handled by this warp
             const int row = (qd & 1) * 32 + lane;           // row of this lane inside the 64-row matrix
             const bool mine = (row >> 4) == blk;
             const bool is_q = qd < 2;                       // lanes 0..63 hold q rows (-> Aqk), 64..127 k rows (-> L)
             const float bi = sBeta[row];
             const uint32_t taddr = tmem + ((uint32_t)(qd * 32) << 16) + 8 * blk * (blk + 1);
-#pragma unroll
-            for (int gcol = 0; gcol < 4; ++gcol) {
+#pragma unroll 1
+            for (int gcol = gpar; gcol < 4; gcol += NWARPS / 8) {
                 uint32_t r[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) r[e] = 0u;
@@ -476,8 +486,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             }
         }
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int idx = tid + 256 * n, j = idx >> 4, ch = idx & 15;
+        for (int n = 0; n < NIT; ++n) {
+            const int idx = tid + INTRA_THREADS * n, j = idx >> 4, ch = idx & 15;
             const float b = sBeta[j];
             const uint32_t w4[4] = {raw[n].x, raw[n].y, raw[n].z, raw[n].w};
             uint32_t o4[4];
@@ -535,8 +545,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
         __syncthreads();
         // level 2: block rows 32..63 x cols 0..31. One 16x8 tile per warp (2 m-tiles x 4 n-tiles)
-        const int mt = warp >> 2, nt = warp & 3;
-        {
+        const int mt = (warp >> 2) & 1, nt = warp & 3;
+        if (warp < 8) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             mma_tile_3xtf32<4>(sL + (32 + 16 * mt) * LROW, LROW, sAi + 8 * nt, LROW, acc, g8, t4);
             float* td = sT + (16 * mt) * TROW + 8 * nt;
@@ -544,7 +554,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             td[(g8 + 8) * TROW + 2 * t4] = acc[2]; td[(g8 + 8) * TROW + 2 * t4 + 1] = acc[3];
         }
         __syncthreads();
-        {
+        if (warp < 8) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             mma_tile_3xtf32<4>(sAi + (32 + 16 * mt) * LROW + 32, LROW, sT + 8 * nt, TROW, acc, g8, t4);
             float* xd = sAi + (32 + 16 * mt) * LROW + 8 * nt;
@@ -554,24 +564,25 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     }
     __syncthreads();
     {   // Akk -> fp16 K-major operand (and fp32 to HBM when the backward pass wants it)
-        const int row = tid >> 2, c16 = (tid & 3) * 16;
-        float v[16];
+        constexpr int CPT = 4096 / INTRA_THREADS;              // columns per thread: 16 or 8
+        const int row = tid / (64 / CPT), c0 = (tid % (64 / CPT)) * CPT;
+        float v[CPT];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const int j = c16 + e;
+        for (int e = 0; e < CPT; ++e) {
+            const int j = c0 + e;
             v[e] = (j <= row) ? sAi[row * LROW + j] : 0.f;
         }
 #pragma unroll
-        for (int hc = 0; hc < 2; ++hc) {
-            const int ch = (c16 >> 3) + hc;
+        for (int hc = 0; hc < CPT / 8; ++hc) {
+            const int ch = (c0 >> 3) + hc;
             *reinterpret_cast<uint4*>(sm + SM_AKK16 + row * 128 + ((ch ^ (row & 7)) << 4)) =
                 make_uint4(pack_f16(v[8 * hc], v[8 * hc + 1]), pack_f16(v[8 * hc + 2], v[8 * hc + 3]),
                            pack_f16(v[8 * hc + 4], v[8 * hc + 5]), pack_f16(v[8 * hc + 6], v[8 * hc + 7]));
         }
         if (p.akk_out) {
-            float* ao = p.akk_out + ((size_t)c * p.H + h) * BT * BT + row * BT + c16;
+            float* ao = p.akk_out + ((size_t)c * p.H + h) * BT * BT + row * BT + c0;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
+            for (int q4 = 0; q4 < CPT / 4; ++q4)
                 *reinterpret_cast<float4*>(ao + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
         }
     }
@@ -599,11 +610,13 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 
     // ---- 7. epilogue: lane = channel, columns = tokens; fp16 into the swizzled tile pack ----
     {
-        const int qd = warp & 3, which = warp >> 2, d = 32 * qd + lane;
+        const int qd = warp & 3, which = (warp >> 2) & 1, d = 32 * qd + lane;
+        constexpr int CGN = 4 / (NWARPS / 8);                  // token-column groups per warp
+        const int cg0 = (warp >> 3) * CGN;
         const uint32_t taddr = tmem + ((uint32_t)(32 * qd) << 16) + 64 * which;
         unsigned char* dst = which ? tile + (d < 64 ? TP_U0 : TP_U1) : tile + TP_W;
-#pragma unroll
-        for (int cg = 0; cg < 4; ++cg) {
+#pragma unroll 1
+        for (int cg = cg0; cg < cg0 + CGN; ++cg) {
             uint32_t r[16];
             umma::ld_32x32b_x16(taddr + 16 * cg, r);
             umma::wait_ld();
