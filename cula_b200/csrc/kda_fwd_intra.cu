@@ -42,14 +42,14 @@ constexpr int SM_MISC = 111616;           // beta[64], barriers, tmem base, half
 constexpr int SM_TOTAL = 113664;
 constexpr int KATOM_A = 16384, KATOM_B = 20480;
 // regions reused once the Gram MMAs have completed
-constexpr int SM_XS = SM_OPA;             // X = beta k 2^g, fp16 [2 mn-atoms][64 tokens][128 B], SW128 (MN-major A operand)
+constexpr int SM_XS = SM_OPA;             // X = beta k 2^g, fp16 [2 mn-atoms][64 tokens][128 B], SW128 (MN-major B operand)
 constexpr int SM_YS = SM_OPA + 16384;     // Y = beta v, same layout
 constexpr int LROW = 68;                  // padded fp32 row of the 64x64 matrices
 constexpr int SM_LF = SM_OPB;             // L fp32 [64][68]
 constexpr int SM_AINV = SM_OPB + 17408;   // (I+L)^-1 fp32 [64][68]
 constexpr int SM_TM = SM_OPB + 34816;     // scratch for the block products [32][36]
 constexpr int TROW = 36;
-constexpr int SM_AKK16 = SM_G;            // Akk fp16 [64][128 B], SW128 (K-major B operand)
+constexpr int SM_AKK16 = SM_G;            // Akk fp16, stacked twice: [128][128 B], SW128 (K-major A operand)
 
 // anchor tables
 constexpr int TAB_E = 0;     // [4]  2^(r_I)
@@ -224,22 +224,22 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
         for (int n = 0; n < NIT; ++n) {
             const int row = (tid >> 4) + (INTRA_THREADS / 16) * n;
-            float a[8];
             if (p.gate_mode == GATE_LOWER_BOUND) {
                 // lower_bound * sigmoid(alpha x) / ln2 with one ex2 and one rcp (flush-to-zero approximations)
-                const float c0 = -alpha * RCP_LN2, c1 = p.lower_bound * RCP_LN2;
+                const float c0 = -alpha * RCP_LN2, c1 = (row < ci.valid) ? p.lower_bound * RCP_LN2 : 0.f;
+                float a[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) a[e] = c1 * fast_rcp(1.f + fast_exp2(c0 * (gv[n][e] + bias[e])));
+                *reinterpret_cast<float4*>(sG + row * DK + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
+                *reinterpret_cast<float4*>(sG + row * DK + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
             } else {
-#pragma unroll 1
-                for (int e = 0; e < 8; ++e) a[e] = RCP_LN2 * gate_activation(gv[n][e], alpha, bias[e], p.gate_mode, p.lower_bound);
-            }
-            if (row >= ci.valid) {
+                // other gate forms: rolled, element by element (keeps the long softplus code out of line)
+                const float keep = (row < ci.valid) ? RCP_LN2 : 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) a[e] = 0.f;
+                for (int e = 0; e < 8; ++e)
+                    sG[row * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] =
+                        keep * gate_activation(gv[n][e], alpha, bias[e], p.gate_mode, p.lower_bound);
             }
-            *reinterpret_cast<float4*>(sG + row * DK + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
-            *reinterpret_cast<float4*>(sG + row * DK + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
         }
     }
     __syncthreads();
@@ -442,13 +442,16 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             const uint32_t taddr = tmem + ((uint32_t)(qd * 32) << 16) + 8 * blk * (blk + 1);
 #pragma unroll 1
             for (int gcol = gpar; gcol < 4; gcol += NWARPS / 8) {
-                uint32_t r[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) r[e] = 0u;
-                if (gcol <= blk) {                           // warp-uniform
-                    umma::ld_32x32b_x16(taddr + 16 * gcol, r);
-                    umma::wait_ld();
+                if (gcol > blk) {                            // warp-uniform: nothing but zeros right of the block
+                    if (mine && is_q) {
+                        *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol + 8)) = make_uint4(0, 0, 0, 0);
+                    }
+                    continue;
                 }
+                uint32_t r[16];
+                umma::ld_32x32b_x16(taddr + 16 * gcol, r);
+                umma::wait_ld();
                 if (mine) {
                     float vals[16];
 #pragma unroll
@@ -575,9 +578,11 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
         for (int hc = 0; hc < CPT / 8; ++hc) {
             const int ch = (c0 >> 3) + hc;
-            *reinterpret_cast<uint4*>(sm + SM_AKK16 + row * 128 + ((ch ^ (row & 7)) << 4)) =
-                make_uint4(pack_f16(v[8 * hc], v[8 * hc + 1]), pack_f16(v[8 * hc + 2], v[8 * hc + 3]),
-                           pack_f16(v[8 * hc + 4], v[8 * hc + 5]), pack_f16(v[8 * hc + 6], v[8 * hc + 7]));
+            const uint4 pk = make_uint4(pack_f16(v[8 * hc], v[8 * hc + 1]), pack_f16(v[8 * hc + 2], v[8 * hc + 3]),
+                                        pack_f16(v[8 * hc + 4], v[8 * hc + 5]), pack_f16(v[8 * hc + 6], v[8 * hc + 7]));
+            unsigned char* dstk = sm + SM_AKK16 + row * 128 + ((ch ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(dstk) = pk;
+            *reinterpret_cast<uint4*>(dstk + 8192) = pk;        // rows 64..127 of the A operand repeat Akk
         }
         if (p.akk_out) {
             float* ao = p.akk_out + ((size_t)c * p.H + h) * BT * BT + row * BT + c0;
@@ -590,42 +595,44 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     umma::fence_before_sync();
     __syncthreads();
 
-    // ---- 6. w^T = X^T Akk^T (TMEM columns 0..63), u^T = Y^T Akk^T (columns 64..127) ----
+    // ---- 6. [w | u] = Akk [X | Y]: one M=128 x N=256 x K=64 product. A = Akk stacked twice (K-major), so TMEM
+    //         lanes 0..63 and 64..127 both hold the 64 token rows; B = [X | Y] as four MN-major 64-channel atoms ----
     if (tid == 0) {
         umma::fence_after_sync();
-        const uint32_t idesc = umma::make_idesc(umma::FMT_F16, 128, 64, true, false);
+        const uint32_t idesc = umma::make_idesc(umma::FMT_F16, 128, 256, false, true);
 #pragma unroll
-        for (int which = 0; which < 2; ++which) {
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                const uint64_t ad = sdesc_sw128(sm_u32 + (which ? SM_YS : SM_XS) + ks * 2048, 8192, 1024);
-                const uint64_t bd = sdesc_sw128(sm_u32 + SM_AKK16 + ks * 32, 16, 1024);
-                umma::mma_f16(tmem + 64 * which, ad, bd, idesc, ks != 0);
-            }
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = sdesc_sw128(sm_u32 + SM_AKK16 + ks * 32, 16, 1024);
+            const uint64_t bd = sdesc_sw128(sm_u32 + SM_XS + ks * 2048, 8192, 1024);
+            umma::mma_f16(tmem, ad, bd, idesc, ks != 0);
         }
         umma::commit(&bars[2]);
     }
     if (!mbar_wait(&bars[2], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
     umma::fence_after_sync();
 
-    // ---- 7. epilogue: lane = channel, columns = tokens; fp16 into the swizzled tile pack ----
+    // ---- 7. epilogue: lane = token, columns = channels; lanes 0..63 write w, the duplicate lanes 64..127 write u;
+    //         each thread converts 64/(NWARPS/8) channels to fp16 and stores 16 bytes at a time ----
     {
-        const int qd = warp & 3, which = (warp >> 2) & 1, d = 32 * qd + lane;
-        constexpr int CGN = 4 / (NWARPS / 8);                  // token-column groups per warp
-        const int cg0 = (warp >> 3) * CGN;
-        const uint32_t taddr = tmem + ((uint32_t)(32 * qd) << 16) + 64 * which;
-        unsigned char* dst = which ? tile + (d < 64 ? TP_U0 : TP_U1) : tile + TP_W;
+        const int qd = warp & 3, is_u = qd >> 1, tok = 32 * (qd & 1) + lane;
+        constexpr int CPW = 512 / NWARPS;                      // channels per warp: 64 (8 warps) or 32 (16 warps)
+        const int ch0 = (warp >> 2) * CPW;                     // first channel (0..127) of this warp
+        const uint32_t taddr = tmem + ((uint32_t)(32 * qd) << 16) + 128 * is_u + ch0;
 #pragma unroll 1
-        for (int cg = cg0; cg < cg0 + CGN; ++cg) {
+        for (int cg = 0; cg < CPW / 16; ++cg) {
             uint32_t r[16];
             umma::ld_32x32b_x16(taddr + 16 * cg, r);
             umma::wait_ld();
+            const int chn = ch0 + 16 * cg;
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const int tok = 16 * cg + e;
-                const __half hv = __float2half_rn(__uint_as_float(r[e]));
-                if (which) *reinterpret_cast<__half*>(dst + swz128(tok, d & 63)) = hv;
-                else *reinterpret_cast<__half*>(dst + swz256(tok, d)) = hv;
+            for (int hc = 0; hc < 2; ++hc) {
+                const uint4 pk = make_uint4(pack_f16(__uint_as_float(r[8 * hc]), __uint_as_float(r[8 * hc + 1])),
+                                            pack_f16(__uint_as_float(r[8 * hc + 2]), __uint_as_float(r[8 * hc + 3])),
+                                            pack_f16(__uint_as_float(r[8 * hc + 4]), __uint_as_float(r[8 * hc + 5])),
+                                            pack_f16(__uint_as_float(r[8 * hc + 6]), __uint_as_float(r[8 * hc + 7])));
+                const int cc = chn + 8 * hc;
+                if (is_u) *reinterpret_cast<uint4*>(tile + (cc < 64 ? TP_U0 : TP_U1) + swz128(tok, cc & 63)) = pk;
+                else *reinterpret_cast<uint4*>(tile + TP_W + swz256(tok, cc)) = pk;
             }
         }
     }
