@@ -291,7 +291,7 @@ def main():
 
     import torch.distributed as dist
     from cula_b200 import _native
-    from cula_b200.kda import check_status, chunk_kda
+    from cula_b200.kda import check_status, chunk_kda, chunk_kda_host
     from cula_b200.synthetic import make_inputs
 
     torch.cuda.set_device(local_rank)
@@ -351,10 +351,9 @@ def main():
     ht_host = torch.empty(B, H, 128, 128, dtype=torch.float32).pin_memory()
 
     def e2e_step():
-        t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-        o, ht = fwd(t)
-        o_host.copy_(o, non_blocking=True)
-        ht_host.copy_(ht, non_blocking=True)
+        # the public host-buffer call: uploads, kernels and downloads are pipelined over 512-token segments
+        chunk_kda_host(host["q"], host["k"], host["v"], host["g"], host["beta"], out=o_host, final_state_out=ht_host,
+                       A_log=d["A_log"], dt_bias=d["dt_bias"], **kw)
 
     ms_e2e = timed(e2e_step, max(3, args.steps // 2), 3)
     h2d = sum(v.numel() * v.element_size() for v in host.values())

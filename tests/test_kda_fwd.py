@@ -191,3 +191,21 @@ def test_return_intermediate_states():
     short = {k: (v[:, :128] if k in ("q", "k", "v", "g", "beta") else v) for k, v in inp.items()}
     _, ht128 = oracle_fwd(short)
     assert err_ratio(ht128, h[:, 2].float().cpu()) < 5e-3
+
+
+def test_host_pipelined_forward_matches_device_call():
+    """chunk_kda_host (segments + carried state, copies overlapped) returns exactly what chunk_kda returns."""
+    from cula_b200.kda import chunk_kda, chunk_kda_host
+    B, T, H = 2, 1200, 3                      # not a multiple of the segment length
+    inp = make_inputs(B, T, H, seed=6, gate_offset=-7.0, h0_std=0.5)
+    host = {k: v.pin_memory() for k, v in inp.items()}
+    o_h, ht_h = chunk_kda_host(host["q"], host["k"], host["v"], host["g"], host["beta"], segment_tokens=512,
+                               initial_state=host["initial_state"], output_final_state=True, use_qk_l2norm_in_kernel=True,
+                               use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=host["A_log"],
+                               dt_bias=host["dt_bias"])
+    d = {k: v.cuda() for k, v in inp.items()}
+    o_d, ht_d = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"],
+                          output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True,
+                          lower_bound=-5.0, A_log=d["A_log"], dt_bias=d["dt_bias"])
+    torch.cuda.synchronize()
+    assert o_h.device.type == "cpu" and torch.equal(o_h, o_d.cpu()) and torch.equal(ht_h, ht_d.cpu())
