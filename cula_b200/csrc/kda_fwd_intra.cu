@@ -51,10 +51,6 @@ constexpr int SM_TM = SM_OPB + 34816;     // scratch for the block products [32]
 constexpr int TROW = 36;
 constexpr int SM_AKK16 = SM_G;            // Akk fp16, stacked twice: [128][128 B], SW128 (K-major A operand)
 
-// anchor tables
-constexpr int TAB_E = 0;     // [4]  2^(r_I)
-constexpr int TAB_T1 = 4;    // [3]  2^(g_last - r_{I+1}),  I = 0..2
-constexpr int TAB_T2 = 7;    // [3]  2^(r_2 - r_1), 2^(r_3 - r_1), 2^(r_3 - r_2)
 
 __device__ __forceinline__ uint64_t sdesc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return umma::make_sdesc(addr, lbo, sbo) | (2ull << 61);
@@ -113,7 +109,6 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     unsigned char* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sm_u32 = smem_u32(sm);
     float* sG = reinterpret_cast<float*>(sm + SM_G);
-    float* sTab = reinterpret_cast<float*>(sm + SM_TAB);
     float* sBeta = reinterpret_cast<float*>(sm + SM_MISC);
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SM_MISC + 256);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + SM_MISC + 288);
@@ -135,18 +130,12 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     umma::fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    // persistent over (chunk, head) tiles; the completion barriers flip phase once per tile
-    for (int tile_id = blockIdx.x, iter = 0; tile_id < p.num_tiles; tile_id += gridDim.x, ++iter) {
-    const uint32_t par = iter & 1;
-    const int c = tile_id / p.H, h = tile_id - c * p.H;
-    const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
-    const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DK;
-    unsigned char* tile = p.tiles + ((size_t)c * p.H + h) * TP_BYTES;
-
-    // q, k rows of this tile into registers first, so their latency hides behind the gate pass.
-    // Thread (rq, l8): rows rq and rq+32, channels 32*grp + 4*l8 .. +3 for the four channel groups grp.
     uint2 qraw[RS][4], kraw[RS][4];
-    {
+    uint2 graw[NIT][2];             // bf16 gate rows of the (row, 16-lane) mapping; fp32 gates are loaded in place
+    auto fetch_rows = [&](int t_id) {
+        const int c2 = t_id / p.H, h2 = t_id - c2 * p.H;
+        const ChunkInfo ci2 = chunk_info(c2, p.cu_seqlens, p.chunk_indices, p.T);
+        const size_t base2 = (size_t)ci2.row0 * tok_stride + (size_t)h2 * DK;
         const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q);
         const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(p.k);
 #pragma unroll
@@ -155,8 +144,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
             for (int grp = 0; grp < 4; ++grp) {
                 uint2 qv = make_uint2(0, 0), kv = make_uint2(0, 0);
-                if (row < ci.valid) {
-                    size_t off = base + (size_t)row * tok_stride + 32 * grp + 4 * l8;
+                if (row < ci2.valid) {
+                    size_t off = base2 + (size_t)row * tok_stride + 32 * grp + 4 * l8;
                     qv = *reinterpret_cast<const uint2*>(qp + off);
                     kv = *reinterpret_cast<const uint2*>(kp + off);
                 }
@@ -164,7 +153,31 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 kraw[rs][grp] = kv;
             }
         }
-    }
+        if (!p.g_fp32) {
+#pragma unroll
+            for (int n = 0; n < NIT; ++n) {
+                const int row = (tid >> 4) + (INTRA_THREADS / 16) * n;
+                graw[n][0] = graw[n][1] = make_uint2(0, 0);
+                if (row < ci2.valid) {
+                    const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.g) + base2 + (size_t)row * tok_stride + 4 * (tid & 15);
+                    graw[n][0] = *reinterpret_cast<const uint2*>(gp);
+                    graw[n][1] = *reinterpret_cast<const uint2*>(gp + 64);
+                }
+            }
+        }
+    };
+    if ((int)blockIdx.x < p.num_tiles) fetch_rows(blockIdx.x);
+
+    // persistent over (chunk, head) tiles; the completion barriers flip phase once per tile
+    for (int tile_id = blockIdx.x, iter = 0; tile_id < p.num_tiles; tile_id += gridDim.x, ++iter) {
+    const uint32_t par = iter & 1;
+    const int c = tile_id / p.H, h = tile_id - c * p.H;
+    const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
+    const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DK;
+    unsigned char* tile = p.tiles + ((size_t)c * p.H + h) * TP_BYTES;
+
+    // q, k, g rows of this tile are already in registers: they were fetched while the previous tile was in its
+    // epilogues (first tile: before the loop). Thread (rq, l8): rows rq (+RSTEP), channels 32*grp + 4*l8 .. +3.
     if (tid < 256) {   // pull this tile's v rows and the next tile's inputs towards L2 (two 128-byte lines per row)
         const int row = tid >> 2, part = tid & 3;
         if (part < 2 && row < ci.valid)
@@ -211,8 +224,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                     gv[n][0] = lo.x; gv[n][1] = lo.y; gv[n][2] = lo.z; gv[n][3] = lo.w;
                     gv[n][4] = hi.x; gv[n][5] = hi.y; gv[n][6] = hi.z; gv[n][7] = hi.w;
                 } else {
-                    const uint2 lo = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off);
-                    const uint2 hi = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off + 64);
+                    const uint2 lo = graw[n][0], hi = graw[n][1];
                     float2 f;
                     f = unpack_bf16(lo.x); gv[n][0] = f.x; gv[n][1] = f.y;
                     f = unpack_bf16(lo.y); gv[n][2] = f.x; gv[n][3] = f.y;
@@ -297,27 +309,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         for (int r = 0; r < 64 / NPART; ++r) sG[(part * (64 / NPART) + r) * DK + d] += t0;
     }
     __syncthreads();
-    // ---- anchor tables (r_I = G[16 I], g_last = G[63]) ----
-    for (int i = tid; i < 10 * DK; i += INTRA_THREADS) {
-        const int t = i >> 7, d = i & 127;
-        const float r0 = sG[d], r1 = sG[16 * DK + d], r2 = sG[32 * DK + d], r3 = sG[48 * DK + d], gl = sG[63 * DK + d];
-        float x;
-        switch (t) {
-            case 0: x = r0; break;
-            case 1: x = r1; break;
-            case 2: x = r2; break;
-            case 3: x = r3; break;
-            case 4: x = gl - r1; break;
-            case 5: x = gl - r2; break;
-            case 6: x = gl - r3; break;
-            case 7: x = r2 - r1; break;
-            case 8: x = r3 - r1; break;
-            default: x = r3 - r2; break;
-        }
-        sTab[i] = fast_exp2(x);
-    }
     if (tid < DK) reinterpret_cast<float*>(tile + TP_DECAY)[tid] = fast_exp2(sG[63 * DK + tid]);
-    __syncthreads();
 
     // ---- 3. operand generation + Gram MMAs, one 64-channel half at a time ----
     uint2 xpk[RS][4];
@@ -330,19 +322,14 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
         for (int rs = 0; rs < RS; ++rs) {
             const int row = rq + RSTEP * rs, I = row >> 4, r7 = row & 7;
-            const int rowN = (I < 3) ? 16 * (I + 1) : 63;
 #pragma unroll
             for (int it = 0; it < 2; ++it) {
                 const int grp = hf * 2 + it, d0 = 32 * grp + 4 * l8;
                 const float4 Gi = *reinterpret_cast<const float4*>(sG + row * DK + d0);
                 const float4 rI = *reinterpret_cast<const float4*>(sG + 16 * I * DK + d0);
-                const float4 rN = *reinterpret_cast<const float4*>(sG + rowN * DK + d0);
-                const float4 tE = *reinterpret_cast<const float4*>(sTab + (TAB_E + I) * DK + d0);
-                float4 t1 = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (I < 3) t1 = *reinterpret_cast<const float4*>(sTab + (TAB_T1 + I) * DK + d0);
+                const float4 gL = *reinterpret_cast<const float4*>(sG + 63 * DK + d0);
                 const float gi[4] = {Gi.x, Gi.y, Gi.z, Gi.w}, ri[4] = {rI.x, rI.y, rI.z, rI.w};
-                const float rn[4] = {rN.x, rN.y, rN.z, rN.w}, te[4] = {tE.x, tE.y, tE.z, tE.w};
-                const float tt1[4] = {t1.x, t1.y, t1.z, t1.w};
+                const float gl[4] = {gL.x, gL.y, gL.z, gL.w};
                 float qv[4], kv[4];
                 {
                     const uint2 qsel = hf ? qraw[rs][2 + it] : qraw[rs][it];
@@ -352,18 +339,16 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                     a = unpack_bf16(ksel.x); b = unpack_bf16(ksel.y);
                     kv[0] = a.x * rstd_k[rs]; kv[1] = a.y * rstd_k[rs]; kv[2] = b.x * rstd_k[rs]; kv[3] = b.y * rstd_k[rs];
                 }
-                float qa[4], ka[4], kown[4], kend[4], kg[4], qg[4], xx[4];
+                float qa[4], ka[4], kown[4], kg[4], qg[4], xx[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float eA = fast_exp2(gi[e] - ri[e]);      // <= 1
                     const float eB = fast_exp2(ri[e] - gi[e]);      // >= 1, <= 2^108 under the safe gate
-                    const float eE = fast_exp2(rn[e] - gi[e]);      // decay to the end of the block, <= 1
+                    const float eG = fast_exp2(gi[e]);              // 2^(g_i)
                     qa[e] = qv[e] * eA;
                     ka[e] = kv[e] * eA;
                     kown[e] = kv[e] * eB;
-                    kend[e] = kv[e] * eE;
-                    kg[e] = kend[e] * tt1[e];
-                    const float eG = eA * te[e];                    // 2^(g_i)
+                    kg[e] = kv[e] * fast_exp2(gl[e] - gi[e]);
                     qg[e] = p.scale * qv[e] * eG;
                     xx[e] = bet[rs] * kv[e] * eG;
                 }
@@ -375,12 +360,11 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 *reinterpret_cast<float4*>(opb + (8 * I * (I + 1) + row) * 128) = tf32x4(kown[0], kown[1], kown[2], kown[3]);
 #pragma unroll
                 for (int Ip = 1; Ip < 4; ++Ip) {
-                    if (Ip > I) {
-                        float4 f = make_float4(1.f, 1.f, 1.f, 1.f);
-                        if (Ip > I + 1)   // (Ip, I+1) in {(2,1),(3,1),(3,2)}
-                            f = *reinterpret_cast<const float4*>(sTab + (TAB_T2 + (Ip == 2 ? 0 : I + 1)) * DK + d0);
+                    if (Ip > I) {     // copy anchored at the first row of the later block Ip: factor 2^(r_Ip - g_j) <= 1
+                        const float4 rp = *reinterpret_cast<const float4*>(sG + 16 * Ip * DK + d0);
                         *reinterpret_cast<float4*>(opb + (8 * Ip * (Ip + 1) + row) * 128) =
-                            tf32x4(kend[0] * f.x, kend[1] * f.y, kend[2] * f.z, kend[3] * f.w);
+                            tf32x4(kv[0] * fast_exp2(rp.x - gi[0]), kv[1] * fast_exp2(rp.y - gi[1]),
+                                   kv[2] * fast_exp2(rp.z - gi[2]), kv[3] * fast_exp2(rp.w - gi[3]));
                     }
                 }
                 const int goff = swz256(row, d0);
@@ -420,6 +404,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 xpk[rs][grp];
         }
     }
+    if (tile_id + (int)gridDim.x < p.num_tiles) fetch_rows(tile_id + gridDim.x);   // lands during the epilogues
     float* sL = reinterpret_cast<float*>(sm + SM_LF);
     float* sAi = reinterpret_cast<float*>(sm + SM_AINV);
     float* sT = reinterpret_cast<float*>(sm + SM_TM);
