@@ -55,7 +55,8 @@ extern "C" int cula_kda_fwd_scan(const void* d_tiles, const float* d_h0, void* d
                                  void* d_vnew_out, float* d_h32_out, const int* d_cu_seqlens, const int* d_chunk_offsets,
                                  const int* d_seq_order, int N, int T, int H, int* d_status, void* stream) {
     if (N == 0) return 0;
-    if (!d_tiles || !d_o || !d_status || N < 0 || H <= 0) return CULA_KDA_EINVAL;
+    if (!d_tiles || !d_status || N < 0 || H <= 0) return CULA_KDA_EINVAL;
+    if (!d_o && !d_vnew_out) return CULA_KDA_EINVAL;      // nothing to produce
     if ((d_cu_seqlens == nullptr) != (d_chunk_offsets == nullptr)) return CULA_KDA_EINVAL;
     if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
     if ((d_h_out || d_h32_out) && !d_vnew_out) return CULA_KDA_EINVAL;
@@ -94,6 +95,7 @@ extern "C" int cula_kda_bwd_scratch_floats(void) { return kda::BWD_SCRATCH_FLOAT
 extern "C" int cula_kda_bwd_grad_scale(const void* d_do, long long n_do, const float* d_dht, long long n_dht,
                                        unsigned int* d_amax, float* d_gscale, void* stream) {
     if (!d_do || !d_amax || !d_gscale || n_do < 0 || n_dht < 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_do) || misaligned(d_dht)) return CULA_KDA_EALIGN;
     return kda_launch_grad_scale(d_do, (size_t)n_do, d_dht, (size_t)n_dht, d_amax, d_gscale, static_cast<cudaStream_t>(stream));
 }
 

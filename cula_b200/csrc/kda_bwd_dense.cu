@@ -13,7 +13,10 @@
 
 namespace kda {
 
-constexpr int BD_THREADS = 256;
+constexpr int BD_THREADS = 512;
+constexpr int BD_NQ = BD_THREADS / 128;   // column groups: a warp = 16-row tile x column group
+constexpr int BD_NT128 = 128 / BD_NQ / 8; // n-tiles per warp over the 128 key channels
+constexpr int BD_NT64 = 64 / BD_NQ / 8;   // n-tiles per warp over 64 token / value columns
 constexpr int PR = 68;                    // padded fp32 row: fragment loads hit 32 distinct banks
 // shared memory (floats)
 constexpr int BD_S = 0;                   // S_h   [128][68]
@@ -24,8 +27,8 @@ constexpr int BD_DVN = BD_VN + 64 * PR;   // dVn_h
 constexpr int BD_V = BD_DVN + 64 * PR;    // V_h (raw)
 constexpr int BD_A = BD_V + 64 * PR;      // A [64][68]
 constexpr int BD_BETA = BD_A + 64 * PR;   // beta[64]
-constexpr int BD_RED = BD_BETA + 64;      // dbeta_u[2][64] partials, dD[2][128] partials
-constexpr int BD_FLOATS = BD_RED + 128 + 256;
+constexpr int BD_RED = BD_BETA + 64;      // dbeta_u partials [BD_NQ][64]
+constexpr int BD_FLOATS = BD_RED + BD_NQ * 64;
 constexpr int BD_SMEM = BD_FLOATS * 4;
 
 __device__ __forceinline__ float tf32r(float x) {
@@ -44,7 +47,7 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
     extern __shared__ __align__(16) float sm[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int mt = warp & 3, nh = warp >> 2;          // 16-row tile, column half
+    const int mt = warp & 3, nh = warp >> 2;          // 16-row tile, column group
     const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
     const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
     const size_t tile_idx = (size_t)c * p.H + h;
@@ -75,16 +78,16 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
         sm[BD_BETA + tid] = b;
     }
 
-    float accQ[8][4], accW[8][4], accK[8][4], accP[4][4], accA[4][4];
+    float accQ[BD_NT128][4], accW[BD_NT128][4], accK[BD_NT128][4], accP[BD_NT64][4], accA[BD_NT64][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < BD_NT128; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) accQ[i][e] = accW[i][e] = accK[i][e] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < BD_NT64; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) accP[i][e] = accA[i][e] = 0.f;
-    float dD_part = 0.f, dbu0 = 0.f, dbu1 = 0.f;     // dD for row k = tid (tid < 128); dbeta_u for rows 16mt+g, +8
+    float dD_part = 0.f, dbu0 = 0.f, dbu1 = 0.f;     // dD for row k = tid / BD_NQ (a column slice per thread); dbeta_u for rows 16mt+g, +8
 
     for (int vh = 0; vh < 2; ++vh) {
         __syncthreads();        // previous half's fragments are no longer read
@@ -125,10 +128,14 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
         }
         __syncthreads();
         // ---- dD partial: row k = tid ----
-        if (tid < 128) {
+        {
+            const int row = tid / BD_NQ, v0 = (tid % BD_NQ) * (64 / BD_NQ);
             float a = 0.f;
 #pragma unroll 8
-            for (int v = 0; v < 64; ++v) a = fmaf(sm[BD_S + tid * PR + v], sm[BD_DS + tid * PR + v], a);
+            for (int v = 0; v < 64 / BD_NQ; ++v) {
+                const int vv = v0 + ((v + row) & (64 / BD_NQ - 1));      // rotated start: spreads the banks
+                a = fmaf(sm[BD_S + row * PR + vv], sm[BD_DS + row * PR + vv], a);
+            }
             dD_part += a;
         }
         // ---- contraction over the 64 value columns of this half ----
@@ -142,8 +149,8 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             const float fV[4] = {aV[g * PR + k0 + t], aV[(g + 8) * PR + k0 + t], aV[g * PR + k0 + t + 4], aV[(g + 8) * PR + k0 + t + 4]};
             const float fD[4] = {aD[g * PR + k0 + t], aD[(g + 8) * PR + k0 + t], aD[g * PR + k0 + t + 4], aD[(g + 8) * PR + k0 + t + 4]};
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const int n0 = 64 * nh + 8 * nt;      // key channel
+            for (int nt = 0; nt < BD_NT128; ++nt) {
+                const int n0 = 8 * BD_NT128 * nh + 8 * nt;      // key channel
                 const float s0 = sm[BD_S + (n0 + g) * PR + k0 + t], s1 = sm[BD_S + (n0 + g) * PR + k0 + t + 4];
                 const float d0 = sm[BD_DS + (n0 + g) * PR + k0 + t], d1 = sm[BD_DS + (n0 + g) * PR + k0 + t + 4];
                 mma_tf32(accQ[nt], fO, s0, s1);
@@ -151,8 +158,8 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
                 mma_tf32(accK[nt], fV, d0, d1);
             }
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int j0 = 32 * nh + 8 * nt;      // token column
+            for (int nt = 0; nt < BD_NT64; ++nt) {
+                const int j0 = 8 * BD_NT64 * nh + 8 * nt;      // token column
                 const float v0 = sm[BD_VN + (j0 + g) * PR + k0 + t], v1 = sm[BD_VN + (j0 + g) * PR + k0 + t + 4];
                 const float y0 = sm[BD_V + (j0 + g) * PR + k0 + t], y1 = sm[BD_V + (j0 + g) * PR + k0 + t + 4];
                 mma_tf32(accP[nt], fO, v0, v1);
@@ -160,9 +167,9 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             }
         }
         // ---- Zu = A^T dVn_h : [64 i] x [64 v of this half], contraction over the 64 tokens j ----
-        float accZ[4][4];
+        float accZ[BD_NT64][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < BD_NT64; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) accZ[i][e] = 0.f;
 #pragma unroll 2
@@ -171,8 +178,8 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             const float fA[4] = {sm[BD_A + (j0 + t) * PR + i0 + g], sm[BD_A + (j0 + t) * PR + i0 + g + 8],
                                  sm[BD_A + (j0 + t + 4) * PR + i0 + g], sm[BD_A + (j0 + t + 4) * PR + i0 + g + 8]};
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int v0 = 32 * nh + 8 * nt;
+            for (int nt = 0; nt < BD_NT64; ++nt) {
+                const int v0 = 8 * BD_NT64 * nh + 8 * nt;
                 mma_tf32(accZ[nt], fA, sm[BD_DVN + (j0 + t) * PR + v0 + g], sm[BD_DVN + (j0 + t + 4) * PR + v0 + g]);
             }
         }
@@ -181,8 +188,8 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             const float b0 = sm[BD_BETA + r0], b1 = sm[BD_BETA + r1];
             __nv_bfloat16* dvp = reinterpret_cast<__nv_bfloat16*>(p.dv);
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int vc = 32 * nh + 8 * nt + 2 * t;
+            for (int nt = 0; nt < BD_NT64; ++nt) {
+                const int vc = 8 * BD_NT64 * nh + 8 * nt + 2 * t;
                 dbu0 += accZ[nt][0] * sm[BD_V + r0 * PR + vc] + accZ[nt][1] * sm[BD_V + r0 * PR + vc + 1];
                 dbu1 += accZ[nt][2] * sm[BD_V + r1 * PR + vc] + accZ[nt][3] * sm[BD_V + r1 * PR + vc + 1];
                 if (r0 < ci.valid)
@@ -198,8 +205,8 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
     {
         const int r0 = 16 * mt + g, r1 = r0 + 8;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            const int col = 64 * nh + 8 * nt + 2 * t;
+        for (int nt = 0; nt < BD_NT128; ++nt) {
+            const int col = 8 * BD_NT128 * nh + 8 * nt + 2 * t;
             *reinterpret_cast<float2*>(scr + SCR_DQG + r0 * DK + col) = make_float2(accQ[nt][0], accQ[nt][1]);
             *reinterpret_cast<float2*>(scr + SCR_DQG + r1 * DK + col) = make_float2(accQ[nt][2], accQ[nt][3]);
             *reinterpret_cast<float2*>(scr + SCR_DW + r0 * DK + col) = make_float2(-accW[nt][0], -accW[nt][1]);
@@ -208,8 +215,8 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             *reinterpret_cast<float2*>(scr + SCR_DKG + r1 * DK + col) = make_float2(accK[nt][2], accK[nt][3]);
         }
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = 32 * nh + 8 * nt + 2 * t;
+        for (int nt = 0; nt < BD_NT64; ++nt) {
+            const int col = 8 * BD_NT64 * nh + 8 * nt + 2 * t;
             const float bj0 = sm[BD_BETA + col], bj1 = sm[BD_BETA + col + 1];
             float p00 = (col <= r0) ? accP[nt][0] : 0.f, p01 = (col + 1 <= r0) ? accP[nt][1] : 0.f;
             float p10 = (col <= r1) ? accP[nt][2] : 0.f, p11 = (col + 1 <= r1) ? accP[nt][3] : 0.f;
@@ -220,7 +227,7 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             *reinterpret_cast<float2*>(scr + SCR_DAU + r0 * BT + col) = make_float2(a00, a01);
             *reinterpret_cast<float2*>(scr + SCR_DAU + r1 * BT + col) = make_float2(a10, a11);
         }
-        // dbeta_u: reduce over the 4 lanes of a quad, then over the two column halves through shared memory
+        // dbeta_u: reduce over the 4 lanes of a quad, then over the column groups through shared memory
         dbu0 += __shfl_xor_sync(0xffffffffu, dbu0, 1); dbu0 += __shfl_xor_sync(0xffffffffu, dbu0, 2);
         dbu1 += __shfl_xor_sync(0xffffffffu, dbu1, 1); dbu1 += __shfl_xor_sync(0xffffffffu, dbu1, 2);
         if (t == 0) {
@@ -228,8 +235,15 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             sm[BD_RED + nh * 64 + r1] = dbu1;
         }
         __syncthreads();
-        if (tid < 64) scr[SCR_DBU + tid] = sm[BD_RED + tid] + sm[BD_RED + 64 + tid];
-        if (tid < 128) scr[SCR_DD + tid] = dD_part;
+        if (tid < 64) {
+            float v = 0.f;
+#pragma unroll
+            for (int x = 0; x < BD_NQ; ++x) v += sm[BD_RED + x * 64 + tid];
+            scr[SCR_DBU + tid] = v;
+        }
+#pragma unroll
+        for (int o = 1; o < BD_NQ; o <<= 1) dD_part += __shfl_xor_sync(0xffffffffu, dD_part, o);
+        if (tid % BD_NQ == 0) scr[SCR_DD + tid / BD_NQ] = dD_part;
     }
 }
 

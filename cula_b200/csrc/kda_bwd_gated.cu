@@ -20,21 +20,35 @@
 
 namespace kda {
 
-constexpr int BG_THREADS = 256;
+constexpr int BG_THREADS = 512;
+constexpr int BG_WARPS = BG_THREADS / 32;
+constexpr int BG_NQ = BG_WARPS / 4;              // column groups in the GEMM phases (a warp = 16-row tile x column group)
+constexpr int BG_NT64 = 64 / BG_NQ / 8;          // n-tiles per warp over 64 columns
+constexpr int BG_NT128 = 128 / BG_NQ / 8;        // n-tiles per warp over 128 columns
+constexpr int BG_NT6 = 128 / BG_WARPS / 8;       // n-tiles per warp in the Gram VJPs (a warp owns 128 / BG_WARPS channels)
+constexpr int BG_PASS_ROWS = BG_THREADS / 16;    // rows per pass of the wide loads (16 threads per row)
+constexpr int BG_SEG = BG_THREADS / 128;         // row segments of the cumulative sums (a thread per channel and segment)
+constexpr int BG_SEG_ROWS = 64 / BG_SEG;
 constexpr int AR = 68;                         // padded row of the 64x64 fp32 matrices
-constexpr int AS = 132;                        // padded row of the 64x128 fp32 matrices
+constexpr int AS = 136;                        // padded row of the 64x128 fp32 matrices: both fragment patterns
+                                               // (8 rows x 4 columns, 4 rows x 8 columns) hit 32 distinct banks
+constexpr int GS = 136;                        // row of the gate matrix (floats), same reason
+constexpr int QS = 136;                        // row of the bf16 q / k copies (elements): 68 words
 // shared memory map (floats)
 constexpr int BG_G = 0;                        // G    [64][128] log2 cumulative gate
-constexpr int BG_ACC1 = BG_G + 8192;           // dW, later dq-hat accumulator            [64][132]
+constexpr int BG_ACC1 = BG_G + 64 * GS;           // dW, later dq-hat accumulator            [64][132]
 constexpr int BG_ACC2 = BG_ACC1 + 64 * AS;     // dk-hat accumulator
 constexpr int BG_ACC3 = BG_ACC2 + 64 * AS;     // X, later dG accumulator
-constexpr int BG_QK = BG_ACC3 + 64 * AS;       // q raw, k raw as bf16 [64][128] each (8192 floats total)
-constexpr int BG_A = BG_QK + 8192;             // A [64][68]
+constexpr int BG_QK = BG_ACC3 + 64 * AS;       // q raw, k raw as bf16 [64][QS] each
+constexpr int BG_A = BG_QK + 64 * QS;             // A [64][68]
 constexpr int BG_C1 = BG_A + 64 * AR;          // T1, later cP = scale * dPs          [64][68]
 constexpr int BG_C2 = BG_C1 + 64 * AR;         // dA, later cR = beta_i * dL          [64][68]
 constexpr int BG_MISC = BG_C2 + 64 * AR;
-constexpr int MS_RSTDQ = 0, MS_RSTDK = 64, MS_BETA = 128, MS_DBETA = 192, MS_HALF = 256, MS_RED = 384,
-              MS_PBETA = 400 /* [2][64] */, MS_PGL = 528 /* [4][128] */, MS_COL = 1040 /* [128] */, MS_END = 1168;
+constexpr int MS_RSTDQ = 0, MS_RSTDK = 64, MS_BETA = 128, MS_DBETA = 192, MS_RED = 256 /* [BG_WARPS] */,
+              MS_PBETA = 288 /* [BG_NQ][64] */, MS_PGL = MS_PBETA + BG_NQ * 64 /* [4][128] */,
+              MS_HALF = MS_PGL /* [BG_SEG][128], used before and after the lifetime of MS_PGL */,
+              MS_COL = MS_PGL + 512 /* [128] */, MS_END = MS_COL + 128;
+static_assert(BG_SEG <= 4, "segment totals share the 512 floats of MS_PGL");
 constexpr int BG_FLOATS = BG_MISC + MS_END;
 constexpr int BG_SMEM = BG_FLOATS * 4;
 
@@ -72,7 +86,7 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     float* acc2 = sm + BG_ACC2;
     float* acc3 = sm + BG_ACC3;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(sm + BG_QK);
-    __nv_bfloat16* sK = sQ + 64 * 128;
+    __nv_bfloat16* sK = sQ + 64 * QS;
     float* sA = sm + BG_A;
     float* c1 = sm + BG_C1;
     float* c2 = sm + BG_C2;
@@ -103,10 +117,14 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     for (int e = 0; e < 8; ++e)
         bias[e] = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] : 0.f;
 
+    // the scratch record and M are first read several phases from now: pull them into L2 meanwhile
+    for (int i = tid; i < (BWD_SCRATCH_FLOATS + 31) / 32; i += BG_THREADS) prefetch_l2(scr + 32 * i);
+    if (tid < 128) prefetch_l2(p.mkk + tile_idx * 4096 + 32 * tid);
+
     // ---- 1a. wide loads: gate activation -> sG (log2 domain, zero for padding rows); q, k -> bf16 copies + norms ----
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-        const int row = (tid >> 4) + 16 * n;
+    for (int n = 0; n < 64 / BG_PASS_ROWS; ++n) {
+        const int row = (tid >> 4) + BG_PASS_ROWS * n;
         const size_t off = base + (size_t)row * tok_stride + 4 * pc;
         float gv[8];
         uint2 q0 = make_uint2(0, 0), q1 = q0, k0 = q0, k1 = q0;
@@ -135,12 +153,12 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
 #pragma unroll
         for (int e = 0; e < 8; ++e)
             a[e] = (row < ci.valid) ? RCP_LN2 * bg_gate(gv[e], bias[e], alpha, p.gate_mode, p.lower_bound) : 0.f;
-        *reinterpret_cast<float4*>(sG + row * DK + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
-        *reinterpret_cast<float4*>(sG + row * DK + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
-        *reinterpret_cast<uint2*>(sQ + row * DK + 4 * pc) = q0;
-        *reinterpret_cast<uint2*>(sQ + row * DK + 64 + 4 * pc) = q1;
-        *reinterpret_cast<uint2*>(sK + row * DK + 4 * pc) = k0;
-        *reinterpret_cast<uint2*>(sK + row * DK + 64 + 4 * pc) = k1;
+        *reinterpret_cast<float4*>(sG + row * GS + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<float4*>(sG + row * GS + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
+        *reinterpret_cast<uint2*>(sQ + row * QS + 4 * pc) = q0;
+        *reinterpret_cast<uint2*>(sQ + row * QS + 64 + 4 * pc) = q1;
+        *reinterpret_cast<uint2*>(sK + row * QS + 4 * pc) = k0;
+        *reinterpret_cast<uint2*>(sK + row * QS + 64 + 4 * pc) = k1;
         float sq = 0.f, sk = 0.f;
         {
             const uint32_t qw[4] = {q0.x, q0.y, q1.x, q1.y}, kw[4] = {k0.x, k0.y, k1.x, k1.y};
@@ -179,22 +197,23 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         *reinterpret_cast<float4*>(sA + row * AR + c4) = make_float4(bg_tf32(a.x), bg_tf32(a.y), bg_tf32(a.z), bg_tf32(a.w));
     }
     __syncthreads();
-    // ---- 1b. cumulative sum down the rows (two halves per channel, then the second half adds the first's total) ----
+    // ---- 1b. cumulative sum down the rows (a row segment per thread, then the earlier segments' totals are added) ----
     {
-        const int d = tid & 127, half = tid >> 7;
+        const int d = tid & 127, seg = tid >> 7;
         float run = 0.f;
 #pragma unroll 8
-        for (int r = 0; r < 32; ++r) {
-            const int row = half * 32 + r;
-            run += sG[row * DK + d];
-            sG[row * DK + d] = run;
+        for (int r = 0; r < BG_SEG_ROWS; ++r) {
+            const int row = seg * BG_SEG_ROWS + r;
+            run += sG[row * GS + d];
+            sG[row * GS + d] = run;
         }
-        if (half == 0) sHalf[d] = run;
+        sHalf[seg * 128 + d] = run;
         __syncthreads();
-        if (half == 1) {
-            const float t0 = sHalf[d];
+        float t0 = 0.f;
+        for (int s2 = 0; s2 < seg; ++s2) t0 += sHalf[s2 * 128 + d];
+        if (seg > 0) {
 #pragma unroll 8
-            for (int r = 32; r < 64; ++r) sG[r * DK + d] += t0;
+            for (int r = 0; r < BG_SEG_ROWS; ++r) sG[(seg * BG_SEG_ROWS + r) * GS + d] += t0;
         }
     }
     __syncthreads();
@@ -208,34 +227,34 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         float x[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-            x[e] = bg_tf32(bk * __bfloat162float(sK[row * DK + c4 + e]) * fast_exp2(sG[row * DK + c4 + e]));
+            x[e] = bg_tf32(bk * __bfloat162float(sK[row * QS + c4 + e]) * fast_exp2(sG[row * GS + c4 + e]));
         *reinterpret_cast<float4*>(acc3 + row * AS + c4) = make_float4(x[0], x[1], x[2], x[3]);
     }
     __syncthreads();
 
-    const int mt = warp & 3, nh = warp >> 2;     // 16-row tile and column half of this warp in the GEMM phases
+    const int mt = warp & 3, nh = warp >> 2;     // 16-row tile and column group of this warp in the GEMM phases
     const int r0 = 16 * mt + g8, r1 = r0 + 8;
 
     // ---- 3. dA = dAu + stril(dW X^T) -> c2 (zero on and above the diagonal) ----
     {
-        float acc[4][4];
+        float acc[BG_NT64][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-        if (32 * nh <= 16 * mt + 15) {
+        for (int nt = 0; nt < BG_NT64; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        if (8 * BG_NT64 * nh <= 16 * mt + 15) {
 #pragma unroll 4
             for (int ks = 0; ks < 16; ++ks) {
                 const int k0 = 8 * ks;
                 const float fa[4] = {acc1[r0 * AS + k0 + t4], acc1[r1 * AS + k0 + t4], acc1[r0 * AS + k0 + t4 + 4], acc1[r1 * AS + k0 + t4 + 4]};
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    const int j = 32 * nh + 8 * nt + g8;
+                for (int nt = 0; nt < BG_NT64; ++nt) {
+                    const int j = 8 * BG_NT64 * nh + 8 * nt + g8;
                     bg_mma(acc[nt], fa, acc3[j * AS + k0 + t4], acc3[j * AS + k0 + t4 + 4]);
                 }
             }
         }
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = 32 * nh + 8 * nt + 2 * t4;
+        for (int nt = 0; nt < BG_NT64; ++nt) {
+            const int col = 8 * BG_NT64 * nh + 8 * nt + 2 * t4;
             const float2 u0 = *reinterpret_cast<const float2*>(scr + SCR_DAU + r0 * BT + col);
             const float2 u1 = *reinterpret_cast<const float2*>(scr + SCR_DAU + r1 * BT + col);
             c2[r0 * AR + col] = (col < r0) ? bg_tf32(acc[nt][0] + u0.x) : 0.f;
@@ -247,21 +266,21 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     __syncthreads();
     // ---- 4a. T1 = dA A^T -> c1 ----
     {
-        float acc[4][4];
+        float acc[BG_NT64][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        for (int nt = 0; nt < BG_NT64; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
         for (int ks = 0; ks < 2 * mt + 2; ++ks) {          // dA[i][j] = 0 for j >= i: later k-steps contribute nothing
             const int k0 = 8 * ks;
             const float fa[4] = {c2[r0 * AR + k0 + t4], c2[r1 * AR + k0 + t4], c2[r0 * AR + k0 + t4 + 4], c2[r1 * AR + k0 + t4 + 4]};
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int mm = 32 * nh + 8 * nt + g8;
+            for (int nt = 0; nt < BG_NT64; ++nt) {
+                const int mm = 8 * BG_NT64 * nh + 8 * nt + g8;
                 bg_mma(acc[nt], fa, sA[mm * AR + k0 + t4], sA[mm * AR + k0 + t4 + 4]);
             }
         }
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = 32 * nh + 8 * nt + 2 * t4;
+        for (int nt = 0; nt < BG_NT64; ++nt) {
+            const int col = 8 * BG_NT64 * nh + 8 * nt + 2 * t4;
             c1[r0 * AR + col] = bg_tf32(acc[nt][0]);
             c1[r0 * AR + col + 1] = bg_tf32(acc[nt][1]);
             c1[r1 * AR + col] = bg_tf32(acc[nt][2]);
@@ -271,15 +290,15 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     __syncthreads();
     // ---- 4b. dL = -stril(A^T T1); dbeta += rowsum(dL * M); cR = beta_i dL -> c2 ----
     {
-        float acc[4][4];
+        float acc[BG_NT64][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        for (int nt = 0; nt < BG_NT64; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
         for (int ks = 2 * mt; ks < 8; ++ks) {              // A[m][i] = 0 for m < i
             const int k0 = 8 * ks;
             const float fa[4] = {sA[(k0 + t4) * AR + r0], sA[(k0 + t4) * AR + r1], sA[(k0 + t4 + 4) * AR + r0], sA[(k0 + t4 + 4) * AR + r1]};
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int j = 32 * nh + 8 * nt + g8;
+            for (int nt = 0; nt < BG_NT64; ++nt) {
+                const int j = 8 * BG_NT64 * nh + 8 * nt + g8;
                 bg_mma(acc[nt], fa, c1[(k0 + t4) * AR + j], c1[(k0 + t4 + 4) * AR + j]);
             }
         }
@@ -287,8 +306,8 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         const float* mk = p.mkk + tile_idx * 4096;
         float db0 = 0.f, db1 = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = 32 * nh + 8 * nt + 2 * t4;
+        for (int nt = 0; nt < BG_NT64; ++nt) {
+            const int col = 8 * BG_NT64 * nh + 8 * nt + 2 * t4;
             const float2 m0 = *reinterpret_cast<const float2*>(mk + r0 * BT + col);
             const float2 m1 = *reinterpret_cast<const float2*>(mk + r1 * BT + col);
             const float v00 = (col < r0) ? -acc[nt][0] : 0.f, v01 = (col + 1 < r0) ? -acc[nt][1] : 0.f;
@@ -308,7 +327,12 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         }
     }
     __syncthreads();
-    if (tid < 64) sDbeta[tid] += pBeta[tid] + pBeta[64 + tid];
+    if (tid < 64) {
+        float v = 0.f;
+#pragma unroll
+        for (int x = 0; x < BG_NQ; ++x) v += pBeta[x * 64 + tid];
+        sDbeta[tid] += v;
+    }
     for (int x = tid; x < 64 * 16; x += BG_THREADS) {      // cP = scale * dPs -> c1 (T1 is no longer needed)
         const int row = x >> 4, c4 = (x & 15) * 4;
         const float4 v = *reinterpret_cast<const float4*>(scr + SCR_DPS + row * BT + c4);
@@ -318,15 +342,15 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
 
     // ---- 5. Zw = A^T dW (gradient w.r.t. X); initial values of the dq-hat, dk-hat and dG accumulators ----
     {
-        float zw[8][4];
+        float zw[BG_NT128][4];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) zw[nt][0] = zw[nt][1] = zw[nt][2] = zw[nt][3] = 0.f;
+        for (int nt = 0; nt < BG_NT128; ++nt) zw[nt][0] = zw[nt][1] = zw[nt][2] = zw[nt][3] = 0.f;
         for (int ks = 2 * mt; ks < 8; ++ks) {
             const int k0 = 8 * ks;
             const float fa[4] = {sA[(k0 + t4) * AR + r0], sA[(k0 + t4) * AR + r1], sA[(k0 + t4 + 4) * AR + r0], sA[(k0 + t4 + 4) * AR + r1]};
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const int d = 64 * nh + 8 * nt + g8;
+            for (int nt = 0; nt < BG_NT128; ++nt) {
+                const int d = 8 * BG_NT128 * nh + 8 * nt + g8;
                 bg_mma(zw[nt], fa, acc1[(k0 + t4) * AS + d], acc1[(k0 + t4 + 4) * AS + d]);
             }
         }
@@ -335,18 +359,18 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         const float rq[2] = {rstd_q[r0], rstd_q[r1]}, rk[2] = {rstd_k[r0], rstd_k[r1]};
         float dbw[2] = {0.f, 0.f};
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            const int col = 64 * nh + 8 * nt + 2 * t4;
-            const float2 gl = *reinterpret_cast<const float2*>(sG + 63 * DK + col);
+        for (int nt = 0; nt < BG_NT128; ++nt) {
+            const int col = 8 * BG_NT128 * nh + 8 * nt + 2 * t4;
+            const float2 gl = *reinterpret_cast<const float2*>(sG + 63 * GS + col);
             float cs0 = 0.f, cs1 = 0.f;                    // column sums of dKg * Kg over this thread's two rows
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
                 const int row = rr ? r1 : r0;
-                const float2 gi = *reinterpret_cast<const float2*>(sG + row * DK + col);
+                const float2 gi = *reinterpret_cast<const float2*>(sG + row * GS + col);
                 const float2 dqg = *reinterpret_cast<const float2*>(scr + SCR_DQG + row * DK + col);
                 const float2 dkg = *reinterpret_cast<const float2*>(scr + SCR_DKG + row * DK + col);
-                const float2 qf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + row * DK + col));
-                const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * DK + col));
+                const float2 qf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + row * QS + col));
+                const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * QS + col));
                 const float gg[2] = {gi.x, gi.y}, gls[2] = {gl.x, gl.y}, dq2[2] = {dqg.x, dqg.y}, dk2[2] = {dkg.x, dkg.y};
                 const float qh[2] = {qf.x * rq[rr], qf.y * rq[rr]}, kh[2] = {kf.x * rk[rr], kf.y * rk[rr]};
 #pragma unroll
@@ -380,38 +404,45 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         }
     }
     __syncthreads();
-    if (tid < 64) sDbeta[tid] += pBeta[tid] + pBeta[64 + tid];
+    if (tid < 64) {
+        float v = 0.f;
+#pragma unroll
+        for (int x = 0; x < BG_NQ; ++x) v += pBeta[x * 64 + tid];
+        sDbeta[tid] += v;
+    }
     if (tid < 128) {   // g_last sits in row 63 (padding rows repeat the last real value): fold its gradient in there
         const float dgl = (pGl[tid] + pGl[128 + tid]) + (pGl[256 + tid] + pGl[384 + tid]) +
-                          fast_exp2(sG[63 * DK + tid]) * scr[SCR_DD + tid];
+                          fast_exp2(sG[63 * GS + tid]) * scr[SCR_DD + tid];
         acc3[63 * AS + tid] += dgl;
     }
     __syncthreads();
 
-    // ---- 6. VJPs of the gated Gram matrices. Warp w owns key channels 16w..16w+15 for all 64 rows; the same
+    // ---- 6. VJPs of the gated Gram matrices. Warp w owns 128 / BG_WARPS key channels for all 64 rows; the same
     //         thread owns the same (row, channel) cells in the row-side and column-side updates: no synchronisation ----
     {
-        const int dB0 = 16 * warp + g8;                   // channel of this lane's B-fragment column (n-tile 0; +8 for n-tile 1)
+        const int dB0 = 8 * BG_NT6 * warp + g8;          // channel of this lane's B-fragment column in n-tile 0 (+8 per n-tile)
 #pragma unroll 1
         for (int I = 0; I < 4; ++I) {                     // row side: rows of block I against columns j < 16(I+1)
-            float accP[2][4], accR[2][4];
+            float accP[BG_NT6][4], accR[BG_NT6][4];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+            for (int nt = 0; nt < BG_NT6; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) accP[nt][e] = accR[nt][e] = 0.f;
             const int i0 = 16 * I + g8, i1 = i0 + 8;
-            const float rI0 = sG[16 * I * DK + dB0], rI1 = sG[16 * I * DK + dB0 + 8];
+            float rIv[BG_NT6];
+#pragma unroll
+            for (int nt = 0; nt < BG_NT6; ++nt) rIv[nt] = sG[16 * I * GS + dB0 + 8 * nt];
             for (int ks = 0; ks < 2 * I + 2; ++ks) {
                 const int j0 = 8 * ks + t4, j1 = j0 + 4;
                 const float aP[4] = {c1[i0 * AR + j0], c1[i1 * AR + j0], c1[i0 * AR + j1], c1[i1 * AR + j1]};
                 const float aR[4] = {c2[i0 * AR + j0], c2[i1 * AR + j0], c2[i0 * AR + j1], c2[i1 * AR + j1]};
                 const float k0s = rstd_k[j0], k1s = rstd_k[j1];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+                for (int nt = 0; nt < BG_NT6; ++nt) {
                     const int d = dB0 + 8 * nt;
-                    const float rI = nt ? rI1 : rI0;
-                    const float b0 = __bfloat162float(sK[j0 * DK + d]) * k0s * fast_exp2(fminf(rI - sG[j0 * DK + d], 120.f));
-                    const float b1 = __bfloat162float(sK[j1 * DK + d]) * k1s * fast_exp2(fminf(rI - sG[j1 * DK + d], 120.f));
+                    const float rI = rIv[nt];
+                    const float b0 = __bfloat162float(sK[j0 * QS + d]) * k0s * fast_exp2(fminf(rI - sG[j0 * GS + d], 120.f));
+                    const float b1 = __bfloat162float(sK[j1 * QS + d]) * k1s * fast_exp2(fminf(rI - sG[j1 * GS + d], 120.f));
                     const float h0 = bg_tf32(b0), h1 = bg_tf32(b1), l0 = bg_tf32(b0 - h0), l1 = bg_tf32(b1 - h1);
                     bg_mma(accP[nt], aP, l0, l1);
                     bg_mma(accP[nt], aP, h0, h1);
@@ -420,15 +451,15 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
                 }
             }
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const int col = 16 * warp + 8 * nt + 2 * t4;
-                const float2 rI = *reinterpret_cast<const float2*>(sG + 16 * I * DK + col);
+            for (int nt = 0; nt < BG_NT6; ++nt) {
+                const int col = 8 * BG_NT6 * warp + 8 * nt + 2 * t4;
+                const float2 rI = *reinterpret_cast<const float2*>(sG + 16 * I * GS + col);
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                     const int row = rr ? i1 : i0;
-                    const float2 gi = *reinterpret_cast<const float2*>(sG + row * DK + col);
-                    const float2 qf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + row * DK + col));
-                    const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * DK + col));
+                    const float2 gi = *reinterpret_cast<const float2*>(sG + row * GS + col);
+                    const float2 qf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + row * QS + col));
+                    const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * QS + col));
                     const float f0 = fast_exp2(gi.x - rI.x), f1 = fast_exp2(gi.y - rI.y);
                     const float dq0 = f0 * accP[nt][2 * rr], dq1 = f1 * accP[nt][2 * rr + 1];
                     const float dk0 = f0 * accR[nt][2 * rr], dk1 = f1 * accR[nt][2 * rr + 1];
@@ -443,36 +474,38 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
         }
 #pragma unroll 1
         for (int J = 0; J < 4; ++J) {                     // column side: columns of block J against rows i >= 16J
-            float accC[2][4];
+            float accC[BG_NT6][4];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+            for (int nt = 0; nt < BG_NT6; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) accC[nt][e] = 0.f;
             const int jc0 = 16 * J + g8, jc1 = jc0 + 8;
-            const float sJ0 = sG[(16 * J + 15) * DK + dB0], sJ1 = sG[(16 * J + 15) * DK + dB0 + 8];
+            float sJv[BG_NT6];
+#pragma unroll
+            for (int nt = 0; nt < BG_NT6; ++nt) sJv[nt] = sG[(16 * J + 15) * GS + dB0 + 8 * nt];
             for (int ks = 2 * J; ks < 8; ++ks) {
                 const int ia = 8 * ks + t4, ib = ia + 4;
                 const float aP[4] = {c1[ia * AR + jc0], c1[ia * AR + jc1], c1[ib * AR + jc0], c1[ib * AR + jc1]};
                 const float aR[4] = {c2[ia * AR + jc0], c2[ia * AR + jc1], c2[ib * AR + jc0], c2[ib * AR + jc1]};
                 const float qa = rstd_q[ia], qb = rstd_q[ib], ka = rstd_k[ia], kb = rstd_k[ib];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+                for (int nt = 0; nt < BG_NT6; ++nt) {
                     const int d = dB0 + 8 * nt;
-                    const float sJ = nt ? sJ1 : sJ0;
-                    const float ea = fast_exp2(fminf(sG[ia * DK + d] - sJ, 120.f)), eb = fast_exp2(fminf(sG[ib * DK + d] - sJ, 120.f));
-                    bg_mma_split(accC[nt], aP, __bfloat162float(sQ[ia * DK + d]) * qa * ea, __bfloat162float(sQ[ib * DK + d]) * qb * eb);
-                    bg_mma_split(accC[nt], aR, __bfloat162float(sK[ia * DK + d]) * ka * ea, __bfloat162float(sK[ib * DK + d]) * kb * eb);
+                    const float sJ = sJv[nt];
+                    const float ea = fast_exp2(fminf(sG[ia * GS + d] - sJ, 120.f)), eb = fast_exp2(fminf(sG[ib * GS + d] - sJ, 120.f));
+                    bg_mma_split(accC[nt], aP, __bfloat162float(sQ[ia * QS + d]) * qa * ea, __bfloat162float(sQ[ib * QS + d]) * qb * eb);
+                    bg_mma_split(accC[nt], aR, __bfloat162float(sK[ia * QS + d]) * ka * ea, __bfloat162float(sK[ib * QS + d]) * kb * eb);
                 }
             }
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const int col = 16 * warp + 8 * nt + 2 * t4;
-                const float2 sJ = *reinterpret_cast<const float2*>(sG + (16 * J + 15) * DK + col);
+            for (int nt = 0; nt < BG_NT6; ++nt) {
+                const int col = 8 * BG_NT6 * warp + 8 * nt + 2 * t4;
+                const float2 sJ = *reinterpret_cast<const float2*>(sG + (16 * J + 15) * GS + col);
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                     const int row = rr ? jc1 : jc0;
-                    const float2 gj = *reinterpret_cast<const float2*>(sG + row * DK + col);
-                    const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * DK + col));
+                    const float2 gj = *reinterpret_cast<const float2*>(sG + row * GS + col);
+                    const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * QS + col));
                     const float d0 = fast_exp2(sJ.x - gj.x) * accC[nt][2 * rr], d1 = fast_exp2(sJ.y - gj.y) * accC[nt][2 * rr + 1];
                     acc2[row * AS + col] += d0;
                     acc2[row * AS + col + 1] += d1;
@@ -484,22 +517,23 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     }
     __syncthreads();
 
-    // ---- 7a. reverse cumulative sum of dG down the rows, in place (two halves per channel) ----
+    // ---- 7a. reverse cumulative sum of dG down the rows, in place (a row segment per thread, then the later segments' totals) ----
     {
-        const int d = tid & 127, half = tid >> 7;
+        const int d = tid & 127, seg = tid >> 7;
         float run = 0.f;
 #pragma unroll 8
-        for (int r = 31; r >= 0; --r) {
-            const int row = half * 32 + r;
+        for (int r = BG_SEG_ROWS - 1; r >= 0; --r) {
+            const int row = seg * BG_SEG_ROWS + r;
             run += acc3[row * AS + d];
             acc3[row * AS + d] = run;
         }
-        if (half == 1) sHalf[d] = run;
+        sHalf[seg * 128 + d] = run;
         __syncthreads();
-        if (half == 0) {
-            const float t1 = sHalf[d];
+        float t1 = 0.f;
+        for (int s2 = BG_SEG - 1; s2 > seg; --s2) t1 += sHalf[s2 * 128 + d];
+        if (seg < BG_SEG - 1) {
 #pragma unroll 8
-            for (int r = 0; r < 32; ++r) acc3[r * AS + d] += t1;
+            for (int r = 0; r < BG_SEG_ROWS; ++r) acc3[(seg * BG_SEG_ROWS + r) * AS + d] += t1;
         }
     }
     __syncthreads();
@@ -510,8 +544,8 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
 #pragma unroll
         for (int e = 0; e < 8; ++e) colsum[e] = 0.f;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int row = (tid >> 4) + 16 * n;
+        for (int n = 0; n < 64 / BG_PASS_ROWS; ++n) {
+            const int row = (tid >> 4) + BG_PASS_ROWS * n;
             if (row >= ci.valid) continue;
             const size_t off = base + (size_t)row * tok_stride + 4 * pc;
             float gv[8], dx[8];
@@ -576,20 +610,24 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     __syncthreads();
     if (p.gate_mode != GATE_NONE) {
         if (p.ddt_bias && tid < 128) atomicAdd(&p.ddt_bias[h * DK + tid], sCol[tid]);
-        if (p.dA_log && tid == 0)
-            atomicAdd(&p.dA_log[h], ((sRed[0] + sRed[1]) + (sRed[2] + sRed[3])) + ((sRed[4] + sRed[5]) + (sRed[6] + sRed[7])));
+        if (p.dA_log && tid == 0) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < BG_WARPS; ++w) v += sRed[w];
+            atomicAdd(&p.dA_log[h], v);
+        }
     }
 
     // ---- 8. L2-norm VJP and stores of dq, dk (a warp per row); dbeta ----
-    for (int r = 0; r < 8; ++r) {
-        const int row = warp * 8 + r;
+    for (int r = 0; r < 64 / BG_WARPS; ++r) {
+        const int row = warp * (64 / BG_WARPS) + r;
         if (row >= ci.valid) continue;
         float dq[4], dk[4], qh[4], kh[4];
         float sq = 0.f, sk = 0.f;
         const float4 a1 = *reinterpret_cast<const float4*>(acc1 + row * AS + lane * 4);
         const float4 a2 = *reinterpret_cast<const float4*>(acc2 + row * AS + lane * 4);
-        const uint2 qr = *reinterpret_cast<const uint2*>(sQ + row * DK + lane * 4);
-        const uint2 kr = *reinterpret_cast<const uint2*>(sK + row * DK + lane * 4);
+        const uint2 qr = *reinterpret_cast<const uint2*>(sQ + row * QS + lane * 4);
+        const uint2 kr = *reinterpret_cast<const uint2*>(sK + row * QS + lane * 4);
         dq[0] = a1.x * gs_inv; dq[1] = a1.y * gs_inv; dq[2] = a1.z * gs_inv; dq[3] = a1.w * gs_inv;
         dk[0] = a2.x * gs_inv; dk[1] = a2.y * gs_inv; dk[2] = a2.z * gs_inv; dk[3] = a2.w * gs_inv;
         float2 f;

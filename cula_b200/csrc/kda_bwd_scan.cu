@@ -32,10 +32,25 @@ constexpr int BS_DO = TP_HEAD_BYTES;
 __global__ void kda_grad_amax_kernel(const __nv_bfloat16* d_o, size_t n_do, const float* dht, size_t n_dht,
                                      unsigned int* amax_bits) {
     float m = 0.f;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_do; i += (size_t)gridDim.x * blockDim.x)
-        m = fmaxf(m, fabsf(__bfloat162float(d_o[i])));
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_dht; i += (size_t)gridDim.x * blockDim.x)
-        m = fmaxf(m, fabsf(dht[i]));
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
+    // 16-byte loads over the bulk (the tensors come 16-byte aligned from the C ABI), scalar loads over the tail
+    const uint4* do4 = reinterpret_cast<const uint4*>(d_o);
+    for (size_t i = tid; i < n_do / 8; i += nthr) {
+        const uint4 v = do4[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf16(w[e]);
+            m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+    for (size_t i = (n_do / 8) * 8 + tid; i < n_do; i += nthr) m = fmaxf(m, fabsf(__bfloat162float(d_o[i])));
+    const float4* h4 = reinterpret_cast<const float4*>(dht);
+    for (size_t i = tid; i < n_dht / 4; i += nthr) {
+        const float4 v = h4[i];
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    for (size_t i = (n_dht / 4) * 4 + tid; i < n_dht; i += nthr) m = fmaxf(m, fabsf(dht[i]));
 #pragma unroll
     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((threadIdx.x & 31) == 0 && m > 0.f && m < INFINITY) atomicMax(amax_bits, __float_as_uint(m));
@@ -295,7 +310,7 @@ extern "C" int kda_launch_grad_scale(const void* d_o, size_t n_do, const float* 
     using namespace kda;
     cudaError_t e = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream);
     if (e != cudaSuccess) return (int)e;
-    kda_grad_amax_kernel<<<592, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(d_o), n_do, dht, dht ? n_dht : 0,
+    kda_grad_amax_kernel<<<1184, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(d_o), n_do, dht, dht ? n_dht : 0,
                                                   amax_bits);
     kda_grad_scale_kernel<<<1, 1, 0, stream>>>(amax_bits, gscale);
     return (int)cudaGetLastError();

@@ -243,8 +243,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
             __syncwarp();
         }
 
-        // ---- o^T = S^T qg^T + v_new^T Aqk^T ----
-        if (!TRANSITION) {
+        // ---- o^T = S^T qg^T + v_new^T Aqk^T (skipped when no output is wanted: backward recomputation) ----
+        if (!TRANSITION && (!STORE_HV || p.o != nullptr)) {
             float oacc[8][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) oacc[nt][0] = oacc[nt][1] = oacc[nt][2] = oacc[nt][3] = 0.f;

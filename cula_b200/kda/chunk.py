@@ -48,7 +48,7 @@ def _gate_mode(use_gate_in_kernel, safe_gate, lower_bound):
 
 def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
                   use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias,
-                  store_states=False, store_akk=False, store_for_backward=False):
+                  store_states=False, store_akk=False, store_for_backward=False, want_output=True):
     """Forward orchestration (the role of cula/kda/chunk_fwd.py:39-152): the chunk-parallel stage
     writes one tile pack per (chunk, head); the scan consumes them, carries the fp32 state and
     writes ``o``. Returns a dict with o, final_state and the intermediates kept for backward."""
@@ -63,11 +63,11 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
         n_seqs, num_chunks = tab.n_seqs, tab.num_chunks
         cu_p, ci_p, co_p, so_p = (tab.cu_seqlens.data_ptr(), tab.chunk_indices.data_ptr(),
                                   tab.chunk_offsets.data_ptr(), tab.seq_order.data_ptr())
-        o = torch.zeros_like(v)        # rows past cu_seqlens[-1] stay zero (cula/kda/chunk_fwd.py:129-130)
+        o = torch.zeros_like(v) if want_output else None   # rows past cu_seqlens[-1] stay zero (cula/kda/chunk_fwd.py:129-130)
     else:
         n_seqs, num_chunks = B, B * ((T + CHUNK - 1) // CHUNK)
         cu_p = ci_p = co_p = so_p = None
-        o = torch.empty_like(v)
+        o = torch.empty_like(v) if want_output else None
     tiles = torch.empty(num_chunks * H * lib.cula_kda_tile_pack_bytes(), dtype=torch.uint8, device=dev)
     akk = (torch.empty(num_chunks * H, CHUNK, CHUNK, dtype=torch.float32, device=dev)
            if (store_akk or store_for_backward) else None)
@@ -88,7 +88,7 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     if store_states or store_for_backward:
         vnew = torch.empty(num_chunks * H, CHUNK, v.shape[-1], dtype=torch.float16, device=dev)
     _native.check(lib.cula_kda_fwd_scan(
-        tiles.data_ptr(), _ptr(initial_state), o.data_ptr(), _ptr(final_state), _ptr(h), _ptr(vnew), _ptr(h32),
+        tiles.data_ptr(), _ptr(initial_state), _ptr(o), _ptr(final_state), _ptr(h), _ptr(vnew), _ptr(h32),
         cu_p, co_p, so_p, n_seqs, T, H, _status_word(dev).data_ptr(), stream), "cula_kda_fwd_scan")
     return dict(o=o, final_state=final_state, tiles=tiles, akk=akk, mkk=mkk, h=h, h32=h32, vnew=vnew,
                 num_chunks=num_chunks)
@@ -107,7 +107,7 @@ def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, c
     if saved is None:
         saved = chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, False, cu_seqlens, cu_seqlens_cpu,
                               use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias,
-                              store_for_backward=True)
+                              store_for_backward=True, want_output=False)
     if cu_seqlens is not None:
         tab = get_varlen_tables(cu_seqlens, cu_seqlens_cpu)
         n_seqs, num_chunks = tab.n_seqs, tab.num_chunks

@@ -68,7 +68,8 @@ int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* d_v,
  * Replaces chunk_gated_delta_rule_fwd_h(k=kg, w, u, gk, initial_state, output_final_state, cu_seqlens, ...)
  *   (cula/ops/chunk_delta_h.py:1991-2168, called at cula/kda/chunk_fwd.py:111-120) and
  *   chunk_gla_fwd_o(q, v_new, g, A=Aqk, h, o, scale, ...) (cula/ops/fwd_o.py:1755-1852, chunk_fwd.py:131-143).
- * d_h0 / d_ht: [N, H, 128, 128] fp32 or NULL. d_o: [B*T, H, 128] bf16; only rows of real tokens are written.
+ * d_h0 / d_ht: [N, H, 128, 128] fp32 or NULL. d_o: [B*T, H, 128] bf16; only rows of real tokens are written
+ * (d_o may be NULL when d_vnew_out is given: the backward recomputation needs the states, not the output).
  * d_h_out (bf16 [num_chunks*H][128][128], state entering each chunk) and d_vnew_out (fp16
  * [num_chunks*H][64][128]) and d_h32_out (the same states in fp32, for the backward pass) are optional;
  * d_vnew_out must be given whenever a state output is.
