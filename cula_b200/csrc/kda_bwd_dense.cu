@@ -43,14 +43,14 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const float (&a)[4], flo
                    "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
 }
 
-__global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdDenseParams p) {
-    extern __shared__ __align__(16) float sm[];
+// One (chunk, head) tile. next_tile >= 0 names the tile this CTA handles next: its inputs are pulled into L2 midway.
+__device__ __forceinline__ void bd_tile(const BwdDenseParams& p, float* sm, const int tile, const int next_tile) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int mt = warp & 3, nh = warp >> 2;          // 16-row tile, column group
-    const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
+    const int c = tile / p.H, h = tile - c * p.H;
     const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
-    const size_t tile_idx = (size_t)c * p.H + h;
+    const size_t tile_idx = (size_t)tile;
     const size_t tok_stride = (size_t)p.H * DV;
     const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DV;
     const float gs = p.gscale[0], gs_inv = p.gscale[1];
@@ -127,6 +127,28 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
             }
         }
         __syncthreads();
+        // next tile of this CTA: pull its inputs into L2 while the second half computes
+        if (vh == 1 && next_tile >= 0) {
+            const size_t nt_idx = (size_t)next_tile;
+            const int cn = next_tile / p.H, hn = next_tile - cn * p.H;
+            const ChunkInfo cin = chunk_info(cn, p.cu_seqlens, p.chunk_indices, p.T);
+            const size_t nb = (size_t)cin.row0 * tok_stride + (size_t)hn * DV;
+            for (int i = tid; i < 512; i += BD_THREADS) {     // S and dS': 64 KB each, 128-byte lines
+                prefetch_l2(p.h32 + nt_idx * (size_t)(DK * DV) + 32 * i);
+                prefetch_l2(p.ds + nt_idx * (size_t)(DK * DV) + 32 * i);
+            }
+            if (tid < 128) {
+                prefetch_l2(reinterpret_cast<const __half*>(p.vnew) + nt_idx * (size_t)(BT * DV) + 64 * tid);
+                prefetch_l2(reinterpret_cast<const __half*>(p.dvn) + nt_idx * (size_t)(BT * DV) + 64 * tid);
+                prefetch_l2(p.akk + nt_idx * 4096 + 32 * tid);
+            } else if (tid < 256) {
+                const int row = (tid - 128) >> 1, half = tid & 1;
+                if (row < cin.valid) {
+                    prefetch_l2(dOg + nb + (size_t)row * tok_stride + 64 * half);
+                    prefetch_l2(Vg + nb + (size_t)row * tok_stride + 64 * half);
+                }
+            }
+        }
         // ---- dD partial: row k = tid ----
         {
             const int row = tid / BD_NQ, v0 = (tid % BD_NQ) * (64 / BD_NQ);
@@ -247,6 +269,16 @@ __global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdD
     }
 }
 
+// Persistent: CTA b handles tiles b, b + gridDim.x, ... so that the next tile's inputs can be prefetched.
+__global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdDenseParams p, const int num_tiles) {
+    extern __shared__ __align__(16) float sm[];
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int next = tile + gridDim.x;
+        bd_tile(p, sm, tile, next < num_tiles ? next : -1);
+        __syncthreads();                                  // shared memory is reused by the next tile
+    }
+}
+
 }  // namespace kda
 
 extern "C" int kda_launch_bwd_dense(const kda::BwdDenseParams* p, int num_chunks, cudaStream_t stream) {
@@ -254,6 +286,10 @@ extern "C" int kda_launch_bwd_dense(const kda::BwdDenseParams* p, int num_chunks
     if (num_chunks <= 0) return 0;
     cudaError_t e = cudaFuncSetAttribute(kda_bwd_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BD_SMEM);
     if (e != cudaSuccess) return (int)e;
-    kda_bwd_dense_kernel<<<num_chunks * p->H, BD_THREADS, BD_SMEM, stream>>>(*p);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = num_chunks * p->H;
+    kda_bwd_dense_kernel<<<tiles < sms ? tiles : sms, BD_THREADS, BD_SMEM, stream>>>(*p, tiles);
     return (int)cudaGetLastError();
 }

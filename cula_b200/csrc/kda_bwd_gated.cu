@@ -79,8 +79,8 @@ __device__ __forceinline__ float bg_gate(float graw, float bias, float alpha, in
     return -alpha * (x > 20.f ? x : log1pf(__expf(x)));
 }
 
-__global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdGatedParams p) {
-    extern __shared__ __align__(16) float sm[];
+// One (chunk, head) tile. next_tile >= 0 names the tile this CTA handles next: its inputs are pulled into L2 midway.
+__device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, const int tile, const int next_tile) {
     float* sG = sm + BG_G;
     float* acc1 = sm + BG_ACC1;
     float* acc2 = sm + BG_ACC2;
@@ -103,9 +103,9 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g8 = lane >> 2, t4 = lane & 3;
-    const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
+    const int c = tile / p.H, h = tile - c * p.H;
     const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
-    const size_t tile_idx = (size_t)c * p.H + h;
+    const size_t tile_idx = (size_t)tile;
     const size_t tok_stride = (size_t)p.H * DK;
     const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DK;
     const float* scr = p.scratch + tile_idx * (size_t)BWD_SCRATCH_FLOATS;
@@ -116,10 +116,6 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
 #pragma unroll
     for (int e = 0; e < 8; ++e)
         bias[e] = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] : 0.f;
-
-    // the scratch record and M are first read several phases from now: pull them into L2 meanwhile
-    for (int i = tid; i < (BWD_SCRATCH_FLOATS + 31) / 32; i += BG_THREADS) prefetch_l2(scr + 32 * i);
-    if (tid < 128) prefetch_l2(p.mkk + tile_idx * 4096 + 32 * tid);
 
     // ---- 1a. wide loads: gate activation -> sG (log2 domain, zero for padding rows); q, k -> bf16 copies + norms ----
 #pragma unroll
@@ -417,6 +413,36 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     }
     __syncthreads();
 
+    // ---- next tile of this CTA: pull its inputs into L2 while the Gram phase computes (the first tile comes cold) ----
+    if (next_tile >= 0) {
+        const int cn = next_tile / p.H, hn = next_tile - cn * p.H;
+        const ChunkInfo cin = chunk_info(cn, p.cu_seqlens, p.chunk_indices, p.T);
+        const size_t nb = (size_t)cin.row0 * tok_stride + (size_t)hn * DK;
+        const float* nscr = p.scratch + (size_t)next_tile * (size_t)BWD_SCRATCH_FLOATS;
+        for (int i = tid; i < (BWD_SCRATCH_FLOATS + 31) / 32; i += BG_THREADS) prefetch_l2(nscr + 32 * i);
+        if (tid < 64 * 4) {                               // q, k, g rows: 256 B (bf16) or 512 B (fp32 g) each
+            const int row = tid >> 2, part = tid & 3;
+            if (row < cin.valid) {
+                const size_t o = nb + (size_t)row * tok_stride;
+                if (part < 2) {
+                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(part ? p.k : p.q) + o;
+                    prefetch_l2(src);
+                    prefetch_l2(src + 64);
+                } else if (p.g_fp32) {
+                    const float* src = reinterpret_cast<const float*>(p.g) + o + 64 * (part - 2);
+                    prefetch_l2(src);
+                    prefetch_l2(src + 32);
+                } else {
+                    prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.g) + o + 64 * (part - 2));
+                }
+            }
+        } else if (tid < 64 * 4 + 128) {
+            prefetch_l2(p.akk + (size_t)next_tile * 4096 + 32 * (tid - 256));
+        } else {
+            prefetch_l2(p.mkk + (size_t)next_tile * 4096 + 32 * (tid - 384));
+        }
+    }
+
     // ---- 6. VJPs of the gated Gram matrices. Warp w owns 128 / BG_WARPS key channels for all 64 rows; the same
     //         thread owns the same (row, channel) cells in the row-side and column-side updates: no synchronisation ----
     {
@@ -664,6 +690,16 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
     }
 }
 
+// Persistent: CTA b handles tiles b, b + gridDim.x, ... so that the next tile's inputs can be prefetched.
+__global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdGatedParams p, const int num_tiles) {
+    extern __shared__ __align__(16) float sm[];
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int next = tile + gridDim.x;
+        bg_tile(p, sm, tile, next < num_tiles ? next : -1);
+        __syncthreads();                                  // shared memory is reused by the next tile
+    }
+}
+
 }  // namespace kda
 
 extern "C" int kda_launch_bwd_gated(const kda::BwdGatedParams* p, int num_chunks, cudaStream_t stream) {
@@ -672,6 +708,10 @@ extern "C" int kda_launch_bwd_gated(const kda::BwdGatedParams* p, int num_chunks
     if (num_chunks <= 0) return 0;
     cudaError_t e = cudaFuncSetAttribute(kda_bwd_gated_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BG_SMEM);
     if (e != cudaSuccess) return (int)e;
-    kda_bwd_gated_kernel<<<num_chunks * p->H, BG_THREADS, BG_SMEM, stream>>>(*p);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = num_chunks * p->H;
+    kda_bwd_gated_kernel<<<tiles < sms ? tiles : sms, BG_THREADS, BG_SMEM, stream>>>(*p, tiles);
     return (int)cudaGetLastError();
 }

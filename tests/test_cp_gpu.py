@@ -22,8 +22,9 @@ def _oracle(inp):
     return torch.from_numpy(o), torch.from_numpy(ht)
 
 
+@pytest.mark.parametrize("segments", [1, 2])
 @pytest.mark.parametrize("world,T,gate_offset", [(2, 256, -8.0), (4, 1024, -8.0), (3, 64 * 5 + 17, -6.0), (4, 512, 0.0)])
-def test_cp_emulated_ranks_match_oracle(world, T, gate_offset):
+def test_cp_emulated_ranks_match_oracle(world, T, gate_offset, segments):
     from cula_b200.kda import check_status
     from cula_b200.kda.cp import CudaBackend, cp_forward
     H = 4
@@ -35,8 +36,8 @@ def test_cp_emulated_ranks_match_oracle(world, T, gate_offset):
         sl = slice(bounds[r], bounds[r + 1])
         backends.append(CudaBackend(inp["q"][:, sl].cuda(), inp["k"][:, sl].cuda(), inp["v"][:, sl].cuda(),
                                     inp["g"][:, sl].cuda(), inp["beta"][:, sl].cuda(), 128 ** -0.5, True, True, True, -5.0,
-                                    inp["A_log"].cuda(), inp["dt_bias"].cuda()))
-    trans = [b.zeros_transition() if r == world - 1 else b.transition() for r, b in enumerate(backends)]
+                                    inp["A_log"].cuda(), inp["dt_bias"].cuda(), segments=segments))
+    trans = [b.transition() for b in backends]               # [P, H, 128, 128] pairs; some segments are empty here
     stacked = {"C": torch.stack([t[0] for t in trans]), "M": torch.stack([t[1] for t in trans])}
 
     class Replay:                       # the emulated collective: every rank sees the same stacked tensors
@@ -68,14 +69,16 @@ def test_cp_transition_is_the_affine_map_of_the_shard():
     T, H = 320, 2
     inp = make_inputs(1, T, H, seed=4, gate_offset=-8.0, h0_std=1.0)
     d = {k: v.cuda() for k, v in inp.items()}
-    b = CudaBackend(d["q"], d["k"], d["v"], d["g"], d["beta"], 128 ** -0.5, True, True, True, -5.0, d["A_log"], d["dt_bias"])
+    b = CudaBackend(d["q"], d["k"], d["v"], d["g"], d["beta"], 128 ** -0.5, True, True, True, -5.0, d["A_log"], d["dt_bias"],
+                    segments=1)
     C, M = b.transition()
+    C, M = C[0], M[0]
     _, ht = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
                       initial_state=d["initial_state"], output_final_state=True, use_qk_l2norm_in_kernel=True,
                       use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
     pred = torch.matmul(M.double(), d["initial_state"][0].double()) + C.double()
     assert err_ratio(ht[0].double().cpu(), pred.cpu()) <= 2e-3
-    folded = b.fold(C[None], M[None], d["initial_state"], 1)
+    folded = b.fold(C[None], M[None], d["initial_state"], 0, 1)
     assert err_ratio(pred.cpu(), folded.double().cpu()) <= 1e-5
 
 

@@ -14,34 +14,47 @@ from oracle.naive_kda import chunk_kda_oracle, err_ratio, kda_gate, l2norm, make
 
 
 class OracleBackend:
-    """transition / fold / forward of one shard evaluated with the fp32 token recurrence."""
+    """transition / fold / forward of one shard evaluated with the fp32 token recurrence. ``bounds`` cuts the
+    shard into segments (token offsets, [0, ..., T])."""
 
-    def __init__(self, shard):
+    def __init__(self, shard, bounds=None):
         self.q, self.k = l2norm(shard["q"]), l2norm(shard["k"])
         self.v, self.beta = shard["v"].float(), shard["beta"].float()
         self.a = kda_gate(shard["g"], shard["A_log"], shard["dt_bias"], -5.0)
         self.H = self.q.shape[2]
+        self.bounds = bounds if bounds is not None else [0, self.q.shape[1]]
+        self.n_segments = len(self.bounds) - 1
 
-    def zeros_transition(self):
-        z = torch.zeros(self.H, 128, 128)
-        return z, z.clone()
+    def _seg(self, i):
+        sl = slice(self.bounds[i], self.bounds[i + 1])
+        return self.q[:, sl], self.k[:, sl], self.v[:, sl], self.a[:, sl], self.beta[:, sl]
 
     def transition(self):
-        _, C = naive_recurrent_kda(self.q, self.k, self.v, self.a, self.beta, None, None, True)
-        # M: the recurrence is linear in the state when v = 0; push the identity through it
-        eye = torch.eye(128).expand(1, self.H, 128, 128)
-        _, M = naive_recurrent_kda(self.q, self.k, torch.zeros_like(self.v), self.a, self.beta, None, eye, True)
-        return C[0], M[0]
+        Cs, Ms = [], []
+        for i in range(self.n_segments):
+            q, k, v, a, beta = self._seg(i)
+            _, C = naive_recurrent_kda(q, k, v, a, beta, None, None, True)
+            # M: the recurrence is linear in the state when v = 0; push the identity through it
+            eye = torch.eye(128).expand(1, self.H, 128, 128)
+            _, M = naive_recurrent_kda(q, k, torch.zeros_like(v), a, beta, None, eye, True)
+            Cs.append(C[0])
+            Ms.append(M[0])
+        return torch.stack(Cs), torch.stack(Ms)
 
-    def fold(self, C_all, M_all, h0, n_prev):
+    def fold(self, C_all, M_all, h0, start, n):
         S = torch.zeros(self.H, 128, 128) if h0 is None else h0.reshape(self.H, 128, 128).clone()
-        for j in range(n_prev):
+        for j in range(start, start + n):
             S = M_all[j] @ S + C_all[j]
         return S
 
-    def forward(self, s_in, want_final):
-        s_in = None if s_in is None else s_in.reshape(1, self.H, 128, 128)
-        return naive_recurrent_kda(self.q, self.k, self.v, self.a, self.beta, None, s_in, want_final)
+    def forward(self, states, want_final):
+        outs, ht = [], None
+        for i, s_in in enumerate(states):
+            q, k, v, a, beta = self._seg(i)
+            s_in = None if s_in is None else s_in.reshape(1, self.H, 128, 128)
+            o, ht = naive_recurrent_kda(q, k, v, a, beta, None, s_in, want_final)
+            outs.append(o)
+        return torch.cat(outs, dim=1), ht
 
 
 def _free_port():
@@ -50,7 +63,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, T, H, out_dir):
+def _worker(rank, world, port, T, H, out_dir, segmented):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -58,7 +71,9 @@ def _worker(rank, world, port, T, H, out_dir):
         per = T // world
         lo, hi = rank * per, (T if rank == world - 1 else (rank + 1) * per)
         shard = {n: (t[:, lo:hi] if n in ("q", "k", "v", "g", "beta") else t) for n, t in inp.items()}
-        o, ht = cp_forward(OracleBackend(shard), gather_with_group(None), rank, world, inp["initial_state"], True)
+        n_loc = hi - lo
+        bounds = [0, 64, n_loc] if segmented else None       # same segment count on every rank
+        o, ht = cp_forward(OracleBackend(shard, bounds), gather_with_group(None), rank, world, inp["initial_state"], True)
         assert (ht is not None) == (rank == world - 1)
         torch.save((o, ht), os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
@@ -66,10 +81,11 @@ def _worker(rank, world, port, T, H, out_dir):
 
 
 @pytest.mark.timeout(300)
-def test_cp_forward_two_gloo_ranks(tmp_path):
-    world, T, H = 2, 192, 2                      # 128 + 64 tokens; weak gates so the carried state matters
+@pytest.mark.parametrize("segmented", [False, True])
+def test_cp_forward_two_gloo_ranks(tmp_path, segmented):
+    world, T, H = 2, 320, 2                      # 160 + 160 tokens; weak gates so the carried state matters
     port = _free_port()
-    mp.spawn(_worker, args=(world, port, T, H, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, T, H, str(tmp_path), segmented), nprocs=world, join=True)
     parts = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
     o = torch.cat([p[0] for p in parts], dim=1)
     ht = parts[-1][1]
@@ -79,14 +95,16 @@ def test_cp_forward_two_gloo_ranks(tmp_path):
                                      safe_gate=True, lower_bound=-5.0, A_log=inp["A_log"], dt_bias=inp["dt_bias"])
     assert err_ratio(o_ref, o) < 1e-5 and err_ratio(ht_ref, ht) < 1e-5
     # the carried state matters in this fixture: dropping it must be visible
-    o_wrong, _ = OracleBackend({n: (t[:, 128:] if n in ("q", "k", "v", "g", "beta") else t)
-                                for n, t in inp.items()}).forward(None, False)
-    assert err_ratio(o_ref[:, 128:], o_wrong) > 1e-2
+    o_wrong, _ = OracleBackend({n: (t[:, 160:] if n in ("q", "k", "v", "g", "beta") else t)
+                                for n, t in inp.items()}).forward([None], False)
+    assert err_ratio(o_ref[:, 160:], o_wrong) > 1e-2
 
 
 def test_cp_single_rank_is_plain_forward():
     inp = make_inputs(1, 70, 1, seed=1, gate_offset=-6.0, h0_std=0.5)
     o, ht = cp_forward(OracleBackend(inp), None, 0, 1, inp["initial_state"], True)
+    o2, ht2 = cp_forward(OracleBackend(inp, [0, 64, 70]), None, 0, 1, inp["initial_state"], True)   # one rank, two segments
+    assert err_ratio(o, o2) < 1e-6 and err_ratio(ht, ht2) < 1e-6
     o_ref, ht_ref = chunk_kda_oracle(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=inp["initial_state"],
                                      output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
                                      safe_gate=True, lower_bound=-5.0, A_log=inp["A_log"], dt_bias=inp["dt_bias"])
