@@ -25,15 +25,36 @@ constexpr int SCAN_THREADS = (SCAN_CONSUMERS + 1) * 32;
 constexpr int SCAN_SMEM = SCAN_STAGES * SCAN_STAGE_BYTES + SCAN_CONSUMERS * SCAN_STG_BYTES + 64;
 constexpr int ST_U = TP_HEAD_BYTES;                      // offset of the U half inside a stage
 
+// Shared-memory layout of a pipeline stage. The full scan stages the whole head of a tile pack plus one U half and
+// runs one CTA per SM; the transition scan needs only W, KG, DECAY and the U half, packs them tightly, keeps two
+// stages (the producer warp pulls the chunks after those into L2) and so fits two CTAs per SM.
+template <bool TRANSITION>
+struct ScanLayout {
+    static constexpr int STAGES = SCAN_STAGES, STAGE_BYTES = SCAN_STAGE_BYTES;
+    static constexpr int W = TP_W, KG = TP_KG, DECAY = TP_DECAY, U = ST_U;
+    static constexpr int STG = SCAN_CONSUMERS * SCAN_STG_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STG + 64;
+    static constexpr int CTAS_PER_SM = 1;
+};
+template <>
+struct ScanLayout<true> {
+    static constexpr int STAGES = 2;
+    static constexpr int W = 0, KG = 16384, DECAY = 32768, U = 33280, STAGE_BYTES = 41472;
+    static constexpr int STG = 0;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STG + 64;
+    static constexpr int CTAS_PER_SM = 2;
+};
+
 // TRANSITION: the affine action of a whole shard on the state, S_out = M S_in + C, from the same recurrence with
 // four column groups per (sequence, head): groups 0,1 carry C (zero start, normal u; written to p.ht) and groups
 // 2,3 carry the K x K matrix M = prod_c (D_c - kg_c^T w_c) (identity start, u = 0; written to p.m_out). No output
 // rows are produced. Used by context parallelism.
 template <bool STORE_HV, bool TRANSITION>
-__global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(SCAN_THREADS, ScanLayout<TRANSITION>::CTAS_PER_SM) kda_fwd_scan_kernel(const ScanParams p) {
+    using L = ScanLayout<TRANSITION>;
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + SCAN_STAGES * SCAN_STAGE_BYTES + SCAN_CONSUMERS * SCAN_STG_BYTES);
-    uint64_t* empty = full + SCAN_STAGES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES + L::STG);
+    uint64_t* empty = full + L::STAGES;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool is_m = TRANSITION && blockIdx.x >= 2;     // this CTA carries columns of M
     const int vh = blockIdx.x & 1, h = blockIdx.y;
@@ -51,7 +72,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
     const int nchunks = (len + BT - 1) / BT;
 
     if (tid == 0) {
-        for (int s = 0; s < SCAN_STAGES; ++s) {
+        for (int s = 0; s < L::STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], SCAN_CONSUMERS);
         }
@@ -61,6 +82,40 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
 
     if (warp == SCAN_CONSUMERS) {
         // ------------------------------- producer warp -------------------------------
+        if (TRANSITION) {
+            const int u_off = vh ? TP_U1 : TP_U0;
+            for (int c = 0; c < nchunks; ++c) {
+                const int s = c % L::STAGES, use = c / L::STAGES;
+                bool ok = true;
+                if (lane == 0) {
+                    if (use > 0) ok = mbar_wait(&empty[s], (use - 1) & 1);
+                    if (ok) {
+                        const unsigned char* tile = p.tiles + ((size_t)(chunk0 + c) * p.H + h) * TP_BYTES;
+                        unsigned char* dst = smem + s * L::STAGE_BYTES;
+                        mbar_arrive_expect_tx(&full[s], is_m ? L::U : L::STAGE_BYTES);
+                        bulk_g2s(dst + L::W, tile + TP_W, 16384, &full[s]);
+                        bulk_g2s(dst + L::KG, tile + TP_KG, 16384, &full[s]);
+                        bulk_g2s(dst + L::DECAY, tile + TP_DECAY, 512, &full[s]);
+                        if (!is_m) bulk_g2s(dst + L::U, tile + u_off, 8192, &full[s]);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+                    break;
+                }
+                const int cn = c + L::STAGES;                 // not yet being copied: pull it into L2
+                if (cn < nchunks) {
+                    const unsigned char* tile = p.tiles + ((size_t)(chunk0 + cn) * p.H + h) * TP_BYTES;
+                    for (int i = lane; i < (is_m ? 260 : 324); i += 32) {
+                        const int off = i < 128 ? TP_W + i * 128 : i < 256 ? TP_KG + (i - 128) * 128
+                                      : i < 260 ? TP_DECAY + (i - 256) * 128 : u_off + (i - 260) * 128;
+                        prefetch_l2(tile + off);
+                    }
+                }
+            }
+            return;
+        }
         if (lane == 0) {
             for (int c = 0; c < nchunks; ++c) {
                 const int s = c % SCAN_STAGES, use = c / SCAN_STAGES;
@@ -70,14 +125,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
                 }
                 const unsigned char* tile = p.tiles + ((size_t)(chunk0 + c) * p.H + h) * TP_BYTES;
                 unsigned char* dst = smem + s * SCAN_STAGE_BYTES;
-                if (is_m) {
-                    mbar_arrive_expect_tx(&full[s], TP_HEAD_BYTES);
-                    bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
-                } else {
-                    mbar_arrive_expect_tx(&full[s], SCAN_STAGE_BYTES);
-                    bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
-                    bulk_g2s(dst + ST_U, tile + (vh ? TP_U1 : TP_U0), 8192, &full[s]);
-                }
+                mbar_arrive_expect_tx(&full[s], SCAN_STAGE_BYTES);
+                bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
+                bulk_g2s(dst + ST_U, tile + (vh ? TP_U1 : TP_U0), 8192, &full[s]);
             }
         }
         return;
@@ -87,7 +137,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
     const int g = lane >> 2, t = lane & 3;
     const int m = lane >> 3, r = lane & 7;          // ldmatrix/stmatrix: matrix index, row inside it
     const int vb = vh * 64 + warp * 16;             // first value column of this warp
-    unsigned char* stg = smem + SCAN_STAGES * SCAN_STAGE_BYTES + warp * SCAN_STG_BYTES;
+    unsigned char* stg = smem + L::STAGES * L::STAGE_BYTES + warp * SCAN_STG_BYTES;   // unused by the transition scan
     const uint32_t stg_u32 = smem_u32(stg);
 
     float S[16][4];
@@ -121,12 +171,12 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
     for (int kp = 0; kp < 4; ++kp) x256[kp] = (uint32_t)(((4 * kp + m) ^ r) << 4);
 
     for (int c = 0; c < nchunks; ++c) {
-        const int s = c % SCAN_STAGES;
-        if (!mbar_wait(&full[s], (c / SCAN_STAGES) & 1)) {
+        const int s = c % L::STAGES;
+        if (!mbar_wait(&full[s], (c / L::STAGES) & 1)) {
             atomicExch(p.status, STATUS_WAIT_TIMEOUT);
             return;
         }
-        const uint32_t st = smem_u32(smem + s * SCAN_STAGE_BYTES);
+        const uint32_t st = smem_u32(smem + s * L::STAGE_BYTES);
         const int valid = min(BT, len - c * BT);
         const size_t tile_idx = (size_t)(chunk0 + c) * p.H + h;
 
@@ -193,7 +243,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4(st + TP_W + (8 * nt + r) * 256 + x256[kp], b0, b1, b2, b3);
+                ldsm_x4(st + L::W + (8 * nt + r) * 256 + x256[kp], b0, b1, b2, b3);
                 mma_f16(acc[nt], sa[2 * kp], b0, b1);
                 mma_f16(acc[nt], sa[2 * kp + 1], b2, b3);
             }
@@ -209,7 +259,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
         for (int np = 0; np < 4; ++np) {
             uint32_t r0, r1, r2, r3;
             int row = 8 * (2 * np + (m >> 1)) + r, ch = 2 * warp + (m & 1);
-            ldsm_x4_t(st + ST_U + row * 128 + ((ch ^ r) << 4), r0, r1, r2, r3);
+            ldsm_x4_t(st + L::U + row * 128 + ((ch ^ r) << 4), r0, r1, r2, r3);
             float2 f;
             f = unpack_f16(r0); acc[2 * np][0] = fmaf(-s_down, acc[2 * np][0], f.x); acc[2 * np][1] = fmaf(-s_down, acc[2 * np][1], f.y);
             f = unpack_f16(r1); acc[2 * np][2] = fmaf(-s_down, acc[2 * np][2], f.x); acc[2 * np][3] = fmaf(-s_down, acc[2 * np][3], f.y);
@@ -297,7 +347,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
 
         // ---- S^T <- S^T diag(decay) + v_new^T kg ----
         {
-            const float* dec = reinterpret_cast<const float*>(smem + s * SCAN_STAGE_BYTES + TP_DECAY);
+            const float* dec = reinterpret_cast<const float*>(smem + s * L::STAGE_BYTES + L::DECAY);
 #pragma unroll
             for (int jt = 0; jt < 16; ++jt) {
                 float2 d2 = *reinterpret_cast<const float2*>(dec + 8 * jt + 2 * t);
@@ -309,7 +359,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_fwd_scan_kernel(const Sca
                 for (int jp = 0; jp < 8; ++jp) {
                     uint32_t b0, b1, b2, b3;
                     int row = 16 * ks + (m & 1) * 8 + r, ch = 2 * jp + (m >> 1);
-                    ldsm_x4_t(st + TP_KG + row * 256 + ((ch ^ r) << 4), b0, b1, b2, b3);
+                    ldsm_x4_t(st + L::KG + row * 256 + ((ch ^ r) << 4), b0, b1, b2, b3);
                     mma_f16(S[2 * jp], va[ks], b0, b1);
                     mma_f16(S[2 * jp + 1], va[ks], b2, b3);
                 }
@@ -359,8 +409,9 @@ extern "C" int kda_launch_fwd_transition(const kda::ScanParams* p, cudaStream_t 
     using namespace kda;
     if (p->N <= 0) return 0;
     dim3 grid(4, p->H, p->N);
-    cudaError_t e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+    constexpr int smem = ScanLayout<true>::SMEM;
+    cudaError_t e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    kda_fwd_scan_kernel<false, true><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+    kda_fwd_scan_kernel<false, true><<<grid, SCAN_THREADS, smem, stream>>>(*p);
     return (int)cudaGetLastError();
 }
