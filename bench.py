@@ -224,8 +224,8 @@ def run_extra(args, rank, world, local_rank):
         d = {k: v.to(dev) for k, v in inp.items() if v is not None}
         step = lambda: chunk_kda_cp(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
                                     output_final_state=True, **kw)
-        tokens, metric, scaling, launches = T, "chunk_kda context-parallel forward tokens/s", "strong", (4 if world > 1 else 2)
-        cfg = {"T_total": T, "T_per_gpu": per, "exchange": "all-gather of (C|M) [2 segments,H,128,256] fp32 per rank over NCCL",
+        tokens, metric, scaling, launches = T, "chunk_kda context-parallel forward tokens/s", "strong", (6 if world > 1 else 2)
+        cfg = {"T_total": T, "T_per_gpu": per, "exchange": "one all-gather of (C|M) [2,H,128,128] fp32 per rank over NCCL",
                "segments_per_shard": 2 if world > 1 else 1}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 

@@ -6,8 +6,8 @@
 extern "C" int kda_launch_fwd_intra(const kda::IntraParams* p, int num_chunks, cudaStream_t stream);
 extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream);
 extern "C" int kda_launch_fwd_transition(const kda::ScanParams* p, cudaStream_t stream);
-extern "C" int kda_launch_cp_fold(const float* c_all, const float* m_all, const float* h0, float* s_in, int n_prev, int H,
-                                  cudaStream_t stream);
+extern "C" int kda_launch_cp_fold(const float* c_all, const float* m_all, const float* h0, float* s_out, int n, int H,
+                                  long long stride_floats, cudaStream_t stream);
 extern "C" int kda_launch_grad_scale(const void* d_o, size_t n_do, const float* dht, size_t n_dht, unsigned int* amax_bits,
                                      float* gscale, cudaStream_t stream);
 extern "C" int kda_launch_bwd_scan(const kda::BwdScanParams* p, cudaStream_t stream);
@@ -83,11 +83,13 @@ extern "C" int cula_kda_cp_transition(const void* d_tiles, float* d_c_out, float
     return kda_launch_fwd_transition(&p, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, const float* d_h0, float* d_s_in, int n_prev,
-                                int H, void* stream) {
-    if (!d_s_in || n_prev < 0 || H <= 0 || (n_prev > 0 && (!d_c_all || !d_m_all))) return CULA_KDA_EINVAL;
-    if (misaligned(d_m_all)) return CULA_KDA_EALIGN;
-    return kda_launch_cp_fold(d_c_all, d_m_all, d_h0, d_s_in, n_prev, H, static_cast<cudaStream_t>(stream));
+extern "C" int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, const float* d_h0, float* d_s_out, int n,
+                                int H, long long stride_floats, void* stream) {
+    if (!d_s_out || n < 0 || H <= 0 || (n > 0 && !d_m_all)) return CULA_KDA_EINVAL;
+    if (stride_floats <= 0) stride_floats = (long long)H * kda::DK * kda::DV;
+    if (misaligned(d_m_all) || misaligned(d_c_all) || misaligned(d_h0) || misaligned(d_s_out) || (stride_floats & 3))
+        return CULA_KDA_EALIGN;
+    return kda_launch_cp_fold(d_c_all, d_m_all, d_h0, d_s_out, n, H, stride_floats, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cula_kda_bwd_scratch_floats(void) { return kda::BWD_SCRATCH_FLOATS; }

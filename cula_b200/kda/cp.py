@@ -4,14 +4,14 @@ Every rank holds a contiguous shard ``[1, T_local, H, 128]`` of the same sequenc
 64-token chunk on every rank but the last). A shard acts on the carried state as ``S_out = M S_in + C`` per head, so
 
 1. each rank runs the chunk-parallel stage on its shard and one launch that scans ``(C | M)`` (no output rows),
-2. the ``(C, M)`` pairs are all-gathered (``[H, 128, 256]`` fp32 = 4 MiB per rank and segment at H = 32) into every
-   rank's own memory with NCCL,
+2. the ``(C | M)`` pairs are all-gathered (``[2, H, 128, 128]`` fp32 = 4 MiB per rank at H = 32) into every rank's
+   own memory with one NCCL collective,
 3. each rank folds its predecessors' transitions into its incoming state with a small kernel, and
 4. runs the ordinary fused scan + output pass from that state.
 
-A shard is further cut into ``P`` segments (two when it is long enough): step 1 yields one transition per segment, the
-fold of step 3 also yields the state at every segment boundary, and step 4 then scans the ``P`` segments side by
-side as if they were separate sequences with known initial states. The scan is a latency-bound chain that occupies
+A shard is further cut into ``P`` segments (two by default): step 1 yields one transition per segment (composed
+into the shard's transition before the gather), step 3 also yields the state at every segment boundary, and step 4
+then scans the ``P`` segments side by side as if they were separate sequences with known initial states. The scan is a latency-bound chain that occupies
 64 CTAs per segment, so this halves the time of step 4 at no extra work.
 
 This replaces what the reference gets from flash-linear-attention's ``cp_context`` (cula/kda/chunk.py:348-355,
@@ -76,23 +76,42 @@ class CudaBackend:
             return None, None, None
         return self.tables.cu_seqlens.data_ptr(), self.tables.chunk_offsets.data_ptr(), self.tables.seq_order.data_ptr()
 
-    def transition(self):
-        """(C, M), each [P, H, 128, 128]: the affine action of every segment of this shard on the state."""
-        P = self.n_segments
-        C = torch.empty(P, self.H, 128, 128, dtype=torch.float32, device=self.dev)
-        M = torch.empty(P, self.H, 128, 128, dtype=torch.float32, device=self.dev)
-        cu_p, co_p, _ = self._table_ptrs()
-        _native.check(self.lib.cula_kda_cp_transition(self.tiles.data_ptr(), C.data_ptr(), M.data_ptr(), cu_p, co_p, P,
-                                                      self.T, self.H, self.status, self.stream), "cula_kda_cp_transition")
-        return C, M
+    def _fold(self, c_ptr, m_ptr, h0, n, out, stride=0):
+        _native.check(self.lib.cula_kda_cp_fold(c_ptr, m_ptr, _ptr(h0), out.data_ptr(), int(n), self.H, int(stride),
+                                                self.stream), "cula_kda_cp_fold")
+        return out
 
-    def fold(self, C_all, M_all, h0, start, n):
-        """S = h0 (or 0); for j in [start, start + n): S = M_all[j] S + C_all[j] (chains of [*, H, 128, 128])."""
-        s_in = torch.empty(self.H, 128, 128, dtype=torch.float32, device=self.dev)
-        h0 = None if h0 is None else h0.reshape(self.H, 128, 128).float().contiguous()
-        _native.check(self.lib.cula_kda_cp_fold(C_all[start:].data_ptr(), M_all[start:].data_ptr(), _ptr(h0),
-                                                s_in.data_ptr(), int(n), self.H, self.stream), "cula_kda_cp_fold")
-        return s_in
+    def transition(self):
+        """X [2, H, 128, 128] = (C | M): the affine action of this whole shard on the state. The transitions of the
+        P segments are kept for `incoming`; they are composed here so that only one pair travels."""
+        P = self.n_segments
+        self.C_seg = torch.empty(P, self.H, 128, 128, dtype=torch.float32, device=self.dev)
+        self.M_seg = torch.empty(P, self.H, 128, 128, dtype=torch.float32, device=self.dev)
+        cu_p, co_p, _ = self._table_ptrs()
+        _native.check(self.lib.cula_kda_cp_transition(self.tiles.data_ptr(), self.C_seg.data_ptr(), self.M_seg.data_ptr(),
+                                                      cu_p, co_p, P, self.T, self.H, self.status, self.stream),
+                      "cula_kda_cp_transition")
+        if P == 1:
+            return torch.stack([self.C_seg[0], self.M_seg[0]])
+        X = torch.empty(2, self.H, 128, 128, dtype=torch.float32, device=self.dev)
+        self._fold(self.C_seg.data_ptr(), self.M_seg.data_ptr(), None, P, X[0])            # C = fold of the segments from 0
+        self._fold(None, self.M_seg[1:].data_ptr(), self.M_seg[0], P - 1, X[1])            # M = M_{P-1} ... M_0
+        return X
+
+    def incoming(self, X_all, rank, initial_state):
+        """States entering each of the P segments of this shard: the fold of the shards before this one (X_all is
+        [world, 2, H, 128, 128] in this GPU's memory), then one more step per inner segment boundary."""
+        s = None if initial_state is None else initial_state.reshape(self.H, 128, 128).float().contiguous()
+        if rank > 0:
+            per = self.H * 128 * 128
+            s = self._fold(X_all.data_ptr(), X_all.data_ptr() + 4 * per, s, rank,
+                           torch.empty(self.H, 128, 128, dtype=torch.float32, device=self.dev), stride=2 * per)
+        states = [s]
+        for i in range(1, self.n_segments):
+            s = self._fold(self.C_seg[i - 1:].data_ptr(), self.M_seg[i - 1:].data_ptr(), s, 1,
+                           torch.empty(self.H, 128, 128, dtype=torch.float32, device=self.dev))
+            states.append(s)
+        return states
 
     def forward(self, states, want_final):
         """Scan + output of the P segments from their incoming states (None = zero state)."""
@@ -125,23 +144,13 @@ def gather_with_group(group=None):
 
 def cp_forward(backend, gather, rank, world, initial_state=None, output_final_state=False):
     """Rank-local part of the context-parallel forward. Returns (o_local, final_state or None); the final state
-    is produced on the last rank only. ``backend.n_segments`` (P, the same on every rank) is the number of segments
-    a shard is cut into; the gathered transitions form one chain of ``world * P`` elements."""
+    is produced on the last rank only."""
     last = rank == world - 1
-    P = backend.n_segments
-    if world == 1 and P == 1:
+    if world == 1 and backend.n_segments == 1:
         return backend.forward([initial_state], output_final_state)
-    C, M = backend.transition()                              # [P, H, 128, 128] each
-    if world > 1:
-        C_all, M_all = gather(C), gather(M)                  # [world, P, H, 128, 128]
-        C_all, M_all = C_all.reshape((world * P,) + tuple(C.shape[1:])), M_all.reshape((world * P,) + tuple(M.shape[1:]))
-    else:
-        C_all, M_all = C, M
-    s = initial_state if rank == 0 else backend.fold(C_all, M_all, initial_state, 0, rank * P)
-    states = [s]
-    for i in range(1, P):                                    # state at each inner segment boundary
-        s = backend.fold(C_all, M_all, s, rank * P + i - 1, 1)
-        states.append(s)
+    X = backend.transition()                                  # [2, H, 128, 128]: (C | M) of this shard
+    X_all = gather(X) if world > 1 else X[None]               # [world, 2, H, 128, 128]
+    states = backend.incoming(X_all, rank, initial_state)
     return backend.forward(states, output_final_state and last)
 
 

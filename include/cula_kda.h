@@ -139,10 +139,13 @@ int cula_kda_cp_transition(const void* d_tiles, float* d_c_out, float* d_m_out,
                            const int* d_cu_seqlens, const int* d_chunk_offsets, int N, int T, int H,
                            int* d_status, void* stream);
 
-/* d_s_in [H,128,128] = fold of the first n_prev gathered transitions (d_c_all, d_m_all: [W,H,128,128], in this GPU's
- * own memory) applied to d_h0 (or zero when NULL). Replaces the merge step (fla/ops/cp/chunk_delta_h.py:797-817). */
-int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, const float* d_h0, float* d_s_in, int n_prev, int H,
-                     void* stream);
+/* d_s_out [H,128,128] = S after  S <- d_h0 (zero when NULL);  for j in [0, n): S <- M_j S + C_j,  where element j of
+ * the chain sits at d_c_all + j * stride_floats and d_m_all + j * stride_floats ([H,128,128] fp32 each, in this GPU's
+ * own memory: gathered transitions or the rank's own). stride_floats <= 0 means densely packed (H*128*128).
+ * d_c_all == NULL stands for C_j = 0 (product of the M_j: composing the transitions of a shard's segments).
+ * Replaces the merge step (fla/ops/cp/chunk_delta_h.py:797-817). */
+int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, const float* d_h0, float* d_s_out, int n, int H,
+                     long long stride_floats, void* stream);
 
 /*
  * Whole forward pass (both launches above) for callers that cannot allocate device memory themselves -- a runtime

@@ -37,21 +37,13 @@ def test_cp_emulated_ranks_match_oracle(world, T, gate_offset, segments):
         backends.append(CudaBackend(inp["q"][:, sl].cuda(), inp["k"][:, sl].cuda(), inp["v"][:, sl].cuda(),
                                     inp["g"][:, sl].cuda(), inp["beta"][:, sl].cuda(), 128 ** -0.5, True, True, True, -5.0,
                                     inp["A_log"].cuda(), inp["dt_bias"].cuda(), segments=segments))
-    trans = [b.transition() for b in backends]               # [P, H, 128, 128] pairs; some segments are empty here
-    stacked = {"C": torch.stack([t[0] for t in trans]), "M": torch.stack([t[1] for t in trans])}
-
-    class Replay:                       # the emulated collective: every rank sees the same stacked tensors
-        def __init__(self):
-            self.calls = 0
-
-        def __call__(self, x):
-            self.calls += 1
-            return stacked["C"] if self.calls % 2 == 1 else stacked["M"]
+    trans = [b.transition() for b in backends]               # (C | M) per shard; some segments are empty here
+    X_all = torch.stack(trans)                               # the emulated collective: every rank sees the same tensor
 
     outs, final = [], None
     for r, b in enumerate(backends):
         b.transition = lambda t=trans[r]: t           # already computed above
-        o, ht = cp_forward(b, Replay(), r, world, inp["initial_state"].cuda(), True)
+        o, ht = cp_forward(b, lambda x: X_all, r, world, inp["initial_state"].cuda(), True)
         outs.append(o)
         final = ht if ht is not None else final
     torch.cuda.synchronize()
@@ -72,14 +64,26 @@ def test_cp_transition_is_the_affine_map_of_the_shard():
     b = CudaBackend(d["q"], d["k"], d["v"], d["g"], d["beta"], 128 ** -0.5, True, True, True, -5.0, d["A_log"], d["dt_bias"],
                     segments=1)
     C, M = b.transition()
-    C, M = C[0], M[0]
     _, ht = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
                       initial_state=d["initial_state"], output_final_state=True, use_qk_l2norm_in_kernel=True,
                       use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
     pred = torch.matmul(M.double(), d["initial_state"][0].double()) + C.double()
     assert err_ratio(ht[0].double().cpu(), pred.cpu()) <= 2e-3
-    folded = b.fold(C[None], M[None], d["initial_state"], 0, 1)
+    folded = b.incoming(torch.stack([C, M])[None].repeat(2, 1, 1, 1, 1), 1, d["initial_state"])[0]
     assert err_ratio(pred.cpu(), folded.double().cpu()) <= 1e-5
+
+
+def test_cp_composed_segments_equal_the_whole_shard():
+    """Composing the transitions of two segments must give the transition of the undivided shard."""
+    from cula_b200.kda.cp import CudaBackend
+    T, H = 64 * 7 + 30, 2
+    inp = make_inputs(1, T, H, seed=5, gate_offset=-8.0)
+    d = {k: (v.cuda() if v is not None else None) for k, v in inp.items()}
+    mk = lambda P: CudaBackend(d["q"], d["k"], d["v"], d["g"], d["beta"], 128 ** -0.5, True, True, True, -5.0, d["A_log"],
+                               d["dt_bias"], segments=P)
+    X1, X2, X3 = mk(1).transition(), mk(2).transition(), mk(3).transition()
+    for X in (X2, X3):
+        assert err_ratio(X1[0].cpu(), X[0].cpu()) <= 2e-3 and err_ratio(X1[1].cpu(), X[1].cpu()) <= 2e-3
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

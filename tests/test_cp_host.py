@@ -30,22 +30,28 @@ class OracleBackend:
         return self.q[:, sl], self.k[:, sl], self.v[:, sl], self.a[:, sl], self.beta[:, sl]
 
     def transition(self):
-        Cs, Ms = [], []
+        self.C_seg, self.M_seg = [], []
+        C_tot, M_tot = torch.zeros(self.H, 128, 128), torch.eye(128).expand(self.H, 128, 128).clone()
         for i in range(self.n_segments):
             q, k, v, a, beta = self._seg(i)
             _, C = naive_recurrent_kda(q, k, v, a, beta, None, None, True)
             # M: the recurrence is linear in the state when v = 0; push the identity through it
             eye = torch.eye(128).expand(1, self.H, 128, 128)
             _, M = naive_recurrent_kda(q, k, torch.zeros_like(v), a, beta, None, eye, True)
-            Cs.append(C[0])
-            Ms.append(M[0])
-        return torch.stack(Cs), torch.stack(Ms)
+            self.C_seg.append(C[0])
+            self.M_seg.append(M[0])
+            C_tot, M_tot = M[0] @ C_tot + C[0], M[0] @ M_tot
+        return torch.stack([C_tot, M_tot])
 
-    def fold(self, C_all, M_all, h0, start, n):
-        S = torch.zeros(self.H, 128, 128) if h0 is None else h0.reshape(self.H, 128, 128).clone()
-        for j in range(start, start + n):
-            S = M_all[j] @ S + C_all[j]
-        return S
+    def incoming(self, X_all, rank, initial_state):
+        S = torch.zeros(self.H, 128, 128) if initial_state is None else initial_state.reshape(self.H, 128, 128).clone()
+        for j in range(rank):
+            S = X_all[j, 1] @ S + X_all[j, 0]
+        states = [S]
+        for i in range(1, self.n_segments):
+            S = self.M_seg[i - 1] @ S + self.C_seg[i - 1]
+            states.append(S)
+        return states
 
     def forward(self, states, want_final):
         outs, ht = [], None
