@@ -106,7 +106,9 @@ extern "C" int cula_kda_bwd_scan(const void* d_tiles, const void* d_do, const fl
                                  const int* d_chunk_offsets, const int* d_seq_order, int N, int T, int H, int* d_status,
                                  void* stream) {
     if (N == 0) return 0;
-    if (!d_tiles || !d_do || !d_gscale || !d_dvn_out || !d_ds_out || !d_status || N < 0 || H <= 0) return CULA_KDA_EINVAL;
+    if (!d_tiles || !d_do || !d_gscale || !d_status || N < 0 || H <= 0) return CULA_KDA_EINVAL;
+    if ((d_dvn_out == nullptr) != (d_ds_out == nullptr)) return CULA_KDA_EINVAL;
+    if (!d_dvn_out && !d_dh0) return CULA_KDA_EINVAL;     // nothing to produce
     if ((d_cu_seqlens == nullptr) != (d_chunk_offsets == nullptr)) return CULA_KDA_EINVAL;
     if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
     if (misaligned(d_tiles) || misaligned(d_do) || misaligned(d_dvn_out) || misaligned(d_ds_out)) return CULA_KDA_EALIGN;

@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(BS_THREADS, 1) kda_bwd_scan_kernel(const BwdSc
         const size_t tile_idx = (size_t)(chunk0 + c) * p.H + h;
 
         // ---- dS' (gradient w.r.t. the state leaving this chunk) to HBM, fp32 [128 k][128 v] ----
-        {
+        if (p.ds_out) {
             float* dsg = p.ds_out + tile_idx * (size_t)(DK * DV);
 #pragma unroll
             for (int jt = 0; jt < 16; ++jt) {
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(BS_THREADS, 1) kda_bwd_scan_kernel(const BwdSc
             va[ks][2] = pack_f16(acc[2 * ks + 1][0], acc[2 * ks + 1][1]);
             va[ks][3] = pack_f16(acc[2 * ks + 1][2], acc[2 * ks + 1][3]);
         }
-        {   // dVn, fp16 [64 tokens][128 v]
+        if (p.dvn_out) {   // dVn, fp16 [64 tokens][128 v]
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
                 int trow = 8 * (2 * ks + (m >> 1)) + r;

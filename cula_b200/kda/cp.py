@@ -15,8 +15,8 @@ then scans the ``P`` segments side by side as if they were separate sequences wi
 64 CTAs per segment, so this halves the time of step 4 at no extra work.
 
 This replaces what the reference gets from flash-linear-attention's ``cp_context`` (cula/kda/chunk.py:348-355,
-cula/kda/chunk_fwd.py:99-127; fla/ops/cp/chunk_delta_h.py:736-817). Forward only for now: calling backward on the
-result raises.
+cula/kda/chunk_fwd.py:99-127; fla/ops/cp/chunk_delta_h.py:736-817). The backward pass runs the same exchange in the
+other direction (`CPBackwardState`).
 
 The orchestration (`cp_forward`) is written against two small interfaces, a compute backend and a gather function,
 so the same code runs on NCCL across GPUs, on gloo in CPU tests, and with all ranks emulated in one process.
@@ -142,26 +142,128 @@ def gather_with_group(group=None):
     return gather
 
 
-def cp_forward(backend, gather, rank, world, initial_state=None, output_final_state=False):
+def cp_forward(backend, gather, rank, world, initial_state=None, output_final_state=False, aux=None):
     """Rank-local part of the context-parallel forward. Returns (o_local, final_state or None); the final state
-    is produced on the last rank only."""
+    is produced on the last rank only. ``aux`` (a dict) receives what the backward pass needs: the state entering
+    this shard and the gathered transitions."""
     last = rank == world - 1
     if world == 1 and backend.n_segments == 1:
+        if aux is not None:
+            aux.update(s_in=initial_state, X_all=None)
         return backend.forward([initial_state], output_final_state)
     X = backend.transition()                                  # [2, H, 128, 128]: (C | M) of this shard
     X_all = gather(X) if world > 1 else X[None]               # [world, 2, H, 128, 128]
     states = backend.incoming(X_all, rank, initial_state)
+    if aux is not None:
+        aux.update(s_in=states[0], X_all=X_all)
     return backend.forward(states, output_final_state and last)
 
 
-class _NoBackward(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, o, *inputs):
-        return o.view_as(o)
+class CPBackwardState:
+    """What one rank keeps from the forward pass for the context-parallel backward, and the two steps of it.
+
+    The backward pass of a shard is affine in the gradient of the state leaving the shard:
+    ``dS_in = M^T dS_out + C~`` with the forward ``M`` and ``C~`` the part that comes from the shard's own ``do``.
+    So (1) `prepare` runs the reverse scan with ``dS_out = 0`` and returns ``Y = (C~ | dht)`` for the gather,
+    (2) `finish` folds the successors' ``(M^T, C~)`` onto the last rank's ``dht`` to get this shard's true
+    ``dS_out`` and runs the ordinary backward from it. Mirrors the forward exchange with the direction reversed
+    (fla/ops/cp/chunk_delta_h.py:820-910 is the counterpart the reference reaches)."""
+
+    def __init__(self, q, k, v, g, beta, A_log, dt_bias, s_in, X_all, scale, flags, rank, world):
+        self.q, self.k, self.v, self.g, self.beta, self.A_log, self.dt_bias = q, k, v, g, beta, A_log, dt_bias
+        self.s_in, self.X_all, self.scale, self.flags, self.rank, self.world = s_in, X_all, scale, flags, rank, world
+        self.H = q.shape[2]
+
+    def _s0(self):
+        return None if self.s_in is None else self.s_in.reshape(1, self.H, 128, 128).float().contiguous()
+
+    def prepare(self, do, dht):
+        """Recompute the forward intermediates of the shard; reverse scan from dS_out = 0. Returns Y [2, H, 128, 128]."""
+        from .chunk import chunk_kda_fwd
+        lib = _native.lib()
+        l2, gate_in, safe_gate, lower_bound = self.flags
+        dev = self.q.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        self.do = do.contiguous()
+        self.saved = chunk_kda_fwd(self.q, self.k, self.v, self.g, self.beta, self.scale, self._s0(), False, None, None,
+                                   l2, gate_in, safe_gate, lower_bound, self.A_log, self.dt_bias,
+                                   store_for_backward=True, want_output=False)
+        Y = torch.zeros(2, self.H, 128, 128, dtype=torch.float32, device=dev)
+        if dht is not None:
+            Y[1].copy_(dht.reshape(self.H, 128, 128))
+        if self.world > 1 and self.rank > 0:                  # nobody needs rank 0's C~
+            work = torch.zeros(4, dtype=torch.float32, device=dev)
+            _native.check(lib.cula_kda_bwd_grad_scale(self.do.data_ptr(), self.do.numel(), None, 0, work[2:].data_ptr(),
+                                                      work.data_ptr(), stream), "cula_kda_bwd_grad_scale")
+            _native.check(lib.cula_kda_bwd_scan(self.saved["tiles"].data_ptr(), self.do.data_ptr(), None, work.data_ptr(),
+                                                None, None, Y[0].data_ptr(), None, None, None, 1, self.q.shape[1], self.H,
+                                                _status_word(dev).data_ptr(), stream), "cula_kda_bwd_scan")
+        return Y
+
+    def finish(self, Y_all):
+        """Y_all [world, 2, H, 128, 128] in this GPU's memory. Returns (dq, dk, dv, dg, dbeta, dA_log, ddt_bias, dS_in);
+        dA_log and ddt_bias are this shard's contributions (their sum over the group is the caller's, as it is for
+        data-parallel replicas)."""
+        from .chunk import chunk_kda_bwd
+        lib = _native.lib()
+        l2, gate_in, safe_gate, lower_bound = self.flags
+        dev = self.q.device
+        r, W, H = self.rank, self.world, self.H
+        dht = Y_all[W - 1, 1]
+        if r < W - 1:
+            n = W - 1 - r
+            Mt = self.X_all[r + 1:, 1].flip(0).transpose(-1, -2).contiguous()     # successors, nearest last
+            Ct = Y_all[r + 1:, 0].flip(0).contiguous()
+            out = torch.empty(H, 128, 128, dtype=torch.float32, device=dev)
+            _native.check(lib.cula_kda_cp_fold(Ct.data_ptr(), Mt.data_ptr(), dht.contiguous().data_ptr(), out.data_ptr(), n, H,
+                                               0, torch.cuda.current_stream(dev).cuda_stream), "cula_kda_cp_fold")
+            dht = out
+        s0 = self._s0()
+        if s0 is None:                                        # a zero state still has a gradient slot (it is dS_in)
+            s0 = torch.zeros(1, H, 128, 128, dtype=torch.float32, device=dev)
+        return chunk_kda_bwd(self.q, self.k, self.v, self.g, self.beta, self.scale, s0, self.do,
+                             dht.reshape(1, H, 128, 128), None, None, l2, gate_in, safe_gate, lower_bound, self.A_log,
+                             self.dt_bias, saved=self.saved)
+
+
+class ChunkKDACPFunction(torch.autograd.Function):
+    """Autograd boundary of the context-parallel path: one shard per rank, exchanges inside forward and backward."""
 
     @staticmethod
-    def backward(ctx, do):
-        raise NotImplementedError("chunk_kda_cp: the context-parallel backward pass is not implemented")
+    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, initial_state, scale, output_final_state, flags, group, segments):
+        q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        l2, gate_in, safe_gate, lower_bound = flags
+        aux = {}
+        with torch.cuda.device(q.device):
+            backend = CudaBackend(q, k, v, g, beta, scale, l2, gate_in, safe_gate, lower_bound, A_log, dt_bias,
+                                  segments=1 if world == 1 else segments)
+            o, ht = cp_forward(backend, gather_with_group(group), rank, world, initial_state, output_final_state, aux)
+        ctx.cp = CPBackwardState(q, k, v, g, beta, None if A_log is None else A_log.float().contiguous(),
+                                 None if dt_bias is None else dt_bias.float().contiguous(), aux["s_in"], aux["X_all"],
+                                 scale, flags, rank, world)
+        ctx.group = group
+        ctx.has_h0 = initial_state is not None
+        ctx.param_dtypes = (None if A_log is None else (A_log.dtype, A_log.shape),
+                            None if dt_bias is None else (dt_bias.dtype, dt_bias.shape))
+        if ht is None:
+            ht = torch.empty(0, device=q.device)              # autograd wants a tensor; the wrapper maps it back to None
+            ctx.mark_non_differentiable(ht)
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        cp = ctx.cp
+        with torch.cuda.device(do.device):
+            Y = cp.prepare(do, dht if (cp.rank == cp.world - 1 and dht is not None and dht.numel() > 0) else None)
+            Y_all = gather_with_group(ctx.group)(Y) if cp.world > 1 else Y[None]
+            dq, dk, dv, dg, dbeta, dA, dbias, dh0 = cp.finish(Y_all)
+        if dA is not None and ctx.param_dtypes[0] is not None:
+            dA = dA.to(ctx.param_dtypes[0][0]).view(ctx.param_dtypes[0][1])
+        if dbias is not None and ctx.param_dtypes[1] is not None:
+            dbias = dbias.to(ctx.param_dtypes[1][0]).view(ctx.param_dtypes[1][1])
+        dh0 = dh0 if (ctx.has_h0 and cp.rank == 0) else None
+        return dq, dk, dv, dg, dbeta, dA, dbias, dh0, None, None, None, None, None
 
 
 @torch.compiler.disable
@@ -170,7 +272,9 @@ def chunk_kda_cp(q, k, v, g, beta, scale=None, initial_state=None, output_final_
                  group=None, segments=None, **kwargs):
     """Context-parallel ``chunk_kda`` forward. Arguments as ``chunk_kda`` for this rank's shard of ONE sequence;
     ``initial_state`` ([1, H, 128, 128] fp32) is the state before the first token of the whole sequence and is
-    read on rank 0 of ``group``; ``final_state`` is returned on the last rank (None elsewhere). ``segments`` (default 2) must be the
+    read on rank 0 of ``group``; ``final_state`` is returned on the last rank (None elsewhere). Differentiable: the
+    gradients of ``A_log`` / ``dt_bias`` are this shard's contributions (sum them over the group as for data-parallel
+    replicas), the gradient of ``initial_state`` appears on rank 0. ``segments`` (default 2) must be the
     same on every rank; a shard shorter than that many chunks simply gets empty segments."""
     assert q.shape[0] == 1, "context parallelism expects one sequence (batch size 1)"
     assert q.dtype == k.dtype == v.dtype == torch.bfloat16, "q, k, v must be in bfloat16."
@@ -190,10 +294,7 @@ def chunk_kda_cp(q, k, v, g, beta, scale=None, initial_state=None, output_final_
     assert_blackwell(q.device)
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    with torch.cuda.device(q.device):
-        backend = CudaBackend(q, k, v, g, beta, scale, use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate,
-                              lower_bound, A_log, dt_bias, segments=1 if world == 1 else segments)
-        o, ht = cp_forward(backend, gather_with_group(group), rank, world, initial_state, output_final_state)
-    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, g, beta)):
-        o = _NoBackward.apply(o, q, k, v, g, beta)
-    return o, ht
+    flags = (use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound)
+    o, ht = ChunkKDACPFunction.apply(q, k, v, g, beta, A_log, dt_bias, initial_state, scale, output_final_state, flags,
+                                     group, segments)
+    return o, (ht if ht.numel() > 0 else None)

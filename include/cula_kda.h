@@ -99,6 +99,7 @@ int cula_kda_bwd_grad_scale(const void* d_do, long long n_do, const float* d_dht
 
 /* Reverse state scan: d_dvn_out (fp16 [num_chunks*H][64][128], gradient w.r.t. v_new), d_ds_out (fp32
  * [num_chunks*H][128][128], gradient w.r.t. the state leaving each chunk), d_dh0 ([N,H,128,128] fp32 or NULL).
+ * d_dvn_out and d_ds_out may both be NULL when only d_dh0 is wanted (first pass of the context-parallel backward).
  * Replaces chunk_gated_delta_rule_bwd_dhu (fla/ops/common/chunk_delta_h.py:659-718, cula/kda/chunk_bwd.py:541-555)
  * and the dv half of chunk_kda_bwd_dAv (cula/kda/chunk_bwd.py:510-520). */
 int cula_kda_bwd_scan(const void* d_tiles, const void* d_do, const float* d_dht, const float* d_gscale,

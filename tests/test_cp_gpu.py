@@ -86,6 +86,63 @@ def test_cp_composed_segments_equal_the_whole_shard():
         assert err_ratio(X1[0].cpu(), X[0].cpu()) <= 2e-3 and err_ratio(X1[1].cpu(), X[1].cpu()) <= 2e-3
 
 
+@pytest.mark.parametrize("world,T,segments", [(2, 256, 1), (4, 512, 2), (3, 64 * 5 + 17, 2)])
+def test_cp_backward_emulated_ranks_match_oracle_autograd(world, T, segments):
+    """Forward and backward of every shard with the exchanges emulated in-process; gradients against autograd of
+    the fp32 oracle on the whole sequence. Weak gates, so the gradient that crosses shard boundaries matters."""
+    from cula_b200.kda import check_status
+    from cula_b200.kda.cp import CPBackwardState, CudaBackend, cp_forward
+    from oracle.naive_kda import chunk_kda_oracle
+    H = 2
+    inp = make_inputs(1, T, H, seed=7, gate_offset=-8.0, h0_std=0.5)
+    gen = torch.Generator().manual_seed(11)
+    do = torch.randn(1, T, H, 128, generator=gen).to(torch.bfloat16)
+    dht = 0.1 * torch.randn(1, H, 128, 128, generator=gen)
+    names = ("q", "k", "v", "g", "beta", "A_log", "dt_bias", "initial_state")
+    ref_in = {n: inp[n].detach().float().clone().requires_grad_(True) for n in names}
+    o_ref, ht_ref = chunk_kda_oracle(ref_in["q"], ref_in["k"], ref_in["v"], ref_in["g"], ref_in["beta"],
+                                     initial_state=ref_in["initial_state"], output_final_state=True,
+                                     use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+                                     A_log=ref_in["A_log"], dt_bias=ref_in["dt_bias"])
+    ((o_ref * do.float()).sum() + (ht_ref * dht).sum()).backward()
+
+    per = (T // world) // 64 * 64
+    bounds = [r * per for r in range(world)] + [T]
+    flags = (True, True, True, -5.0)
+    A_log, dt_bias = inp["A_log"].cuda(), inp["dt_bias"].cuda()
+    shards, backends = [], []
+    for r in range(world):
+        sl = slice(bounds[r], bounds[r + 1])
+        sh = {n: inp[n][:, sl].cuda().contiguous() for n in ("q", "k", "v", "g", "beta")}
+        shards.append(sh)
+        backends.append(CudaBackend(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], 128 ** -0.5, *flags, A_log, dt_bias,
+                                    segments=segments))
+    trans = [b.transition() for b in backends]
+    X_all = torch.stack(trans)
+    states = []
+    for r, b in enumerate(backends):
+        b.transition = lambda t=trans[r]: t
+        aux = {}
+        cp_forward(b, lambda x: X_all, r, world, inp["initial_state"].cuda(), True, aux)
+        sh = shards[r]
+        states.append(CPBackwardState(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], A_log, dt_bias, aux["s_in"], aux["X_all"],
+                                      128 ** -0.5, flags, r, world))
+    Y_all = torch.stack([st.prepare(do[:, bounds[r]:bounds[r + 1]].cuda(), dht.cuda() if r == world - 1 else None)
+                         for r, st in enumerate(states)])
+    grads = [st.finish(Y_all) for st in states]
+    torch.cuda.synchronize()
+    check_status()
+    got = {n: torch.cat([g[i] for g in grads], dim=1).float().cpu() for i, n in enumerate(("q", "k", "v", "g", "beta"))}
+    got["A_log"] = sum(g[5] for g in grads).float().cpu().view_as(inp["A_log"])
+    got["dt_bias"] = sum(g[6] for g in grads).float().cpu().view_as(inp["dt_bias"])
+    got["initial_state"] = grads[0][7].float().cpu()
+    tol = {"g": 2e-2, "beta": 2e-2}
+    for n in names:
+        ref = ref_in[n].grad
+        e = err_ratio(ref, got[n])
+        assert e <= tol.get(n, 8e-3) and torch.isfinite(got[n]).all(), (n, e)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_cp_two_gpus_nccl(tmp_path):
     script = os.path.join(ROOT, "tests", "cp_nccl_worker.py")
