@@ -35,6 +35,11 @@ WORKLOADS = {
 }
 # Secondary workloads (selected with --workload; not the headline line): forward+backward, the packed varlen
 # forward, and the context-parallel forward of one long sequence split over the ranks (strong scaling).
+# DRAM bytes of one launch, from the ncu captures summarised under profiles/ (same command line as this script)
+NCU_TRAFFIC_BYTES = {
+    ("fwd_B2_T2048_H32", "kda_fwd_intra_kernel"): 135190272 + 104998656,
+    ("fwd_B2_T2048_H32", "kda_fwd_scan_kernel"): 152075520 + 21043968,
+}
 EXTRA_WORKLOADS = {
     "fwdbwd_B4_T8192_H32": dict(kind="fwdbwd", B=4, T=8192, H=32),
     "fwdbwd_B2_T2048_H32": dict(kind="fwdbwd", B=2, T=2048, H=32),
@@ -391,7 +396,9 @@ def main():
     peaks = load_peaks()
     achieved = kernels[dom]["bytes"] / (kernels[dom]["ms"] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get((args.workload, dom)),
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload (profiles/)",
+                "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
                 "kernels_ms": {k: v["ms"] for k, v in kernels.items()}}
 

@@ -161,31 +161,50 @@ __device__ __forceinline__ void bd_tile(const BwdDenseParams& p, float* sm, cons
             dD_part += a;
         }
         // ---- contraction over the 64 value columns of this half ----
-        const float* aO = sm + BD_DO + (16 * mt) * PR;
-        const float* aV = sm + BD_VN + (16 * mt) * PR;
-        const float* aD = sm + BD_DVN + (16 * mt) * PR;
+        // tf32 fragments come from ldmatrix: an 8 x 8 b16 tile is an 8 x 4 tile of 32-bit words, and lane l receives
+        // word (row l / 4, column l % 4) -- exactly the m16n8k8 tf32 fragment layout. One x4 load fetches a whole
+        // A fragment (rows 0-7 / 8-15 x words 0-3 / 4-7) or the B fragments of two n-tiles.
+        const uint32_t sm_u32 = smem_u32(sm);
+        const int lr = lane & 7, lm = lane >> 3;
+        const uint32_t a_off = (uint32_t)(((16 * mt + lr + 8 * (lm & 1)) * PR + 4 * (lm >> 1)) * 4);   // + k0 * 4
+        const uint32_t b_off = (uint32_t)(((lr + 8 * (lm >> 1)) * PR + 4 * (lm & 1)) * 4);              // + (n0 * PR + k0) * 4
 #pragma unroll 2
         for (int ks = 0; ks < 8; ++ks) {
             const int k0 = 8 * ks;
-            const float fO[4] = {aO[g * PR + k0 + t], aO[(g + 8) * PR + k0 + t], aO[g * PR + k0 + t + 4], aO[(g + 8) * PR + k0 + t + 4]};
-            const float fV[4] = {aV[g * PR + k0 + t], aV[(g + 8) * PR + k0 + t], aV[g * PR + k0 + t + 4], aV[(g + 8) * PR + k0 + t + 4]};
-            const float fD[4] = {aD[g * PR + k0 + t], aD[(g + 8) * PR + k0 + t], aD[g * PR + k0 + t + 4], aD[(g + 8) * PR + k0 + t + 4]};
+            float fO[4], fV[4], fD[4];
+            ldsm_x4(sm_u32 + BD_DO * 4 + a_off + k0 * 4, reinterpret_cast<uint32_t&>(fO[0]), reinterpret_cast<uint32_t&>(fO[1]),
+                    reinterpret_cast<uint32_t&>(fO[2]), reinterpret_cast<uint32_t&>(fO[3]));
+            ldsm_x4(sm_u32 + BD_VN * 4 + a_off + k0 * 4, reinterpret_cast<uint32_t&>(fV[0]), reinterpret_cast<uint32_t&>(fV[1]),
+                    reinterpret_cast<uint32_t&>(fV[2]), reinterpret_cast<uint32_t&>(fV[3]));
+            ldsm_x4(sm_u32 + BD_DVN * 4 + a_off + k0 * 4, reinterpret_cast<uint32_t&>(fD[0]), reinterpret_cast<uint32_t&>(fD[1]),
+                    reinterpret_cast<uint32_t&>(fD[2]), reinterpret_cast<uint32_t&>(fD[3]));
 #pragma unroll
-            for (int nt = 0; nt < BD_NT128; ++nt) {
-                const int n0 = 8 * BD_NT128 * nh + 8 * nt;      // key channel
-                const float s0 = sm[BD_S + (n0 + g) * PR + k0 + t], s1 = sm[BD_S + (n0 + g) * PR + k0 + t + 4];
-                const float d0 = sm[BD_DS + (n0 + g) * PR + k0 + t], d1 = sm[BD_DS + (n0 + g) * PR + k0 + t + 4];
-                mma_tf32(accQ[nt], fO, s0, s1);
-                mma_tf32(accW[nt], fD, s0, s1);
-                mma_tf32(accK[nt], fV, d0, d1);
+            for (int np = 0; np < BD_NT128 / 2; ++np) {
+                const int n0 = 8 * BD_NT128 * nh + 16 * np;      // key channels n0 .. n0 + 15
+                float s[4], d[4];
+                ldsm_x4(sm_u32 + (BD_S + n0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(s[0]), reinterpret_cast<uint32_t&>(s[1]),
+                        reinterpret_cast<uint32_t&>(s[2]), reinterpret_cast<uint32_t&>(s[3]));
+                ldsm_x4(sm_u32 + (BD_DS + n0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(d[0]), reinterpret_cast<uint32_t&>(d[1]),
+                        reinterpret_cast<uint32_t&>(d[2]), reinterpret_cast<uint32_t&>(d[3]));
+                mma_tf32(accQ[2 * np], fO, s[0], s[1]);
+                mma_tf32(accW[2 * np], fD, s[0], s[1]);
+                mma_tf32(accK[2 * np], fV, d[0], d[1]);
+                mma_tf32(accQ[2 * np + 1], fO, s[2], s[3]);
+                mma_tf32(accW[2 * np + 1], fD, s[2], s[3]);
+                mma_tf32(accK[2 * np + 1], fV, d[2], d[3]);
             }
-#pragma unroll
-            for (int nt = 0; nt < BD_NT64; ++nt) {
-                const int j0 = 8 * BD_NT64 * nh + 8 * nt;      // token column
-                const float v0 = sm[BD_VN + (j0 + g) * PR + k0 + t], v1 = sm[BD_VN + (j0 + g) * PR + k0 + t + 4];
-                const float y0 = sm[BD_V + (j0 + g) * PR + k0 + t], y1 = sm[BD_V + (j0 + g) * PR + k0 + t + 4];
-                mma_tf32(accP[nt], fO, v0, v1);
-                mma_tf32(accA[nt], fD, y0, y1);
+            static_assert(BD_NT64 == 2 && BD_NT128 % 2 == 0, "fragment pairing below assumes two token n-tiles per warp");
+            {
+                const int j0 = 8 * BD_NT64 * nh;                  // token columns j0 .. j0 + 15
+                float vn[4], vv[4];
+                ldsm_x4(sm_u32 + (BD_VN + j0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(vn[0]), reinterpret_cast<uint32_t&>(vn[1]),
+                        reinterpret_cast<uint32_t&>(vn[2]), reinterpret_cast<uint32_t&>(vn[3]));
+                ldsm_x4(sm_u32 + (BD_V + j0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(vv[0]), reinterpret_cast<uint32_t&>(vv[1]),
+                        reinterpret_cast<uint32_t&>(vv[2]), reinterpret_cast<uint32_t&>(vv[3]));
+                mma_tf32(accP[0], fO, vn[0], vn[1]);
+                mma_tf32(accA[0], fD, vv[0], vv[1]);
+                mma_tf32(accP[1], fO, vn[2], vn[3]);
+                mma_tf32(accA[1], fD, vv[2], vv[3]);
             }
         }
         // ---- Zu = A^T dVn_h : [64 i] x [64 v of this half], contraction over the 64 tokens j ----
