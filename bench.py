@@ -46,6 +46,7 @@ EXTRA_WORKLOADS = {
     "varlen_64seq_65536_H32": dict(kind="varlen", n_seqs=64, total=65536, H=32),
     "cp_T262144_H32": dict(kind="cp", T=262144, H=32),
     "cp_T32768_H32": dict(kind="cp", T=32768, H=32),
+    "decode_N256_H32": dict(kind="decode", N=256, H=32),
 }
 
 
@@ -222,6 +223,22 @@ def run_extra(args, rank, world, local_rank):
                                  cu_seqlens=cu, output_final_state=True, **kw)
         tokens, metric = T * world, "chunk_kda varlen forward tokens/s"
         cfg = {"sequences_per_gpu": len(lens), "tokens_per_gpu": T, "min_len": min(lens), "max_len": max(lens)}
+    elif w["kind"] == "decode":
+        # one token for each of N sequences against a pool of fp32 states ((V, K) layout), shuffled slots
+        from cula_b200.kda import kda_decode
+        N = w["N"]
+        gen = torch.Generator().manual_seed(rank)
+        r = lambda *s_: torch.randn(*s_, generator=gen)
+        dq, dk, dv = (r(N, 1, H, 128).to(torch.bfloat16).to(dev) for _ in range(3))
+        da, db = (0.1 * r(N, 1, H, 128)).to(torch.bfloat16).to(dev), r(N, 1, H).to(torch.bfloat16).to(dev)
+        dA, dbias = (-2 * torch.rand(H, generator=gen)).to(dev), (0.1 * r(H, 128)).to(dev)
+        pool = (0.01 * r(N, H, 128, 128)).to(dev)
+        slots = torch.randperm(N, generator=gen).to(torch.int32).to(dev)
+        step = lambda: kda_decode(A_log=dA, dt_bias=dbias, q=dq, k=dk, v=dv, a=da, b=db, initial_state_source=pool,
+                                  initial_state_indices=slots)
+        tokens, metric, launches = N * world, "kda_decode tokens/s", 2
+        state_bytes = 2 * N * H * 128 * 128 * 4
+        cfg = {"sequences_per_gpu": N, "state_layout": "vk", "state_bytes_read_plus_written": state_bytes}
     else:   # context parallel: ONE sequence of T tokens split over the ranks
         T = w["T"]
         per = T // world
@@ -264,8 +281,14 @@ def run_extra(args, rank, world, local_rank):
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    extra = {}
+    if w["kind"] == "decode":
+        peaks = load_peaks()
+        ach = cfg["state_bytes_read_plus_written"] / (ms * 1e-3) / 1e9
+        extra["roofline"] = {"kernel": "kda_decode_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
+                             "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
     if rank == 0:
-        print(json.dumps({
+        print(json.dumps({**extra,
             "metric": metric, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",

@@ -18,6 +18,10 @@ namespace {
 inline bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 }
 
+extern "C" int kda_launch_decode(const void* q, const void* k, const void* v, const void* a, int a_fp32, const void* b, int b_fp32,
+                                 const float* A_log, const float* dt_bias, float* state, const int* indices, void* o,
+                                 int N, int H, int HV, int V, int pool, float scale, int use_l2norm, float softplus_beta,
+                                 float softplus_threshold, int state_kv, int* status, cudaStream_t stream);
 extern "C" int kda_fwd_intra_smem_bytes();
 extern "C" int kda_fwd_scan_smem_bytes();
 
@@ -90,6 +94,22 @@ extern "C" int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, cons
     if (misaligned(d_m_all) || misaligned(d_c_all) || misaligned(d_h0) || misaligned(d_s_out) || (stride_floats & 3))
         return CULA_KDA_EALIGN;
     return kda_launch_cp_fold(d_c_all, d_m_all, d_h0, d_s_out, n, H, stride_floats, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_decode(const void* d_q, const void* d_k, const void* d_v, const void* d_a, int a_is_fp32,
+                               const void* d_b, int b_is_fp32, const float* d_A_log, const float* d_dt_bias,
+                               float* d_state, const int* d_state_indices, void* d_o, int N, int H, int HV, int V,
+                               int pool_size, float scale, int use_qk_l2norm, float softplus_beta,
+                               float softplus_threshold, int state_is_kv, int* d_status, void* stream) {
+    if (N == 0) return 0;
+    if (!d_q || !d_k || !d_v || !d_a || !d_b || !d_A_log || !d_state || !d_o || !d_status) return CULA_KDA_EINVAL;
+    if (N < 0 || H <= 0 || HV <= 0 || HV % H != 0 || V <= 0 || V % 32 != 0 || pool_size <= 0) return CULA_KDA_EINVAL;
+    if (!(softplus_beta > 0.f)) return CULA_KDA_EINVAL;
+    if (!d_state_indices && pool_size < N) return CULA_KDA_EINVAL;
+    if (misaligned(d_q) || misaligned(d_k) || misaligned(d_state)) return CULA_KDA_EALIGN;
+    return kda_launch_decode(d_q, d_k, d_v, d_a, a_is_fp32, d_b, b_is_fp32, d_A_log, d_dt_bias, d_state, d_state_indices, d_o,
+                             N, H, HV, V, pool_size, scale, use_qk_l2norm, softplus_beta, softplus_threshold, state_is_kv,
+                             d_status, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cula_kda_bwd_scratch_floats(void) { return kda::BWD_SCRATCH_FLOATS; }

@@ -47,6 +47,7 @@ __host__ __device__ __forceinline__ int swz128(int row, int col) {
 // Status word values written by kernels whose bounded waits give up.
 constexpr int STATUS_OK = 0;
 constexpr int STATUS_WAIT_TIMEOUT = 1;
+constexpr int STATUS_BAD_INDEX = 2;        // a state-pool index past the end of the pool (decode)
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers

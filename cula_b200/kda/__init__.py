@@ -1,4 +1,5 @@
 from .chunk import chunk_kda, check_status  # noqa: F401
+from .decode import fused_sigmoid_gating_delta_rule_update, kda_decode  # noqa: F401
 from .host import chunk_kda_host  # noqa: F401
 
-__all__ = ["chunk_kda", "chunk_kda_host", "check_status"]
+__all__ = ["chunk_kda", "chunk_kda_host", "check_status", "kda_decode", "fused_sigmoid_gating_delta_rule_update"]

@@ -25,7 +25,8 @@ def _status_word(device):
 
 
 def check_status(device=None):
-    """Synchronise and raise if any kernel on ``device`` reported a pipeline wait that gave up."""
+    """Synchronise and raise if any kernel on ``device`` reported a problem (a bounded wait that gave up, a bad
+    state-pool index)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     word = _status_words.get(str(device))
     if word is None:
@@ -33,7 +34,8 @@ def check_status(device=None):
     code = int(word.item())
     if code != 0:
         word.zero_()
-        raise RuntimeError(f"cula_b200 kernel status {code}: a bounded in-kernel wait timed out")
+        what = {1: "a bounded in-kernel wait timed out", 2: "a state-pool index lies past the end of the pool"}
+        raise RuntimeError(f"cula_b200 kernel status {code}: {what.get(code, 'unknown')}")
 
 
 def _ptr(t):

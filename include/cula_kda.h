@@ -148,6 +148,24 @@ int cula_kda_cp_transition(const void* d_tiles, float* d_c_out, float* d_m_out,
 int cula_kda_cp_fold(const float* d_c_all, const float* d_m_all, const float* d_h0, float* d_s_out, int n, int H,
                      long long stride_floats, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * Decode: one token per sequence against a pool of fp32 states, updated in place (the step after prefill).
+ * Replaces the compiled CuTe-DSL callable behind kda_decode / fused_sigmoid_gating_delta_rule_update
+ * (cula/ops/kda_decode.py:1794-2096; kernel arguments at :2080-2094):
+ *   gate = exp(-exp(A_log[hv]) * softplus(a + dt_bias[hv,:])), v_new = sigmoid(b) (v - S^T (gate k)),
+ *   S <- diag(gate) S + k v_new^T, o = S^T (scale q), with q, k L2-normalised when use_qk_l2norm != 0.
+ * d_q, d_k [N,H,128] bf16; d_v, d_o [N,HV,V] bf16 (V % 32 == 0); d_a [N,HV,128] and d_b [N,HV] bf16 or fp32;
+ * d_A_log [HV]; d_dt_bias [HV,128] or NULL; d_state [pool_size,HV,V,128] (state_is_kv == 0, the reference's "vk"
+ * default) or [pool_size,HV,128,V] (state_is_kv != 0); d_state_indices [N] int32 pool slots or NULL (slot = n).
+ * A negative slot skips the sequence (no state access, its output row is zeroed); a slot >= pool_size sets *d_status to 2
+ * and touches nothing. HV must be a multiple of H (grouped value heads).
+ * ------------------------------------------------------------------------------------------------------------ */
+int cula_kda_decode(const void* d_q, const void* d_k, const void* d_v, const void* d_a, int a_is_fp32,
+                    const void* d_b, int b_is_fp32, const float* d_A_log, const float* d_dt_bias,
+                    float* d_state, const int* d_state_indices, void* d_o, int N, int H, int HV, int V,
+                    int pool_size, float scale, int use_qk_l2norm, float softplus_beta,
+                    float softplus_threshold, int state_is_kv, int* d_status, void* stream);
+
 /*
  * Whole forward pass (both launches above) for callers that cannot allocate device memory themselves -- a runtime
  * that has given all device memory to its own pool, a plugin inside a foreign memory manager, a path where
