@@ -236,7 +236,7 @@ def run_extra(args, rank, world, local_rank):
         slots = torch.randperm(N, generator=gen).to(torch.int32).to(dev)
         step = lambda: kda_decode(A_log=dA, dt_bias=dbias, q=dq, k=dk, v=dv, a=da, b=db, initial_state_source=pool,
                                   initial_state_indices=slots)
-        tokens, metric, launches = N * world, "kda_decode tokens/s", 2
+        tokens, metric, launches = N * world, "kda_decode tokens/s", 1
         state_bytes = 2 * N * H * 128 * 128 * 4
         cfg = {"sequences_per_gpu": N, "state_layout": "vk", "state_bytes_read_plus_written": state_bytes}
     else:   # context parallel: ONE sequence of T tokens split over the ranks
