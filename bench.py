@@ -165,7 +165,9 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "chunk_kda forward tokens/s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "B": B, "T": T, "H": H, "K": 128, "V": 128},
+        "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "H": H, "K": 128, "V": 128,
+                   "flags": "l2norm+gate in kernel, safe_gate, lower_bound=-5, final state",
+                   "sample": "one shard of the workload (B x T tokens) per step on the host cores of rank 0"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": f"each step = one full forward of B={B} T={T} H={H} on {cores} host threads "
                                    "(plain-C restatement of the reference's fp32 naive recurrence)"},
@@ -430,7 +432,7 @@ def main():
             dist.destroy_process_group()
         return
     base = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:      # the CPU baseline is timed at N = 1 only
         base, _ = cpu_baseline(B, T, H)
     line = {
         "metric": "chunk_kda forward tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",

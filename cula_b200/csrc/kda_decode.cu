@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodePar
         const int vbase = slice * per_cta + warp * rows_warp, k0 = 4 * lane;
         float4 row[8], nxt[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) row[i] = *reinterpret_cast<const float4*>(S + (size_t)(vbase + i) * DK + k0);
+        for (int i = 0; i < 8; ++i) row[i] = __ldcs(reinterpret_cast<const float4*>(S + (size_t)(vbase + i) * DK + k0));
         float gate[4], kh[4], qs[4];
         dec_key_vectors(p, n, hv, hq, k0, gate, kh, qs);
         float gk[4];
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodePar
             const int v0 = vbase + 8 * bi;
             if (bi + 1 < nb) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) nxt[i] = *reinterpret_cast<const float4*>(S + (size_t)(v0 + 8 + i) * DK + k0);
+                for (int i = 0; i < 8; ++i) nxt[i] = __ldcs(reinterpret_cast<const float4*>(S + (size_t)(v0 + 8 + i) * DK + k0));
             }
             float hk[8];
 #pragma unroll
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodePar
                 row[i].y = fmaf(gate[1], row[i].y, vn * kh[1]);
                 row[i].z = fmaf(gate[2], row[i].z, vn * kh[2]);
                 row[i].w = fmaf(gate[3], row[i].w, vn * kh[3]);
-                *reinterpret_cast<float4*>(S + (size_t)(v0 + i) * DK + k0) = row[i];
+                __stcs(reinterpret_cast<float4*>(S + (size_t)(v0 + i) * DK + k0), row[i]);
                 ov[i] = row[i].x * qs[0] + row[i].y * qs[1] + row[i].z * qs[2] + row[i].w * qs[3];
             }
 #pragma unroll
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodePar
     float4 row[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-        row[i] = *reinterpret_cast<const float4*>(S + (size_t)(32 * warp + rg + 4 * i) * p.V + c0 + 4 * cg);
+        row[i] = __ldcs(reinterpret_cast<const float4*>(S + (size_t)(32 * warp + rg + 4 * i) * p.V + c0 + 4 * cg));
     __syncthreads();
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodePar
         const float gt = s_gate[kk], kh = s_kh[kk], qv = s_qs[kk];
         row[i].x = fmaf(gt, row[i].x, kh * vn[0]); row[i].y = fmaf(gt, row[i].y, kh * vn[1]);
         row[i].z = fmaf(gt, row[i].z, kh * vn[2]); row[i].w = fmaf(gt, row[i].w, kh * vn[3]);
-        *reinterpret_cast<float4*>(S + (size_t)kk * p.V + c0 + 4 * cg) = row[i];
+        __stcs(reinterpret_cast<float4*>(S + (size_t)kk * p.V + c0 + 4 * cg), row[i]);
         acc.x = fmaf(row[i].x, qv, acc.x); acc.y = fmaf(row[i].y, qv, acc.y);
         acc.z = fmaf(row[i].z, qv, acc.z); acc.w = fmaf(row[i].w, qv, acc.w);
     }
