@@ -16,8 +16,9 @@
 //   layout "kv" (pool, HV, K, V): a CTA owns a 32-column value slice; a warp holds 32 key rows (8 lanes x
 //     float4 per row), the contractions reduce over lanes with equal column group and across the 4 warps
 //     through shared memory.
-// Grid = N * HV * slices CTAs of 128 threads (K = 128; V any multiple of 32; slices divides V / 32 and is
-// chosen on the host: 1 when there are enough states to fill the GPU, more for small batches).
+// Work items = N * HV * slices (K = 128; V any multiple of 32; slices divides V / 32 and is chosen on the host: 1
+// when there are enough states to fill the GPU, more for small batches); four persistent CTAs of 128 threads
+// per SM walk them.
 #include "kda_common.cuh"
 
 namespace kda {
@@ -83,9 +84,11 @@ __device__ __forceinline__ void dec_key_vectors(const DecodeParams& p, int n, in
     }
 }
 
-__global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodeParams p) {
+// One work item = one slice of one (sequence, value head) state.
+__device__ __forceinline__ void dec_item(const DecodeParams& p, const int item, float (*red)[4][32], float* s_gate, float* s_kh,
+                                         float* s_qs) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int slice = blockIdx.x % p.slices, nh = blockIdx.x / p.slices;
+    const int slice = item % p.slices, nh = item / p.slices;
     const int per_cta = p.V / p.slices;                     // value rows (vk) or columns (kv) of this CTA, a multiple of 32
     const int n = nh / p.HV, hv = nh - n * p.HV;
     const int hq = hv / (p.HV / p.H);
@@ -159,8 +162,6 @@ __global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodePar
 
     // ---- (K, V) rows: the CTA walks its value columns 32 at a time; warp w owns key rows 32w .. 32w+31, lane (rg, cg):
     //      row group rg = lane / 8 (rows rg, rg+4, ..., rg+28 of the warp's 32), column group cg = lane % 8 ----
-    __shared__ float red[2][4][32];
-    __shared__ float s_gate[DK], s_kh[DK], s_qs[DK];
     {
         float gate[4], kh[4], qs[4];
         dec_key_vectors(p, n, hv, hq, 4 * lane, gate, kh, qs);       // every warp computes the same 128 values
@@ -224,6 +225,16 @@ __global__ void __launch_bounds__(DEC_THREADS) kda_decode_kernel(const DecodePar
     }   // column chunks (the barriers above also order the reuse of `red`)
 }
 
+// Persistent: a few CTAs per SM walk the work items, so the short items do not pay a CTA launch each.
+__global__ void __launch_bounds__(DEC_THREADS, 4) kda_decode_kernel(const DecodeParams p, const int items) {
+    __shared__ float red[2][4][32];
+    __shared__ float s_gate[DK], s_kh[DK], s_qs[DK];
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        dec_item(p, item, red, s_gate, s_kh, s_qs);
+        if (p.state_kv) __syncthreads();                    // the shared vectors are rewritten by the next item
+    }
+}
+
 }  // namespace kda
 
 extern "C" int kda_launch_decode(const void* q, const void* k, const void* v, const void* a, int a_fp32, const void* b, int b_fp32,
@@ -244,6 +255,9 @@ extern "C" int kda_launch_decode(const void* q, const void* k, const void* v, co
     int slices = 1;
     while (slices < V / 32 && (long long)N * HV * slices < 8LL * sms && (V / 32) % (2 * slices) == 0) slices *= 2;
     p.slices = slices;
-    kda_decode_kernel<<<N * HV * slices, DEC_THREADS, 0, stream>>>(p);
+    const long long items = (long long)N * HV * slices;
+    if (items > 0x7fffffffLL) return -1;
+    const long long resident = 4LL * sms;                   // launch bounds keep four 128-thread CTAs resident per SM
+    kda_decode_kernel<<<(int)(items < resident ? items : resident), DEC_THREADS, 0, stream>>>(p, (int)items);
     return (int)cudaGetLastError();
 }
