@@ -2,7 +2,7 @@
 //   gate activation + per-chunk cumulative sum (log2 domain), q/k L2 normalisation,
 //   the gated 64x64 Gram matrices Aqk / L (one M=128 x N=160 TF32 UMMA chain, accumulators in TMEM),
 //   Akk = (I + L)^-1 (blocked 16 -> 32 -> 64 inverse in fp32),
-//   w = Akk (beta k 2^g), u = Akk (beta v) (two M=128 x N=64 FP16 UMMAs),
+//   [w | u] = Akk [beta k 2^g | beta v] (one M=128 x N=256 FP16 UMMA chain),
 //   kg = k 2^(g_last - g), qg = scale q 2^g,
 // and writes the tile pack the state scan consumes (layout in kda_common.cuh).
 //
@@ -18,7 +18,7 @@
 // is [q-hat ; k-hat] scaled by their own block anchors (128 rows). Column block I of the 128 x 160
 // product is valid on the rows of block I only; the epilogue reads exactly those.
 //
-// Two CTAs are resident per SM (111 KB shared memory, 256 TMEM columns each), so one CTA's MUFU-heavy
+// Two CTAs are resident per SM (107 KB shared memory, 256 TMEM columns each), so one CTA's MUFU-heavy
 // operand generation overlaps the other's MMA, inverse and epilogues.
 #include "kda_common.cuh"
 #include "kda_params.h"
@@ -37,9 +37,9 @@ constexpr int NPART = INTRA_THREADS / 128;       // row segments of the column s
 constexpr int SM_OPA = 0;                 // A operand of one 64-channel half: [2 k-atoms][128 rows][128 B], SW128
 constexpr int SM_OPB = 32768;             // B operand: [2 k-atoms][160 rows][128 B], SW128
 constexpr int SM_G = 73728;               // G [64][128] fp32
-constexpr int SM_TAB = 106496;            // 10 x [128] fp32 anchor tables
-constexpr int SM_MISC = 111616;           // beta[64], barriers, tmem base, half totals
-constexpr int SM_TOTAL = 113664;
+constexpr int SM_MISC = 106496;           // beta[64], barriers, tmem base, segment totals of the column scan
+constexpr int SM_TOTAL = 108544;
+static_assert(SM_MISC + 512 + NPART * 128 * 4 <= SM_TOTAL, "segment totals must fit the misc region");
 constexpr int KATOM_A = 16384, KATOM_B = 20480;
 // regions reused once the Gram MMAs have completed
 constexpr int SM_XS = SM_OPA;             // X = beta k 2^g, fp16 [2 mn-atoms][64 tokens][128 B], SW128 (MN-major B operand)

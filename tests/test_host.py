@@ -87,3 +87,37 @@ def test_library_exports_every_declared_symbol():
     assert handle.cula_kda_tile_pack_bytes() == 74240
     _native.lib().cula_kda_strerror.restype = ctypes.c_char_p
     assert b"invalid" in _native.lib().cula_kda_strerror(-1)
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/cula_kda.h is the FFI contract: it must compile as C (no C++ or torch types) and every entry point
+    must return int except the string helper."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("gcc is not available")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "cula_kda.h"\nint (*probe)(void) = cula_kda_tile_pack_bytes;\nint main(void) { return probe == 0; }\n')
+    out = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(src)],
+                         capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    header = open(os.path.join(ROOT, "include", "cula_kda.h")).read()
+    for ret, name in re.findall(r"^(\w[\w\s\*]*?)\s*\b(cula_kda_\w+)\s*\(", header, flags=re.M):
+        assert ret.strip() == ("const char*" if name == "cula_kda_strerror" else "int"), (ret, name)
+
+
+def test_decode_argument_errors_without_gpu():
+    from cula_b200.kda import fused_sigmoid_gating_delta_rule_update, kda_decode
+    q = torch.zeros(2, 1, 2, 128, dtype=torch.bfloat16)
+    v = torch.zeros(2, 1, 2, 128, dtype=torch.bfloat16)
+    a, b = torch.zeros(2, 1, 2, 128, dtype=torch.bfloat16), torch.zeros(2, 1, 2, dtype=torch.bfloat16)
+    A_log, dt_bias = torch.zeros(2), torch.zeros(2, 128)
+    with pytest.raises(NotImplementedError):
+        fused_sigmoid_gating_delta_rule_update(A_log, a, dt_bias, 1.0, 20.0, q, q, v, b, None, None, is_kda=False)
+    with pytest.raises(ValueError):
+        kda_decode(A_log, dt_bias, q, q, v, a, b, torch.zeros(2, 2, 128, 128), None, state_layout="hv")
+    with pytest.raises(AssertionError):
+        kda_decode(A_log, dt_bias, q.float(), q.float(), v, a, b, torch.zeros(2, 2, 128, 128), None)
+    with pytest.raises(RuntimeError):           # valid arguments, but no Blackwell device: the call refuses, no fallback
+        kda_decode(A_log, dt_bias, q, q, v, a, b, torch.zeros(2, 2, 128, 128), None)
