@@ -28,16 +28,21 @@ constexpr int ST_U = TP_HEAD_BYTES;                      // offset of the U half
 // Shared-memory layout of a pipeline stage. The full scan stages the whole head of a tile pack plus one U half and
 // runs one CTA per SM; the transition scan needs only W, KG, DECAY and the U half, packs them tightly, keeps two
 // stages (the producer warp pulls the chunks after those into L2) and so fits two CTAs per SM.
-template <bool TRANSITION>
+// NVH = value halves per CTA. 1: a CTA carries 64 value columns on 4 consumer warps (grid.x = 2), three stages.
+// 2: both halves on 8 consumer warps (two per scheduler, so one warp's dependent chain fills the other's bubbles in
+// the tensor pipe), the whole tile pack per stage, two stages; used when there are more scan CTAs than SMs.
+template <bool TRANSITION, int NVH>
 struct ScanLayout {
-    static constexpr int STAGES = SCAN_STAGES, STAGE_BYTES = SCAN_STAGE_BYTES;
+    static constexpr int CONSUMERS = SCAN_CONSUMERS * NVH;
+    static constexpr int STAGES = NVH == 2 ? 2 : SCAN_STAGES, STAGE_BYTES = TP_HEAD_BYTES + 8192 * NVH;
     static constexpr int W = TP_W, KG = TP_KG, DECAY = TP_DECAY, U = ST_U;
-    static constexpr int STG = SCAN_CONSUMERS * SCAN_STG_BYTES;
+    static constexpr int STG = CONSUMERS * SCAN_STG_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + STG + 64;
     static constexpr int CTAS_PER_SM = 1;
 };
 template <>
-struct ScanLayout<true> {
+struct ScanLayout<true, 1> {
+    static constexpr int CONSUMERS = SCAN_CONSUMERS;
     static constexpr int STAGES = 2;
     static constexpr int W = 0, KG = 16384, DECAY = 32768, U = 33280, STAGE_BYTES = 41472;
     static constexpr int STG = 0;
@@ -49,15 +54,18 @@ struct ScanLayout<true> {
 // four column groups per (sequence, head): groups 0,1 carry C (zero start, normal u; written to p.ht) and groups
 // 2,3 carry the K x K matrix M = prod_c (D_c - kg_c^T w_c) (identity start, u = 0; written to p.m_out). No output
 // rows are produced. Used by context parallelism.
-template <bool STORE_HV, bool TRANSITION>
-__global__ void __launch_bounds__(SCAN_THREADS, ScanLayout<TRANSITION>::CTAS_PER_SM) kda_fwd_scan_kernel(const ScanParams p) {
-    using L = ScanLayout<TRANSITION>;
+template <bool STORE_HV, bool TRANSITION, int NVH = 1>
+__global__ void __launch_bounds__((SCAN_CONSUMERS * NVH + 1) * 32, ScanLayout<TRANSITION, NVH>::CTAS_PER_SM)
+kda_fwd_scan_kernel(const ScanParams p) {
+    static_assert(NVH == 1 || (!STORE_HV && !TRANSITION), "both value halves per CTA: plain forward only");
+    using L = ScanLayout<TRANSITION, NVH>;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES + L::STG);
     uint64_t* empty = full + L::STAGES;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool is_m = TRANSITION && blockIdx.x >= 2;     // this CTA carries columns of M
-    const int vh = blockIdx.x & 1, h = blockIdx.y;
+    const int vh = NVH == 2 ? ((warp >> 2) & 1) : (blockIdx.x & 1), h = blockIdx.y;
+    const int pw = warp & 3;                             // 16-column slice of the value half
     const int n = p.seq_order ? p.seq_order[blockIdx.z] : blockIdx.z;
     int bos, len, chunk0;
     if (p.cu_seqlens) {
@@ -74,13 +82,13 @@ __global__ void __launch_bounds__(SCAN_THREADS, ScanLayout<TRANSITION>::CTAS_PER
     if (tid == 0) {
         for (int s = 0; s < L::STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], SCAN_CONSUMERS);
+            mbar_init(&empty[s], L::CONSUMERS);
         }
         fence_mbar_init();
     }
     __syncthreads();
 
-    if (warp == SCAN_CONSUMERS) {
+    if (warp == L::CONSUMERS) {
         // ------------------------------- producer warp -------------------------------
         if (TRANSITION) {
             const int u_off = vh ? TP_U1 : TP_U0;
@@ -118,16 +126,20 @@ __global__ void __launch_bounds__(SCAN_THREADS, ScanLayout<TRANSITION>::CTAS_PER
         }
         if (lane == 0) {
             for (int c = 0; c < nchunks; ++c) {
-                const int s = c % SCAN_STAGES, use = c / SCAN_STAGES;
+                const int s = c % L::STAGES, use = c / L::STAGES;
                 if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
                     atomicExch(p.status, STATUS_WAIT_TIMEOUT);
                     break;
                 }
                 const unsigned char* tile = p.tiles + ((size_t)(chunk0 + c) * p.H + h) * TP_BYTES;
-                unsigned char* dst = smem + s * SCAN_STAGE_BYTES;
-                mbar_arrive_expect_tx(&full[s], SCAN_STAGE_BYTES);
-                bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
-                bulk_g2s(dst + ST_U, tile + (vh ? TP_U1 : TP_U0), 8192, &full[s]);
+                unsigned char* dst = smem + s * L::STAGE_BYTES;
+                mbar_arrive_expect_tx(&full[s], L::STAGE_BYTES);
+                if (NVH == 2) {
+                    bulk_g2s(dst, tile, TP_BYTES, &full[s]);          // head + both U halves are contiguous
+                } else {
+                    bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
+                    bulk_g2s(dst + ST_U, tile + ((blockIdx.x & 1) ? TP_U1 : TP_U0), 8192, &full[s]);
+                }
             }
         }
         return;
@@ -136,7 +148,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, ScanLayout<TRANSITION>::CTAS_PER
     // ---------------------------------- consumer warps ----------------------------------
     const int g = lane >> 2, t = lane & 3;
     const int m = lane >> 3, r = lane & 7;          // ldmatrix/stmatrix: matrix index, row inside it
-    const int vb = vh * 64 + warp * 16;             // first value column of this warp
+    const int vb = vh * 64 + pw * 16;               // first value column of this warp
     unsigned char* stg = smem + L::STAGES * L::STAGE_BYTES + warp * SCAN_STG_BYTES;   // unused by the transition scan
     const uint32_t stg_u32 = smem_u32(stg);
 
@@ -258,8 +270,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, ScanLayout<TRANSITION>::CTAS_PER
 #pragma unroll
         for (int np = 0; np < 4; ++np) {
             uint32_t r0, r1, r2, r3;
-            int row = 8 * (2 * np + (m >> 1)) + r, ch = 2 * warp + (m & 1);
-            ldsm_x4_t(st + L::U + row * 128 + ((ch ^ r) << 4), r0, r1, r2, r3);
+            int row = 8 * (2 * np + (m >> 1)) + r, ch = 2 * pw + (m & 1);
+            ldsm_x4_t(st + L::U + (NVH == 2 ? vh * 8192 : 0) + row * 128 + ((ch ^ r) << 4), r0, r1, r2, r3);
             float2 f;
             f = unpack_f16(r0); acc[2 * np][0] = fmaf(-s_down, acc[2 * np][0], f.x); acc[2 * np][1] = fmaf(-s_down, acc[2 * np][1], f.y);
             f = unpack_f16(r1); acc[2 * np][2] = fmaf(-s_down, acc[2 * np][2], f.x); acc[2 * np][3] = fmaf(-s_down, acc[2 * np][3], f.y);
@@ -397,9 +409,20 @@ extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream
         if (e != cudaSuccess) return (int)e;
         kda_fwd_scan_kernel<true, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
     } else {
-        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        kda_fwd_scan_kernel<false, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (2LL * p->H * p->N > sms) {
+            // more half-state CTAs than SMs: carry both value halves in one CTA on eight consumer warps
+            using L2 = ScanLayout<false, 2>;
+            e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, L2::SMEM);
+            if (e != cudaSuccess) return (int)e;
+            kda_fwd_scan_kernel<false, false, 2><<<dim3(1, p->H, p->N), (L2::CONSUMERS + 1) * 32, L2::SMEM, stream>>>(*p);
+        } else {
+            e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            kda_fwd_scan_kernel<false, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+        }
     }
     return (int)cudaGetLastError();
 }
@@ -409,7 +432,7 @@ extern "C" int kda_launch_fwd_transition(const kda::ScanParams* p, cudaStream_t 
     using namespace kda;
     if (p->N <= 0) return 0;
     dim3 grid(4, p->H, p->N);
-    constexpr int smem = ScanLayout<true>::SMEM;
+    constexpr int smem = ScanLayout<true, 1>::SMEM;
     cudaError_t e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     kda_fwd_scan_kernel<false, true><<<grid, SCAN_THREADS, smem, stream>>>(*p);
