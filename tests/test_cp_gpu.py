@@ -23,7 +23,8 @@ def _oracle(inp):
 
 
 @pytest.mark.parametrize("segments", [1, 2])
-@pytest.mark.parametrize("world,T,gate_offset", [(2, 256, -8.0), (4, 1024, -8.0), (3, 64 * 5 + 17, -6.0), (4, 512, 0.0)])
+@pytest.mark.parametrize("world,T,gate_offset", [(2, 256, -8.0), (4, 1024, -8.0), (3, 64 * 5 + 17, -6.0), (4, 512, 0.0),
+                                                 (8, 64 * 8 * 3 + 40, -8.0)])
 def test_cp_emulated_ranks_match_oracle(world, T, gate_offset, segments):
     from cula_b200.kda import check_status
     from cula_b200.kda.cp import CudaBackend, cp_forward

@@ -137,3 +137,26 @@ def test_decode_argument_errors():
                                                v.unsqueeze(1), b.unsqueeze(1), state, None, is_kda=False)
     with pytest.raises(ValueError):        # out of the wrong shape
         kda_decode(initial_state_source=state, out=torch.empty(N, HV, 128, dtype=torch.bfloat16, device="cuda"), **args)
+
+
+def test_decode_large_batch_and_bad_index_status():
+    """A batch larger than the persistent grid, and a pool index past the end of the pool: reported, nothing touched."""
+    from cula_b200.kda import check_status, kda_decode
+    N, H, HV = 700, 2, 4
+    q, k, v, a, b, A_log, dt_bias, state = make_decode_inputs(N, H, HV, 128, 128, seed=5)
+    o_ref, s_ref = kda_decode_oracle(q, k, v, a, b, A_log, dt_bias, state)
+    pool = state.cuda()
+    args = dict(A_log=A_log.cuda(), dt_bias=dt_bias.cuda(), q=q.unsqueeze(1).cuda(), k=k.unsqueeze(1).cuda(),
+                v=v.unsqueeze(1).cuda(), a=a.unsqueeze(1).cuda(), b=b.unsqueeze(1).cuda())
+    o = kda_decode(initial_state_source=pool, initial_state_indices=None, **args)
+    torch.cuda.synchronize()
+    check_status()
+    check(o_ref, s_ref, o.squeeze(1), pool)
+    before = pool.clone()
+    bad = torch.arange(N, dtype=torch.int32)
+    bad[3] = N + 5
+    kda_decode(initial_state_source=pool[:N], initial_state_indices=bad.cuda(), **args)
+    with pytest.raises(RuntimeError, match="state-pool index"):
+        check_status()
+    assert torch.equal(pool[3], before[3])                   # the offending sequence touched nothing
+    check_status()                                           # the status word was cleared by the failed check
