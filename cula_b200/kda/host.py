@@ -59,6 +59,10 @@ def chunk_kda_host(q, k, v, g, beta, out=None, final_state_out=None, segment_tok
     # segment_tokens x B tokens.
     seg = min(max(CHUNK, (int(segment_tokens) * B // CHUNK) * CHUNK), ((T + CHUNK - 1) // CHUNK) * CHUNK)
     segments = [(b, s0, min(T, s0 + seg)) for b in range(B) for s0 in range(0, T, seg)]
+    b_l, s0_l, s1_l = segments[-1]
+    if s1_l - s0_l > 2 * CHUNK:                           # a short last segment: its compute and download are the exposed tail
+        cut = s0_l + (((s1_l - s0_l) * 3 // 4) // CHUNK) * CHUNK
+        segments[-1:] = [(b_l, s0_l, cut), (b_l, cut, s1_l)]
     n_seg = len(segments)
     if out is None:
         out = torch.empty(v.shape, dtype=v.dtype).pin_memory()
@@ -78,9 +82,7 @@ def chunk_kda_host(q, k, v, g, beta, out=None, final_state_out=None, segment_tok
     bufs = _segment_buffers(dev, host_in, 1, seg)       # reused across calls: a call ends synchronised (see below)
     in_ready = [torch.cuda.Event() for _ in range(n_seg)]
     done = [torch.cuda.Event() for _ in range(n_seg)]
-    with torch.cuda.stream(s_in):
-        beta_dev = beta.to(dev, non_blocking=True)       # small: the whole tensor in one copy
-    beta_dev.record_stream(main)
+    beta_dev = torch.empty(beta.shape, dtype=beta.dtype, device=dev)
     final_dev = torch.empty(B, H, 128, v.shape[-1], dtype=torch.float32, device=dev) if output_final_state else None
 
     def upload(i):
@@ -90,6 +92,8 @@ def chunk_kda_host(q, k, v, g, beta, out=None, final_state_out=None, segment_tok
                 s_in.wait_event(done[i - 2])              # the buffer set is free once its segment has been computed
             for src, dst in zip(host_in, bufs[i % 2]):
                 dst[0, : s1 - s0].copy_(src[b, s0:s1], non_blocking=True)
+            if i == 0:
+                beta_dev.copy_(beta, non_blocking=True)   # small: the whole tensor in one copy, behind the first blocks
             in_ready[i].record(s_in)
 
     upload(0)
