@@ -57,7 +57,7 @@ struct ScanLayout<true, 1> {
 template <bool STORE_HV, bool TRANSITION, int NVH = 1>
 __global__ void __launch_bounds__((SCAN_CONSUMERS * NVH + 1) * 32, ScanLayout<TRANSITION, NVH>::CTAS_PER_SM)
 kda_fwd_scan_kernel(const ScanParams p) {
-    static_assert(NVH == 1 || (!STORE_HV && !TRANSITION), "both value halves per CTA: plain forward only");
+    static_assert(NVH == 1 || !TRANSITION, "both value halves per CTA: not for the transition scan");
     using L = ScanLayout<TRANSITION, NVH>;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES + L::STG);
@@ -404,17 +404,23 @@ extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream
     if (p->N <= 0) return 0;
     dim3 grid(2, p->H, p->N);
     cudaError_t e;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const bool both_halves = 2LL * p->H * p->N > sms;      // more half-state CTAs than SMs: eight consumer warps per CTA
+    using L2 = ScanLayout<false, 2>;
     if (p->vnew_out) {
-        e = cudaFuncSetAttribute(kda_fwd_scan_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        kda_fwd_scan_kernel<true, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+        if (both_halves) {
+            e = cudaFuncSetAttribute(kda_fwd_scan_kernel<true, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, L2::SMEM);
+            if (e != cudaSuccess) return (int)e;
+            kda_fwd_scan_kernel<true, false, 2><<<dim3(1, p->H, p->N), (L2::CONSUMERS + 1) * 32, L2::SMEM, stream>>>(*p);
+        } else {
+            e = cudaFuncSetAttribute(kda_fwd_scan_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            kda_fwd_scan_kernel<true, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+        }
     } else {
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (2LL * p->H * p->N > sms) {
-            // more half-state CTAs than SMs: carry both value halves in one CTA on eight consumer warps
-            using L2 = ScanLayout<false, 2>;
+        if (both_halves) {
             e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, L2::SMEM);
             if (e != cudaSuccess) return (int)e;
             kda_fwd_scan_kernel<false, false, 2><<<dim3(1, p->H, p->N), (L2::CONSUMERS + 1) * 32, L2::SMEM, stream>>>(*p);

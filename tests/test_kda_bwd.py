@@ -170,3 +170,13 @@ def test_backward_is_deterministic_except_atomics():
     runs = [run_both(inp, do, dht)[1] for _ in range(2)]
     for n in ("q", "k", "v", "g", "beta", "initial_state"):
         assert torch.equal(runs[0][n], runs[1][n]), n
+
+
+def test_backward_with_more_scan_ctas_than_sms():
+    """B * H * 2 > 148: the forward scans (plain and state-keeping) carry both value halves per CTA."""
+    inp = make_inputs(5, 130, 16, seed=9, h0_std=0.1)
+    gen = torch.Generator().manual_seed(10)
+    do = torch.randn(5, 130, 16, 128, generator=gen).to(torch.bfloat16)
+    dht = 0.1 * torch.randn(5, 16, 128, 128, generator=gen)
+    ref, got = run_both(inp, do, dht)
+    assert_grads(ref, got, HEADLINE_TOL, "wide grid")

@@ -209,3 +209,21 @@ def test_host_pipelined_forward_matches_device_call():
                           lower_bound=-5.0, A_log=d["A_log"], dt_bias=d["dt_bias"])
     torch.cuda.synchronize()
     assert o_h.device.type == "cpu" and torch.equal(o_h, o_d.cpu()) and torch.equal(ht_h, ht_d.cpu())
+
+
+def test_intermediate_states_do_not_depend_on_the_scan_variant():
+    """return_intermediate_states for a batch wide enough for the eight-warp scan CTAs (B * H * 2 > 148) must equal,
+    bit for bit, the states of the same sequences run in two narrower batches (four-warp CTAs)."""
+    from cula_b200.kda import chunk_kda
+    B, T, H = 6, 200, 16
+    inp = make_inputs(B, T, H, seed=12, h0_std=0.3)
+    d = {k: v.cuda() for k, v in inp.items()}
+    kw = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=d["A_log"],
+              dt_bias=d["dt_bias"], output_final_state=True, return_intermediate_states=True)
+    with torch.inference_mode():
+        o, ht, h = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"], **kw)
+        parts = [chunk_kda(d["q"][s], d["k"][s], d["v"][s], d["g"][s], d["beta"][s], initial_state=d["initial_state"][s], **kw)
+                 for s in (slice(0, 3), slice(3, 6))]
+    torch.cuda.synchronize()
+    assert torch.equal(o, torch.cat([p[0] for p in parts])) and torch.equal(ht, torch.cat([p[1] for p in parts]))
+    assert torch.equal(h, torch.cat([p[2] for p in parts]))
