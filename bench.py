@@ -143,6 +143,30 @@ def cpu_baseline(B, T, H, budget_s=10.0):
                        f"restatement of the fp32 naive recurrence"), dt / reps
 
 
+def cpu_config1():
+    """The reference's own CPU-runnable case (B=1, T=512, H=4): the C restatement and the torch restatement of the
+    naive recurrence, tokens/s each, a few passes."""
+    from cula_b200.synthetic import make_inputs
+    from oracle import c_oracle
+    from oracle.naive_kda import chunk_kda_oracle
+    B, T, H = WORKLOADS["fwd_B1_T512_H4"]
+    inp = make_inputs(B, T, H, seed=0)
+    f = lambda x: x.float().numpy()
+    a = [f(inp[k]) for k in ("q", "k", "v", "g", "beta")] + [f(inp["A_log"]), f(inp["dt_bias"]), None]
+    c_run = lambda: c_oracle.naive_kda_fwd(*a, use_l2norm=True, gate_mode=2, lower_bound=-5.0)
+    t_run = lambda: chunk_kda_oracle(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], output_final_state=True,
+                                     use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+                                     A_log=inp["A_log"], dt_bias=inp["dt_bias"])
+    out = {"workload": "fwd_B1_T512_H4", "torch_threads": torch.get_num_threads()}
+    for name, run, reps in (("c_tokens_per_s", c_run, 20), ("torch_tokens_per_s", t_run, 3)):
+        run()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            run()
+        out[name] = B * T * reps / (time.perf_counter() - t0)
+    return out
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -439,6 +463,7 @@ def main():
     base = None
     if not args.no_cpu_baseline and world == 1:      # the CPU baseline is timed at N = 1 only
         base, _ = cpu_baseline(B, T, H)
+        base["config1"] = cpu_config1()
     line = {
         "metric": "chunk_kda forward tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
