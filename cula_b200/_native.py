@@ -23,6 +23,8 @@ SIGNATURES = {
     "cula_kda_cp_transition": (_i, [_vp, _fp, _fp, _ip, _ip, _i, _i, _i, _ip, _vp]),
     "cula_kda_cp_fold": (_i, [_fp, _fp, _fp, _fp, _i, _i, ctypes.c_longlong, _vp]),
     "cula_kda_decode": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _fp, _fp, _fp, _ip, _vp, _i, _i, _i, _i, _i, _f, _i, _f, _f, _i, _ip, _vp]),
+    "cula_kda_num_chunks": (_i, [_ip, _i]),
+    "cula_kda_build_chunk_tables": (_i, [_ip, _i, _ip, _ip, _ip]),
     "cula_kda_bwd_scratch_floats": (_i, []),
     "cula_kda_bwd_grad_scale": (_i, [_vp, ctypes.c_longlong, _fp, ctypes.c_longlong, _vp, _fp, _vp]),
     "cula_kda_bwd_scan": (_i, [_vp, _vp, _fp, _fp, _vp, _fp, _fp, _ip, _ip, _ip, _i, _i, _i, _ip, _vp]),

@@ -112,6 +112,49 @@ extern "C" int cula_kda_decode(const void* d_q, const void* d_k, const void* d_v
                              d_status, static_cast<cudaStream_t>(stream));
 }
 
+// ---- host-side index tables for a packed batch (plain host memory in, plain host memory out) ----
+extern "C" int cula_kda_num_chunks(const int* h_cu_seqlens, int N) {
+    if (!h_cu_seqlens || N < 0 || h_cu_seqlens[0] != 0) return CULA_KDA_EINVAL;
+    long long total = 0;
+    for (int n = 0; n < N; ++n) {
+        const int len = h_cu_seqlens[n + 1] - h_cu_seqlens[n];
+        if (len < 0) return CULA_KDA_EINVAL;
+        total += (len + kda::BT - 1) / kda::BT;
+    }
+    return total > 0x7fffffffLL ? CULA_KDA_ETOOBIG : (int)total;
+}
+
+extern "C" int cula_kda_build_chunk_tables(const int* h_cu_seqlens, int N, int* h_chunk_indices, int* h_chunk_offsets,
+                                           int* h_seq_order) {
+    const int total = cula_kda_num_chunks(h_cu_seqlens, N);
+    if (total < 0) return total;
+    if (!h_chunk_indices || !h_chunk_offsets) return CULA_KDA_EINVAL;
+    int c = 0;
+    for (int n = 0; n < N; ++n) {
+        h_chunk_offsets[n] = c;
+        const int chunks = (h_cu_seqlens[n + 1] - h_cu_seqlens[n] + kda::BT - 1) / kda::BT;
+        for (int i = 0; i < chunks; ++i, ++c) {
+            h_chunk_indices[2 * c] = n;
+            h_chunk_indices[2 * c + 1] = i;
+        }
+    }
+    h_chunk_offsets[N] = c;
+    if (h_seq_order) {            // longest sequence first, ties in input order (stable insertion sort: N is small)
+        for (int n = 0; n < N; ++n) {
+            const int len = h_cu_seqlens[n + 1] - h_cu_seqlens[n];
+            int pos = n;
+            while (pos > 0) {
+                const int m = h_seq_order[pos - 1];
+                if (h_cu_seqlens[m + 1] - h_cu_seqlens[m] >= len) break;
+                h_seq_order[pos] = m;
+                --pos;
+            }
+            h_seq_order[pos] = n;
+        }
+    }
+    return 0;
+}
+
 extern "C" int cula_kda_bwd_scratch_floats(void) { return kda::BWD_SCRATCH_FLOATS; }
 
 extern "C" int cula_kda_bwd_grad_scale(const void* d_do, long long n_do, const float* d_dht, long long n_dht,

@@ -82,6 +82,18 @@ int cula_kda_fwd_scan(const void* d_tiles, const float* d_h0, void* d_o, float* 
                       const int* d_cu_seqlens, const int* d_chunk_offsets, const int* d_seq_order,
                       int N, int T, int H, int* d_status, void* stream);
 
+/*
+ * Index tables of a packed batch, computed on the host from HOST memory (h_*): what prepare_chunk_indices
+ * (fla/ops/utils/index.py:138-149) and prepare_chunk_offsets_i32 (cula/ops/chunk_delta_h.py:42-47) produce with torch.
+ * cula_kda_num_chunks: sum of ceil(len / 64) over the N sequences (< 0 on a bad cu_seqlens).
+ * cula_kda_build_chunk_tables: h_chunk_indices [num_chunks][2] (sequence, chunk in sequence), h_chunk_offsets [N+1]
+ * (first global chunk of every sequence), h_seq_order [N] or NULL (sequences by decreasing length, the launch order
+ * cula_kda_fwd_scan balances a ragged batch with). The caller copies them to the device.
+ */
+int cula_kda_num_chunks(const int* h_cu_seqlens, int N);
+int cula_kda_build_chunk_tables(const int* h_cu_seqlens, int N, int* h_chunk_indices, int* h_chunk_offsets,
+                                int* h_seq_order);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Backward pass. The reference's backward is all Triton / flash-linear-attention kernels plus a recompute of
  * its forward intermediates (cula/kda/chunk_bwd.py:432-604); here it is four launches after re-running the two

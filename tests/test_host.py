@@ -121,3 +121,24 @@ def test_decode_argument_errors_without_gpu():
         kda_decode(A_log, dt_bias, q.float(), q.float(), v, a, b, torch.zeros(2, 2, 128, 128), None)
     with pytest.raises(RuntimeError):           # valid arguments, but no Blackwell device: the call refuses, no fallback
         kda_decode(A_log, dt_bias, q, q, v, a, b, torch.zeros(2, 2, 128, 128), None)
+
+
+def test_c_side_chunk_tables_match_the_python_ones():
+    lib = _native.lib()
+    cases = [[0, 15, 85, 149, 186], [0, 64, 64, 70], [0, 1], [0, 8192, 8255, 8255 + 63]]
+    for cu in cases:
+        cu_t = torch.tensor(cu, dtype=torch.int32)
+        N = len(cu) - 1
+        total = lib.cula_kda_num_chunks(cu_t.data_ptr(), N)
+        idx_ref = prepare_chunk_indices(cu_t)
+        assert total == idx_ref.shape[0]
+        idx = torch.empty(max(total, 1), 2, dtype=torch.int32)
+        off = torch.empty(N + 1, dtype=torch.int32)
+        order = torch.empty(N, dtype=torch.int32)
+        assert lib.cula_kda_build_chunk_tables(cu_t.data_ptr(), N, idx.data_ptr(), off.data_ptr(), order.data_ptr()) == 0
+        assert idx[:total].tolist() == idx_ref.tolist()
+        assert off.tolist() == prepare_chunk_offsets(cu_t).tolist()
+        assert order.tolist() == VarlenTables(cu_t).seq_order.tolist()
+    bad = torch.tensor([0, 10, 5], dtype=torch.int32)
+    assert lib.cula_kda_num_chunks(bad.data_ptr(), 2) < 0
+    assert lib.cula_kda_num_chunks(torch.tensor([3, 10], dtype=torch.int32).data_ptr(), 1) < 0
