@@ -57,3 +57,29 @@ def test_c_host_program_matches_oracle(tmp_path):
     assert err_ratio(torch.from_numpy(o_ref), o.float()) <= 5e-3
     assert float((torch.from_numpy(o_ref) - o.float()).abs().max()) <= 2e-2
     assert err_ratio(torch.from_numpy(ht_ref), ht) <= 2e-3
+
+
+@pytest.mark.gpu
+def test_c_host_program_packed_batch(tmp_path):
+    """The same program on a packed batch: index tables from cula_kda_build_chunk_tables, per-sequence states."""
+    _native.lib()
+    exe = _compile(str(tmp_path / "forward_from_c"))
+    lens, H = [15, 70, 64, 37, 130], 2
+    T, N = sum(lens), len(lens)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    inp = make_inputs(1, T, H, seed=9, gate_offset=-6.0)
+    h0 = 0.5 * torch.randn(N, H, 128, 128, generator=torch.Generator().manual_seed(1))
+    raw = lambda t: t.contiguous().view(torch.int16).numpy() if t.dtype == torch.bfloat16 else t.contiguous().numpy()
+    for name, t in (("q", inp["q"]), ("k", inp["k"]), ("v", inp["v"]), ("g", inp["g"]), ("beta", inp["beta"]),
+                    ("A_log", inp["A_log"]), ("dt_bias", inp["dt_bias"]), ("h0", h0), ("cu_seqlens", cu)):
+        raw(t).tofile(str(tmp_path / f"{name}.bin"))
+    res = subprocess.run([exe, str(tmp_path), "1", str(T), str(H)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "C_HOST_OK" in res.stdout, res.stdout + res.stderr
+    o = torch.from_numpy(np.fromfile(str(tmp_path / "o.bin"), dtype=np.int16)).view(torch.bfloat16).view(1, T, H, 128)
+    ht = torch.from_numpy(np.fromfile(str(tmp_path / "ht.bin"), dtype=np.float32)).view(N, H, 128, 128)
+    f = lambda x: x.float().numpy()
+    o_ref, ht_ref = c_oracle.naive_kda_fwd(f(inp["q"]), f(inp["k"]), f(inp["v"]), f(inp["g"]), f(inp["beta"]), f(inp["A_log"]),
+                                           f(inp["dt_bias"]), f(h0), cu_seqlens=cu.numpy(), use_l2norm=True, gate_mode=2,
+                                           lower_bound=-5.0)
+    assert err_ratio(torch.from_numpy(o_ref), o.float()) <= 5e-3
+    assert err_ratio(torch.from_numpy(ht_ref), ht) <= 2e-3
