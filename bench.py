@@ -33,13 +33,32 @@ WORKLOADS = {
     "fwd_B4_T8192_H32": (4, 8192, 32),
     "fwd_B1_T512_H4": (1, 512, 4),
 }
+KERNEL_SOURCES = {"kda_fwd_intra_kernel": "kda_fwd_intra.cu", "kda_fwd_scan_kernel": "kda_fwd_scan.cu"}
+
+
+def ncu_traffic(workload, kernel):
+    """DRAM bytes (read + write) of one launch from the ncu summary committed for this kernel and workload. The
+    summary records the hash of the kernel source it was captured from; if the source has changed since, the
+    figure is stale and None is reported instead. Returns (bytes or None, note)."""
+    import hashlib
+    import re
+    path = os.path.join(ROOT, "profiles", f"{kernel}_{workload.replace('fwd_', '')}.md")
+    src = os.path.join(ROOT, "cula_b200", "csrc", KERNEL_SOURCES.get(kernel, ""))
+    if not (os.path.exists(path) and os.path.isfile(src)):
+        return None, "no ncu summary for this kernel and workload"
+    text = open(path).read()
+    m_bytes = re.search(r"dram_bytes_per_launch:\s*(\d+)", text)
+    m_sha = re.search(r"kernel_source_sha256:\s*([0-9a-f]{16})", text)
+    if not (m_bytes and m_sha):
+        return None, "the ncu summary carries no machine-readable traffic line"
+    sha = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16]
+    if sha != m_sha.group(1):
+        return None, f"stale: {os.path.basename(path)} was captured from another revision of {KERNEL_SOURCES[kernel]}"
+    return int(m_bytes.group(1)), f"ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch ({os.path.basename(path)})"
+
+
 # Secondary workloads (selected with --workload; not the headline line): forward+backward, the packed varlen
 # forward, and the context-parallel forward of one long sequence split over the ranks (strong scaling).
-# DRAM bytes of one launch, from the ncu captures summarised under profiles/ (same command line as this script)
-NCU_TRAFFIC_BYTES = {
-    ("fwd_B2_T2048_H32", "kda_fwd_intra_kernel"): 135190272 + 104998656,
-    ("fwd_B2_T2048_H32", "kda_fwd_scan_kernel"): 152075520 + 21043968,
-}
 EXTRA_WORKLOADS = {
     "fwdbwd_B4_T8192_H32": dict(kind="fwdbwd", B=4, T=8192, H=32),
     "fwdbwd_B2_T2048_H32": dict(kind="fwdbwd", B=2, T=2048, H=32),
@@ -65,9 +84,20 @@ def varlen_lengths(n_seqs=64, total=65536, seed=0):
         diff -= step
         i += 1
     return lens.tolist()
+
+
 FLOP_PER_TOKEN_HEAD = 180224          # dense-tile convention, forward
 BYTES_PER_TOKEN_HEAD = 1282           # compulsory forward traffic: q,k,v,g bf16 + beta + o
 TILE_PACK_BYTES = 74240
+
+
+def headline_config(workload):
+    """The `config` object of the JSON line; both arms (ours, --impl reference) print exactly this."""
+    B, T, H = WORKLOADS[workload]
+    return {"workload": workload, "B_per_gpu": B, "T": T, "H": H, "K": 128, "V": 128,
+            "flags": "l2norm+gate in kernel, safe_gate, lower_bound=-5, final state",
+            "l2": "256 MB flush buffer written before every timed step",
+            "sharding": "batch x head shards, one per rank, no collective"}
 
 
 def load_peaks():
@@ -125,6 +155,7 @@ def cpu_baseline(B, T, H, budget_s=10.0):
     """Time the plain-C oracle on the host cores on the same workload; tokens/s."""
     from cula_b200.synthetic import make_inputs
     from oracle import c_oracle
+    c_oracle.use_all_cores()
     inp = make_inputs(B, T, H, seed=0)
     f = lambda x: x.float().numpy()
     args = [f(inp[k]) for k in ("q", "k", "v", "g", "beta")]
@@ -177,6 +208,7 @@ def run_reference(args, rank, world):
     f = lambda x: x.float().numpy()
     a = [f(inp[k]) for k in ("q", "k", "v", "g", "beta")] + [f(inp["A_log"]), f(inp["dt_bias"]), None]
     run = lambda: c_oracle.naive_kda_fwd(*a, use_l2norm=True, gate_mode=2, lower_bound=-5.0)
+    cores = c_oracle.use_all_cores()         # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers
     for _ in range(args.warmup):
         run()
     t0 = time.perf_counter()
@@ -184,20 +216,140 @@ def run_reference(args, rank, world):
         run()
     dt = (time.perf_counter() - t0) / args.steps
     val = B * T / dt
-    cores = c_oracle.num_threads()
     print(json.dumps({
         "impl": "reference", "metric": "chunk_kda forward tokens/s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "H": H, "K": 128, "V": 128,
-                   "flags": "l2norm+gate in kernel, safe_gate, lower_bound=-5, final state",
-                   "sample": "one shard of the workload (B x T tokens) per step on the host cores of rank 0"},
+        "config": headline_config(args.workload),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"each step = one full forward of B={B} T={T} H={H} on {cores} host threads "
-                                   "(plain-C restatement of the reference's fp32 naive recurrence)"},
+                         "sample": f"each step = one full forward of one rank's shard (B={B} T={T} H={H}) on {cores} "
+                                   "host threads of rank 0 (plain-C restatement of the reference's fp32 naive "
+                                   "recurrence); no L2 flush and no sharding apply to the CPU arm"},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }), flush=True)
+
+
+CP_TOKENS, CP_HEADS = 262144, 32
+
+
+def cp_section(rank, world, dev, flush, steps=10, T_total=CP_TOKENS, H=CP_HEADS):
+    """Context-parallel forward of ONE sequence of ``T_total`` tokens cut into ``world`` contiguous shards (strong
+    scaling): chunk-parallel stage, transition scan, NCCL all-gather of (C | M), folds, final scan -- the collective
+    is inside the timed region, every step starts from a barrier, the time is the max over ranks. Also: the time
+    of each stage (max over ranks, one instrumented step), the time of the same sequence on ONE GPU measured in
+    this run on rank 0's device (`t1_ms`; at world 1 it is the run itself), and an untimed parity check on a
+    weak-gate sequence of 4096 tokens per rank whose state really crosses the shard boundaries, against the
+    single-pass, unsegmented forward of the whole sequence on rank 0."""
+    import torch.distributed as dist
+    import cula_b200.kda.cp as cp
+    from cula_b200.kda import check_status, chunk_kda
+    from cula_b200.synthetic import make_inputs_on_device
+    kw = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def rank_max(values):
+        t = torch.tensor(values, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(x) for x in t.tolist()]
+
+    def timed(fn, n, entry_barrier):
+        evs = []
+        for _ in range(n):
+            flush.zero_()
+            if entry_barrier and world > 1:
+                dist.barrier()              # the ranks enter every step together
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / n
+
+    per = T_total // world
+    d = make_inputs_on_device(1, per, H, dev, seed=100 + rank)       # this rank's shard
+    step = lambda marks=None: cp.chunk_kda_cp(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"],
+                                              dt_bias=d["dt_bias"], output_final_state=True, stage_marks=marks, **kw)
+    for _ in range(3):
+        step()
+    sync_all()
+    ms = rank_max([timed(step, steps, True)])[0]
+    marks = []
+    timed(lambda: step(marks), 1, True)
+    names = [n for n, _ in marks[1:]]
+    stage_ms = rank_max([marks[i][1].elapsed_time(marks[i + 1][1]) for i in range(len(marks) - 1)])
+    check_status(dev)
+    sync_all()
+
+    # ---- the same sequence on one GPU (rank 0's), for the strong-scaling efficiency ----
+    t1 = ms
+    if world > 1:
+        del d
+        if rank == 0:
+            full = make_inputs_on_device(1, T_total, H, dev, seed=100)
+            one = lambda: chunk_kda(full["q"], full["k"], full["v"], full["g"], full["beta"], A_log=full["A_log"],
+                                    dt_bias=full["dt_bias"], output_final_state=True, **kw)
+            for _ in range(3):
+                one()
+            torch.cuda.synchronize()
+            t1 = timed(one, max(3, steps // 2), False)
+            del full
+        torch.cuda.empty_cache()
+        t1 = rank_max([t1 if rank == 0 else 0.0])[0]
+        sync_all()
+
+    # ---- parity: weak gates, 4096 tokens per rank, initial state on rank 0 only ----
+    Tp = 4096 * world
+    full = make_inputs_on_device(1, Tp, H, dev, seed=7, gate_offset=-8.0, h0_std=0.5)   # the same numbers on every rank
+    sl = slice(rank * 4096, (rank + 1) * 4096)
+    sh = {n: (t[:, sl].contiguous() if n in ("q", "k", "v", "g", "beta") else t) for n, t in full.items()}
+    o_cp, ht_cp = cp.chunk_kda_cp(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], A_log=sh["A_log"], dt_bias=sh["dt_bias"],
+                                  initial_state=sh["initial_state"] if rank == 0 else None, output_final_state=True, **kw)
+    if world > 1:
+        parts = [torch.empty_like(o_cp) for _ in range(world)]
+        dist.all_gather(parts, o_cp.contiguous())
+        o_all = torch.cat(parts, dim=1)
+        ht_all = ht_cp if ht_cp is not None else torch.empty(1, H, 128, 128, dtype=torch.float32, device=dev)
+        dist.broadcast(ht_all, src=world - 1)
+    else:
+        o_all, ht_all = o_cp, ht_cp
+    parity = None
+    if rank == 0:
+        cp.MAX_AUTO_SEGMENTS = 1            # the yardstick is the plain single-pass scan of the whole sequence
+        o_ref, ht_ref = chunk_kda(full["q"], full["k"], full["v"], full["g"], full["beta"], A_log=full["A_log"],
+                                  dt_bias=full["dt_bias"], initial_state=full["initial_state"], output_final_state=True, **kw)
+        cp.MAX_AUTO_SEGMENTS = 4
+        rel = lambda a, b: float((a.double() - b.double()).norm() / b.double().norm())
+        # what the carried state contributes: the forward of the last 4096 tokens alone, from a zero state
+        tail = {n: full[n][:, -4096:].contiguous() for n in ("q", "k", "v", "g", "beta")}
+        o_cut, _ = chunk_kda(tail["q"], tail["k"], tail["v"], tail["g"], tail["beta"], A_log=full["A_log"],
+                             dt_bias=full["dt_bias"], **kw)
+        parity = {"tokens": Tp, "gate_offset": -8.0,
+                  "o_rel_rms": rel(o_all.float(), o_ref.float()), "ht_rel": rel(ht_all, ht_ref),
+                  "o_rel_rms_if_state_dropped": rel(o_cut.float(), o_ref[:, -4096:].float()),
+                  "against": "single-pass unsegmented chunk_kda of the whole sequence on rank 0"}
+        torch.cuda.synchronize()
+        check_status(dev)
+        if not (parity["o_rel_rms"] <= 5e-3 and parity["ht_rel"] <= 2e-3):
+            raise RuntimeError(f"context-parallel parity failed: {parity}")
+    sync_all()
+    return {"workload": f"cp_T{T_total}_H{H}", "scaling": "strong", "n_gpus": world, "steps": steps, "ms_per_step": ms,
+            "tokens_per_s": T_total / (ms * 1e-3), "t1_ms": t1, "efficiency": t1 / (world * ms),
+            "t1_source": "the same sequence through chunk_kda on rank 0's GPU alone, in this run "
+                         "(segmented scan: the best single-GPU path)",
+            "per_rank_ms": dict(zip(names, stage_ms)),
+            "exchange": "one all-gather of (C|M) [2,H,128,128] fp32 per rank over NCCL, inside the timed region",
+            "parity": parity}
 
 
 def run_extra(args, rank, world, local_rank):
@@ -206,7 +358,6 @@ def run_extra(args, rank, world, local_rank):
     import torch.distributed as dist
     from cula_b200 import _native
     from cula_b200.kda import check_status, chunk_kda
-    from cula_b200.kda.cp import chunk_kda_cp
     from cula_b200.synthetic import make_inputs
 
     if args.impl == "reference":
@@ -266,15 +417,23 @@ def run_extra(args, rank, world, local_rank):
         state_bytes = 2 * N * H * 128 * 128 * 4
         cfg = {"sequences_per_gpu": N, "state_layout": "vk", "state_bytes_read_plus_written": state_bytes}
     else:   # context parallel: ONE sequence of T tokens split over the ranks
-        T = w["T"]
-        per = T // world
-        inp = make_inputs(1, per, H, seed=100 + rank)       # this rank's shard
-        d = {k: v.to(dev) for k, v in inp.items() if v is not None}
-        step = lambda: chunk_kda_cp(d["q"], d["k"], d["v"], d["g"], d["beta"], A_log=d["A_log"], dt_bias=d["dt_bias"],
-                                    output_final_state=True, **kw)
-        tokens, metric, scaling, launches = T, "chunk_kda context-parallel forward tokens/s", "strong", (6 if world > 1 else 2)
-        cfg = {"T_total": T, "T_per_gpu": per, "exchange": "one all-gather of (C|M) [2,H,128,128] fp32 per rank over NCCL",
-               "segments_per_shard": 2 if world > 1 else 1}
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        res = cp_section(rank, world, dev, flush, steps=args.steps, T_total=w["T"], H=H)
+        clocks = sampler.stop() if rank == 0 else None
+        if rank == 0:
+            print(json.dumps({"metric": "chunk_kda context-parallel forward tokens/s", "value": res["tokens_per_s"],
+                              "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": 3,
+                              "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                              "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                              "config": {"workload": args.workload, "H": H, "K": 128, "V": 128,
+                                         "l2": "256 MB flush buffer written before every timed step"},
+                              "cp": res, "clocks": clocks}), flush=True)
+        if dist.is_initialized():
+            dist.destroy_process_group()
+        return
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def barrier():
@@ -290,13 +449,10 @@ def run_extra(args, rank, world, local_rank):
         sampler.start()
         time.sleep(0.5)
     evs = []
-    if not (w["kind"] == "cp" and world > 1):     # (the context-parallel steps start from a host barrier instead)
-        for _ in range(8):                        # untimed device work queued first: the host gets ahead of the device
-            flush.zero_()
+    for _ in range(8):                            # untimed device work queued first: the host gets ahead of the device
+        flush.zero_()
     for _ in range(args.steps):
         flush.zero_()
-        if w["kind"] == "cp" and world > 1:
-            dist.barrier()                      # ranks enter every step together; the collective is inside the timed region
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         step()
@@ -336,6 +492,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="fwd_B2_T2048_H32", choices=sorted(WORKLOADS) + sorted(EXTRA_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cp", action="store_true", help="skip the context-parallel section of the headline line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -449,15 +606,19 @@ def main():
     dom = max(kernels, key=lambda k: kernels[k]["ms"])
     peaks = load_peaks()
     achieved = kernels[dom]["bytes"] / (kernels[dom]["ms"] * 1e-3) / 1e9
+    traffic, traffic_note = ncu_traffic(args.workload, dom)
     roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get((args.workload, dom)),
-                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload (profiles/)",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "traffic_source": traffic_note,
                 "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
                 "kernels_ms": {k: v["ms"] for k, v in kernels.items()}}
 
+    # ---- the collective-bearing path: one 262,144-token sequence, context parallel over the ranks ----
+    del tiles, o_buf, ht_buf
+    cp = None if args.no_cp else cp_section(rank, world, dev, flush, steps=max(5, min(args.steps, 10)))
+
     if rank != 0:
-        if world > 1:
+        if dist.is_initialized():
             dist.destroy_process_group()
         return
     base = None
@@ -468,10 +629,7 @@ def main():
         "metric": "chunk_kda forward tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "H": H, "K": 128, "V": 128,
-                   "flags": "l2norm+gate in kernel, safe_gate, lower_bound=-5, final state",
-                   "l2": "256 MB flush buffer written before every timed step",
-                   "sharding": "batch x head shards, one per rank, no collective"},
+        "config": headline_config(args.workload),
         "tflops": tokens * H * FLOP_PER_TOKEN_HEAD / (ms * 1e-3) / 1e12,
         "tflops_frac_of_bf16_peak": tokens / world * H * FLOP_PER_TOKEN_HEAD / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
         "hbm_frac_compulsory": tokens / world * H * BYTES_PER_TOKEN_HEAD / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
@@ -480,10 +638,11 @@ def main():
         "gpu_launches": 2 * args.steps,
         "roofline": roofline,
         "cpu_baseline": base,
+        "cp": cp,
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 

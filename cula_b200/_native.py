@@ -34,6 +34,7 @@ SIGNATURES = {
     "cula_kda_noalloc_max_tiles": (_i, []),
     "cula_kda_fwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _fp, _fp, _fp, _vp, _fp, _ip, _ip, _ip,
                                   _i, _i, _i, _i, _f, _i, _i, _f, _ip, _vp]),
+    "cula_kda_selftest_bounded_wait": (_i, [_ip, _i, _vp]),
     "cula_kda_strerror": (ctypes.c_char_p, [_i]),
 }
 

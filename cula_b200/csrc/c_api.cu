@@ -229,6 +229,13 @@ extern "C" int cula_kda_bwd_gated(const void* d_q, const void* d_k, const void* 
     return kda_launch_bwd_gated(&p, num_chunks, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int kda_launch_selftest_wait(int* status, int limit, cudaStream_t stream);
+
+extern "C" int cula_kda_selftest_bounded_wait(int* d_status, int max_polls, void* stream) {
+    if (!d_status || max_polls <= 0 || max_polls > (1 << 22)) return CULA_KDA_EINVAL;
+    return kda_launch_selftest_wait(d_status, max_polls, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" const char* cula_kda_strerror(int code) {
     if (code == 0) return "ok";
     if (code == CULA_KDA_EINVAL) return "invalid argument (null pointer, non-positive size or bad enum)";

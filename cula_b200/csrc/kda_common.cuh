@@ -48,6 +48,7 @@ __host__ __device__ __forceinline__ int swz128(int row, int col) {
 constexpr int STATUS_OK = 0;
 constexpr int STATUS_WAIT_TIMEOUT = 1;
 constexpr int STATUS_BAD_INDEX = 2;        // a state-pool index past the end of the pool (decode)
+constexpr int STATUS_RANGE = 3;            // a forward intermediate left the fp16 range (or is not finite)
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -75,6 +76,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+// true if either fp16 half of x is +-inf or NaN (exponent bits all ones)
+__device__ __forceinline__ bool f16x2_not_finite(uint32_t x) {
+    return __vcmpeq2(x & 0x7c007c00u, 0x7c007c00u) != 0u;
 }
 __device__ __forceinline__ float2 unpack_f16(uint32_t x) {
     return __half22float2(*reinterpret_cast<__half2*>(&x));
@@ -133,9 +138,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~a second and reports false (the caller records a status and unwinds).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (int i = 0; i < (1 << 22); ++i) {
+// Bounded wait: gives up after ~a second (by default) and reports false (the caller records a status and unwinds).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = (1 << 22)) {
+    for (int i = 0; i < limit; ++i) {
         if (mbar_test(bar, parity)) return true;
         if (i > 64) __nanosleep(64);
     }

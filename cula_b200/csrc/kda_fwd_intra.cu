@@ -343,7 +343,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float eA = fast_exp2(gi[e] - ri[e]);      // <= 1
-                    const float eB = fast_exp2(ri[e] - gi[e]);      // >= 1, <= 2^108 under the safe gate
+                    const float eB = fast_exp2(fminf(ri[e] - gi[e], 120.f));   // >= 1, <= 2^116 under the safe gate; the clamp
+                                                                               // keeps an unbounded gate from making inf * 0
                     const float eG = fast_exp2(gi[e]);              // 2^(g_i)
                     qa[e] = qv[e] * eA;
                     ka[e] = kv[e] * eA;
@@ -603,6 +604,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         constexpr int CPW = 512 / NWARPS;                      // channels per warp: 64 (8 warps) or 32 (16 warps)
         const int ch0 = (warp >> 2) * CPW;                     // first channel (0..127) of this warp
         const uint32_t taddr = tmem + ((uint32_t)(32 * qd) << 16) + 128 * is_u + ch0;
+        bool out_of_range = false;
 #pragma unroll 1
         for (int cg = 0; cg < CPW / 16; ++cg) {
             uint32_t r[16];
@@ -615,11 +617,15 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                                             pack_f16(__uint_as_float(r[8 * hc + 2]), __uint_as_float(r[8 * hc + 3])),
                                             pack_f16(__uint_as_float(r[8 * hc + 4]), __uint_as_float(r[8 * hc + 5])),
                                             pack_f16(__uint_as_float(r[8 * hc + 6]), __uint_as_float(r[8 * hc + 7])));
+                out_of_range |= f16x2_not_finite(pk.x) | f16x2_not_finite(pk.y) | f16x2_not_finite(pk.z) | f16x2_not_finite(pk.w);
                 const int cc = chn + 8 * hc;
                 if (is_u) *reinterpret_cast<uint4*>(tile + (cc < 64 ? TP_U0 : TP_U1) + swz128(tok, cc & 63)) = pk;
                 else *reinterpret_cast<uint4*>(tile + TP_W + swz256(tok, cc)) = pk;
             }
         }
+        // w and u inherit the range of v and of (I + L)^-1: fp16 has no room beyond 65504, so say so instead of
+        // handing inf to the scan
+        if (__any_sync(0xffffffffu, out_of_range) && lane == 0) atomicMax(p.status, STATUS_RANGE);
     }
     umma::fence_before_sync();
     __syncthreads();      // TMEM columns and shared memory are free for the next tile

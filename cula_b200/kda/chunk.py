@@ -15,18 +15,32 @@ from ..utils import CHUNK, assert_blackwell, get_varlen_tables
 GATE_NONE, GATE_SOFTPLUS, GATE_LOWER_BOUND = 0, 1, 2
 
 _status_words: dict = {}
+_status_mirrors: dict = {}      # device -> pinned host copy of the status word, refreshed after every chunk_kda forward
+FORWARD_CALLS = 0               # how many times chunk_kda_fwd has run in this process (tests count recomputations)
+
+STATUS_MESSAGES = {
+    1: "a bounded in-kernel wait timed out",
+    2: "a state-pool index lies past the end of the pool",
+    3: "a forward intermediate (w, u, kg, qg or Aqk) left the fp16 range or is not finite; "
+       "check the magnitude of v (|v| < 65504 is required) and of the gate",
+}
 
 
 def _status_word(device):
     key = str(device)
     if key not in _status_words:
-        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):      # an inference tensor could not be cleared outside inference mode later
+            _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status_words[key]
+
+
+def _raise_status(code):
+    raise RuntimeError(f"cula_b200 kernel status {code}: {STATUS_MESSAGES.get(code, 'unknown')}")
 
 
 def check_status(device=None):
     """Synchronise and raise if any kernel on ``device`` reported a problem (a bounded wait that gave up, a bad
-    state-pool index)."""
+    state-pool index, an intermediate outside the fp16 range)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     word = _status_words.get(str(device))
     if word is None:
@@ -34,8 +48,28 @@ def check_status(device=None):
     code = int(word.item())
     if code != 0:
         word.zero_()
-        what = {1: "a bounded in-kernel wait timed out", 2: "a state-pool index lies past the end of the pool"}
-        raise RuntimeError(f"cula_b200 kernel status {code}: {what.get(code, 'unknown')}")
+        mirror = _status_mirrors.get(str(device))
+        if mirror is not None:
+            mirror.zero_()
+        _raise_status(code)
+
+
+def _poll_status(device):
+    """Cheap, non-blocking check made at the start of every ``chunk_kda`` call: the status word of the previous
+    calls is mirrored into pinned host memory by an asynchronous copy queued behind their kernels, so a problem a
+    kernel reported surfaces (as RuntimeError) at the latest on the call after the one that has completed."""
+    mirror = _status_mirrors.get(str(device))
+    if mirror is not None and int(mirror[0]) != 0:
+        check_status(device)
+
+
+def _mirror_status(device):
+    key = str(device)
+    mirror = _status_mirrors.get(key)
+    if mirror is None:
+        with torch.inference_mode(False):
+            mirror = _status_mirrors[key] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    mirror.copy_(_status_word(device), non_blocking=True)
 
 
 def _ptr(t):
@@ -45,7 +79,9 @@ def _ptr(t):
 def _gate_mode(use_gate_in_kernel, safe_gate, lower_bound):
     if not use_gate_in_kernel:
         return GATE_NONE
-    return GATE_LOWER_BOUND if (safe_gate and lower_bound is not None) else GATE_SOFTPLUS
+    # the lower-bound (sigmoid) form whenever a lower bound is given, as kda_gate_chunk_cumsum does
+    # (fla/ops/kda/gate.py:509-548 keys on ``lower_bound is not None`` alone)
+    return GATE_LOWER_BOUND if lower_bound is not None else GATE_SOFTPLUS
 
 
 def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
@@ -54,6 +90,8 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     """Forward orchestration (the role of cula/kda/chunk_fwd.py:39-152): the chunk-parallel stage
     writes one tile pack per (chunk, head); the scan consumes them, carries the fp32 state and
     writes ``o``. Returns a dict with o, final_state and the intermediates kept for backward."""
+    global FORWARD_CALLS
+    FORWARD_CALLS += 1
     lib = _native.lib()
     B, T, H, K = q.shape
     dev = q.device
@@ -81,6 +119,13 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
         cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
         float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), _ptr(mkk), _status_word(dev).data_ptr(), stream),
         "cula_kda_fwd_intra")
+    if (cu_seqlens is None and B == 1 and want_output and not (store_states or store_for_backward)):
+        from .cp import auto_segments, segmented_forward
+        P = auto_segments(num_chunks, H, dev)
+        if P > 1:      # one long sequence: few scan CTAs, many dependent steps -> scan it in P side-by-side segments
+            o, final_state = segmented_forward(q, k, v, g, beta, tiles, initial_state, output_final_state, P)
+            return dict(o=o, final_state=final_state, tiles=tiles, akk=akk, mkk=mkk, h=None, h32=None, vnew=None,
+                        num_chunks=num_chunks)
     final_state = torch.empty(n_seqs, H, K, v.shape[-1], dtype=torch.float32, device=dev) if output_final_state else None
     h = vnew = h32 = None
     if store_states:
@@ -154,12 +199,15 @@ def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, c
 
 
 class ChunkKDAFunction(torch.autograd.Function):
-    """Autograd boundary (cula/kda/chunk.py:28-214)."""
+    """Autograd boundary (cula/kda/chunk.py:28-214). Inputs are made contiguous and the device of ``q`` is made
+    current (the reference's ``input_guard``); forward and backward carry the reference's autocast decorators
+    (cula/kda/chunk.py:29-31,128-130), so backward runs under the autocast state forward ran under."""
 
     @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
                 use_qk_l2norm_in_kernel, use_gate_in_kernel, cu_seqlens, cu_seqlens_cpu, safe_gate, lower_bound,
-                disable_recompute, return_intermediate_states):
+                disable_recompute, return_intermediate_states, keep_intermediates):
         q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
         if A_log is not None:
             A_log = A_log.float().contiguous()
@@ -168,10 +216,12 @@ class ChunkKDAFunction(torch.autograd.Function):
         if initial_state is not None:
             initial_state = initial_state.contiguous()
         with torch.cuda.device(q.device):
+            # keep_intermediates is decided by the caller of .apply: grad mode is always off in here
             out = chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                                 cu_seqlens_cpu, use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound,
                                 A_log, dt_bias, store_states=return_intermediate_states,
-                                store_for_backward=bool(disable_recompute) and torch.is_grad_enabled())
+                                store_for_backward=bool(keep_intermediates))
+            _mirror_status(q.device)
         if return_intermediate_states:
             assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
             assert disable_recompute is False, "return_intermediate_states must be used with disable_recompute=False"
@@ -193,6 +243,7 @@ class ChunkKDAFunction(torch.autograd.Function):
         return out["o"], out["final_state"]
 
     @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, do, dht):
         q, k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens = ctx.saved_tensors
         l2, gate_in, safe_gate, lower_bound = ctx.flags
@@ -204,8 +255,8 @@ class ChunkKDAFunction(torch.autograd.Function):
             dA = dA.to(A_log.dtype).view_as(A_log)
         if dbias is not None and dt_bias is not None:
             dbias = dbias.to(dt_bias.dtype).view_as(dt_bias)
-        # gradients for: q, k, v, g, beta, A_log, dt_bias, scale, initial_state, then 9 non-tensor arguments
-        return (dq, dk, dv, dg, dbeta, dA, dbias, None, dh0) + (None,) * 9
+        # gradients for: q, k, v, g, beta, A_log, dt_bias, scale, initial_state, then 10 non-tensor arguments
+        return (dq, dk, dv, dg, dbeta, dA, dbias, None, dh0) + (None,) * 10
 
 
 @torch.compiler.disable
@@ -230,12 +281,26 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         cu_seqlens: int32 ``[N+1]`` for a packed batch (then B must be 1); cu_seqlens_cpu: optional host copy.
         disable_recompute: keep forward intermediates for backward instead of recomputing them.
         return_intermediate_states: inference only; also return h ``[B, NT, H, 128, 128]`` bf16.
+        cp_context: a :class:`cula_b200.kda.cp.KDACPContext` (process group of the context-parallel ranks); the call
+            is then this rank's shard of ONE sequence and runs through ``chunk_kda_cp`` (the reference takes
+            flash-linear-attention's ``FLACPContext`` here, cula/kda/chunk.py:348-355).
+
+    Numeric range: the chunk-local intermediates w, u, kg, qg, Aqk travel as fp16 (the reference uses bf16), so
+    ``|v|`` and ``|beta v|`` must stay below 65504; q and k are unrestricted when ``use_qk_l2norm_in_kernel`` is
+    set and are expected to be unit rows otherwise. A value that leaves the range is reported through the device
+    status word (``check_status``; also raised by the next ``chunk_kda`` call on the device).
 
     Returns ``(o, final_state)`` (``final_state`` is None unless requested).
     Raises ValueError / AssertionError on the same conditions as the reference (cula/kda/chunk.py:348-388).
     """
     if cp_context is not None:
-        raise NotImplementedError("context parallelism is driven through cula_b200.kda.cp, not cp_context")
+        from .cp import chunk_kda_cp
+        assert cu_seqlens is None, "context parallelism takes this rank's shard of one sequence, not a packed batch"
+        assert not return_intermediate_states, "return_intermediate_states is not supported for context parallelism"
+        return chunk_kda_cp(q, k, v, g, beta, scale=scale, initial_state=initial_state,
+                            output_final_state=output_final_state, use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel,
+                            use_gate_in_kernel=use_gate_in_kernel, safe_gate=safe_gate, lower_bound=lower_bound,
+                            group=cp_context.group, segments=getattr(cp_context, "segments", None), **kwargs)
     if cu_seqlens is not None:
         if q.shape[0] != 1:
             raise ValueError(
@@ -270,9 +335,14 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     if initial_state is not None and cu_seqlens is None:
         assert initial_state.shape[0] == q.shape[0], "one initial state per batch entry is expected."
     assert_blackwell(q.device)
+    _poll_status(q.device)
 
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    # the intermediates are worth keeping only if a backward pass can follow; grad mode has to be read here,
+    # inside autograd.Function.forward it is always off
+    keep = bool(disable_recompute) and torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (q, k, v, g, beta, A_log, dt_bias, initial_state))
     return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
                                   use_qk_l2norm_in_kernel, use_gate_in_kernel, cu_seqlens, cu_seqlens_cpu, safe_gate,
-                                  lower_bound, disable_recompute, return_intermediate_states)
+                                  lower_bound, disable_recompute, return_intermediate_states, keep)

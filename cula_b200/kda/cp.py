@@ -34,12 +34,25 @@ from .chunk import _gate_mode, _ptr, _status_word
 _SEGMENT_TABLES: dict = {}      # (segment bounds, device) -> VarlenTables of the segments of a shard
 
 
+class KDACPContext:
+    """What ``chunk_kda(..., cp_context=...)`` needs to run this rank's shard of one long sequence: the process
+    group of the context-parallel ranks (None = the default group) and, optionally, the number of segments a shard
+    is cut into. Stands where the reference takes flash-linear-attention's ``FLACPContext``
+    (cula/kda/chunk.py:348-355)."""
+
+    def __init__(self, group=None, segments=None):
+        self.group = group
+        self.segments = segments
+
+
 class CudaBackend:
     """Compute steps of one rank on its GPU through the C ABI."""
 
     def __init__(self, q, k, v, g, beta, scale, use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound,
-                 A_log, dt_bias, segments=None):
+                 A_log, dt_bias, segments=None, marks=None, tiles=None):
         assert q.shape[0] == 1, "context parallelism expects one sequence (batch size 1)"
+        self.marks = marks          # optional list: receives (stage name, CUDA event recorded after the stage)
+        self.mark("start")
         self.lib = _native.lib()
         self.q, self.k, self.v, self.g, self.beta = (x.contiguous() for x in (q, k, v, g, beta))
         self.T, self.H = q.shape[1], q.shape[2]
@@ -60,6 +73,9 @@ class CudaBackend:
                     _SEGMENT_TABLES.clear()
                 cpu = torch.tensor(self.bounds, dtype=torch.int32)
                 self.tables = _SEGMENT_TABLES[key] = VarlenTables(cpu.to(self.dev), cpu)
+        if tiles is not None:           # the chunk-parallel stage has already run (single-GPU segmented forward)
+            self.tiles = tiles
+            return
         self.tiles = torch.empty(self.num_chunks * self.H * self.lib.cula_kda_tile_pack_bytes(), dtype=torch.uint8,
                                  device=self.dev)
         A_log = None if A_log is None else A_log.float().contiguous()
@@ -70,6 +86,13 @@ class CudaBackend:
             self.num_chunks, self.T, self.H, float(scale), int(use_qk_l2norm_in_kernel),
             _gate_mode(use_gate_in_kernel, safe_gate, lower_bound), float(lower_bound if lower_bound is not None else 0.0),
             self.tiles.data_ptr(), None, None, self.status, self.stream), "cula_kda_fwd_intra")
+        self.mark("intra")
+
+    def mark(self, name):
+        if self.marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
 
     def _table_ptrs(self):
         if self.tables is None:
@@ -81,16 +104,21 @@ class CudaBackend:
                                                 self.stream), "cula_kda_cp_fold")
         return out
 
-    def transition(self):
+    def transition(self, local_only=False):
         """X [2, H, 128, 128] = (C | M): the affine action of this whole shard on the state. The transitions of the
-        P segments are kept for `incoming`; they are composed here so that only one pair travels."""
+        P segments are kept for `incoming`; they are composed here so that only one pair travels. ``local_only``
+        (a single rank): nobody consumes the shard's own transition, so only the first P - 1 segments are scanned
+        and nothing is composed."""
         P = self.n_segments
         self.C_seg = torch.empty(P, self.H, 128, 128, dtype=torch.float32, device=self.dev)
         self.M_seg = torch.empty(P, self.H, 128, 128, dtype=torch.float32, device=self.dev)
         cu_p, co_p, _ = self._table_ptrs()
         _native.check(self.lib.cula_kda_cp_transition(self.tiles.data_ptr(), self.C_seg.data_ptr(), self.M_seg.data_ptr(),
-                                                      cu_p, co_p, P, self.T, self.H, self.status, self.stream),
-                      "cula_kda_cp_transition")
+                                                      cu_p, co_p, P - 1 if local_only else P, self.T, self.H,
+                                                      self.status, self.stream), "cula_kda_cp_transition")
+        self.mark("transition")
+        if local_only:
+            return None
         if P == 1:
             return torch.stack([self.C_seg[0], self.M_seg[0]])
         X = torch.empty(2, self.H, 128, 128, dtype=torch.float32, device=self.dev)
@@ -98,10 +126,22 @@ class CudaBackend:
         self._fold(None, self.M_seg[1:].data_ptr(), self.M_seg[0], P - 1, X[1])            # M = M_{P-1} ... M_0
         return X
 
+    def absorb_initial_state(self, X, initial_state):
+        """Rank 0 of a multi-rank group: fold the state before the first token into the shard's C,
+        ``C <- M h0 + C``, so that the gathered pairs carry it to every later rank."""
+        h0 = initial_state.reshape(self.H, 128, 128).float().contiguous()
+        out = torch.empty_like(X)
+        out[1].copy_(X[1])
+        self._fold(X[0].data_ptr(), X[1].data_ptr(), h0, 1, out[0])
+        return out
+
     def incoming(self, X_all, rank, initial_state):
         """States entering each of the P segments of this shard: the fold of the shards before this one (X_all is
-        [world, 2, H, 128, 128] in this GPU's memory), then one more step per inner segment boundary."""
-        s = None if initial_state is None else initial_state.reshape(self.H, 128, 128).float().contiguous()
+        [world, 2, H, 128, 128] in this GPU's memory; rank 0's pair already contains the initial state), then one
+        more step per inner segment boundary. ``initial_state`` is read on rank 0 only."""
+        s = None
+        if rank == 0 and initial_state is not None:
+            s = initial_state.reshape(self.H, 128, 128).float().contiguous()
         if rank > 0:
             per = self.H * 128 * 128
             s = self._fold(X_all.data_ptr(), X_all.data_ptr() + 4 * per, s, rank,
@@ -129,6 +169,34 @@ class CudaBackend:
         return o, (ht[P - 1:] if want_final else None)
 
 
+_SM_COUNT: dict = {}
+MAX_AUTO_SEGMENTS = 4       # upper bound of `auto_segments`; 1 switches the single-GPU segmentation off
+
+
+def auto_segments(num_chunks, heads, device):
+    """How many side-by-side segments the scan of ONE long sequence should be cut into on a single GPU: the scan is
+    a chain of ``num_chunks`` dependent steps that occupies only ``2 * heads`` CTAs, so while SMs are idle a second
+    pass pays for itself -- a transition scan per segment (cheaper: no output products), a fold, and then all
+    segments scanned side by side from their now-known incoming states. Per chunk the two passes cost about
+    (0.9 + 1.7) / P microseconds against 1.7 for the plain scan; below a few hundred chunks the extra launches eat
+    the gain. The role of the intra-card mode of flash-linear-attention's merge kernel
+    (fla/ops/cp/chunk_delta_h.py:321-357)."""
+    key = str(device)
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    fit = _SM_COUNT[key] // (2 * heads)          # segments whose four-warp scan CTAs all find an SM
+    if num_chunks < 512 or fit < 2:
+        return 1
+    return max(1, min(MAX_AUTO_SEGMENTS, fit))
+
+
+def segmented_forward(q, k, v, g, beta, tiles, initial_state, output_final_state, segments):
+    """Scan + output of one sequence on one GPU in ``segments`` side-by-side pieces (see `auto_segments`); ``tiles``
+    are the tile packs the chunk-parallel stage has already written. Returns (o, final_state or None)."""
+    backend = CudaBackend(q, k, v, g, beta, None, None, None, None, None, None, None, segments=segments, tiles=tiles)
+    return cp_forward(backend, None, 0, 1, initial_state, output_final_state)
+
+
 def gather_with_group(group=None):
     """all-gather into this rank's own memory: [*shape] -> [world, *shape]."""
     def gather(x):
@@ -151,12 +219,24 @@ def cp_forward(backend, gather, rank, world, initial_state=None, output_final_st
         if aux is not None:
             aux.update(s_in=initial_state, X_all=None)
         return backend.forward([initial_state], output_final_state)
-    X = backend.transition()                                  # [2, H, 128, 128]: (C | M) of this shard
-    X_all = gather(X) if world > 1 else X[None]               # [world, 2, H, 128, 128]
+    mark = getattr(backend, "mark", lambda name: None)
+    if world == 1:
+        backend.transition(local_only=True)                   # segments of one shard on one GPU: nothing travels
+        X_all = None
+    else:
+        X = backend.transition()                              # [2, H, 128, 128]: (C | M) of this shard
+        if rank == 0 and initial_state is not None:
+            X = backend.absorb_initial_state(X, initial_state)    # later ranks never see initial_state itself
+        mark("fold_local")
+        X_all = gather(X)                                     # [world, 2, H, 128, 128]
+    mark("gather")
     states = backend.incoming(X_all, rank, initial_state)
+    mark("fold_incoming")
     if aux is not None:
         aux.update(s_in=states[0], X_all=X_all)
-    return backend.forward(states, output_final_state and last)
+    out = backend.forward(states, output_final_state and last)
+    mark("scan")
+    return out
 
 
 class CPBackwardState:
@@ -230,14 +310,15 @@ class ChunkKDACPFunction(torch.autograd.Function):
     """Autograd boundary of the context-parallel path: one shard per rank, exchanges inside forward and backward."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, initial_state, scale, output_final_state, flags, group, segments):
+    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, initial_state, scale, output_final_state, flags, group, segments,
+                marks=None):
         q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         l2, gate_in, safe_gate, lower_bound = flags
         aux = {}
         with torch.cuda.device(q.device):
             backend = CudaBackend(q, k, v, g, beta, scale, l2, gate_in, safe_gate, lower_bound, A_log, dt_bias,
-                                  segments=1 if world == 1 else segments)
+                                  segments=segments, marks=marks)
             o, ht = cp_forward(backend, gather_with_group(group), rank, world, initial_state, output_final_state, aux)
         ctx.cp = CPBackwardState(q, k, v, g, beta, None if A_log is None else A_log.float().contiguous(),
                                  None if dt_bias is None else dt_bias.float().contiguous(), aux["s_in"], aux["X_all"],
@@ -263,19 +344,20 @@ class ChunkKDACPFunction(torch.autograd.Function):
         if dbias is not None and ctx.param_dtypes[1] is not None:
             dbias = dbias.to(ctx.param_dtypes[1][0]).view(ctx.param_dtypes[1][1])
         dh0 = dh0 if (ctx.has_h0 and cp.rank == 0) else None
-        return dq, dk, dv, dg, dbeta, dA, dbias, dh0, None, None, None, None, None
+        return dq, dk, dv, dg, dbeta, dA, dbias, dh0, None, None, None, None, None, None
 
 
 @torch.compiler.disable
 def chunk_kda_cp(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
                  use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, safe_gate=False, lower_bound=None,
-                 group=None, segments=None, **kwargs):
+                 group=None, segments=None, stage_marks=None, **kwargs):
     """Context-parallel ``chunk_kda`` forward. Arguments as ``chunk_kda`` for this rank's shard of ONE sequence;
     ``initial_state`` ([1, H, 128, 128] fp32) is the state before the first token of the whole sequence and is
     read on rank 0 of ``group``; ``final_state`` is returned on the last rank (None elsewhere). Differentiable: the
     gradients of ``A_log`` / ``dt_bias`` are this shard's contributions (sum them over the group as for data-parallel
     replicas), the gradient of ``initial_state`` appears on rank 0. ``segments`` (default 2) must be the
-    same on every rank; a shard shorter than that many chunks simply gets empty segments."""
+    same on every rank; a shard shorter than that many chunks simply gets empty segments. ``stage_marks`` (a
+    list) receives ``(stage, torch.cuda.Event)`` pairs recorded after each stage of the forward, for profiling."""
     assert q.shape[0] == 1, "context parallelism expects one sequence (batch size 1)"
     assert q.dtype == k.dtype == v.dtype == torch.bfloat16, "q, k, v must be in bfloat16."
     assert q.shape[-1] == k.shape[-1] == v.shape[-1] == 128, "Currently we only support head dim of 128 for KDA"
@@ -296,5 +378,5 @@ def chunk_kda_cp(q, k, v, g, beta, scale=None, initial_state=None, output_final_
         scale = k.shape[-1] ** -0.5
     flags = (use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound)
     o, ht = ChunkKDACPFunction.apply(q, k, v, g, beta, A_log, dt_bias, initial_state, scale, output_final_state, flags,
-                                     group, segments)
+                                     group, segments, stage_marks)
     return o, (ht if ht.numel() > 0 else None)

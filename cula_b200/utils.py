@@ -61,16 +61,22 @@ class VarlenTables:
         self.seqlens_cpu = cpu
 
 
-_TABLE_CACHE: dict = {}
+_TABLE_CACHE: list = []      # (source tensor, its version, cu_seqlens_cpu or None, tables), most recent last
 
 
 def get_varlen_tables(cu_seqlens, cu_seqlens_cpu=None) -> VarlenTables:
-    """Tables cached by tensor identity (data pointer, version, length), as the reference caches its
-    chunk indices by tensor identity; avoids a device->host sync on every call."""
-    key = (cu_seqlens.data_ptr(), cu_seqlens._version, cu_seqlens.numel(), str(cu_seqlens.device))
-    tab = _TABLE_CACHE.get(key)
-    if tab is None:
-        if len(_TABLE_CACHE) > 64:
-            _TABLE_CACHE.clear()
-        tab = _TABLE_CACHE[key] = VarlenTables(cu_seqlens, cu_seqlens_cpu)
+    """Tables cached by tensor IDENTITY, as the reference caches its chunk indices (fla's ``tensor_cache``): an entry
+    holds a reference to the caller's ``cu_seqlens`` tensor itself, so its address cannot be handed to another tensor
+    while the entry lives, and is matched with ``is`` plus the tensor's version counter (an in-place edit
+    invalidates it). Avoids a device->host sync on every call."""
+    version = cu_seqlens._version
+    for i in range(len(_TABLE_CACHE) - 1, -1, -1):
+        src, ver, cpu, tab = _TABLE_CACHE[i]
+        if src is cu_seqlens and ver == version and (cu_seqlens_cpu is None or cpu is None or cpu is cu_seqlens_cpu
+                                                     or torch.equal(cpu, cu_seqlens_cpu)):
+            return tab
+    tab = VarlenTables(cu_seqlens, cu_seqlens_cpu)
+    _TABLE_CACHE.append((cu_seqlens, version, cu_seqlens_cpu, tab))
+    if len(_TABLE_CACHE) > 16:
+        del _TABLE_CACHE[0]
     return tab

@@ -199,6 +199,18 @@ int cula_kda_fwd_noalloc(const void* d_q, const void* d_k, const void* d_v, cons
                          float scale, int use_qk_l2norm, int gate_mode, float lower_bound,
                          int* d_status, void* stream);
 
+/*
+ * Self-test of the bounded waits: launches one warp that waits on a barrier nothing completes; after max_polls
+ * polls (1 .. 2^22) the wait gives up, *d_status is set to 1 (the time-out status every kernel above reports through
+ * its d_status argument) and the kernel returns. Lets a deployment check that a stuck pipeline ends in a status
+ * word instead of a hung GPU. No counterpart in the reference: its device waits are unbounded
+ * (cula/ops/chunk_delta_h.py:1303-1424 pipeline waits) and its CUDA errors end the process
+ * (csrc/kerutils/include/kerutils/common/common.h:24-31).
+ * Status word values: 0 ok, 1 a bounded wait timed out, 2 state-pool index out of range (decode),
+ * 3 a forward intermediate (w, u) left the fp16 range or is not finite.
+ */
+int cula_kda_selftest_bounded_wait(int* d_status, int max_polls, void* stream);
+
 /* Human-readable text for a return value of the functions above. */
 const char* cula_kda_strerror(int code);
 

@@ -39,11 +39,20 @@ def load():
         _lib.naive_kda_fwd.argtypes = [fp] * 8 + [fp, fp, ip] + [ctypes.c_int] * 4 + [ctypes.c_float] + \
                                       [ctypes.c_int, ctypes.c_int, ctypes.c_float]
         _lib.naive_kda_num_threads.restype = ctypes.c_int
+        _lib.naive_kda_set_num_threads.argtypes = [ctypes.c_int]
+        _lib.naive_kda_set_num_threads.restype = None
     return _lib
 
 
 def num_threads():
     return int(load().naive_kda_num_threads())
+
+
+def use_all_cores():
+    """Run on every core this process may use, whatever OMP_NUM_THREADS says (torch.distributed.run exports
+    OMP_NUM_THREADS=1 to its workers). Returns the thread count now in effect."""
+    load().naive_kda_set_num_threads(len(os.sched_getaffinity(0)))
+    return num_threads()
 
 
 def _f32(x):

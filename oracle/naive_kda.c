@@ -41,6 +41,15 @@ int naive_kda_num_threads(void) {
 #endif
 }
 
+/* Set the number of OpenMP threads of later calls (a launcher may have exported OMP_NUM_THREADS=1). */
+void naive_kda_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /*
  * q,k,g: [total_T, H, K]   v,o: [total_T, H, V]   beta: [total_T, H]   (all fp32, token-major)
  * cu_seqlens: [N+1] token offsets of the N sequences (a fixed-length batch passes 0,T,2T,...)

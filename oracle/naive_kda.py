@@ -63,7 +63,7 @@ def naive_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output
     if scale is None:
         scale = K ** -0.5
     q, k, v, g, beta = (x.to(dtype) for x in (q, k, v, g, beta))
-    S = torch.zeros(B, H, K, V, dtype=dtype)
+    S = torch.zeros(B, H, K, V, dtype=dtype, device=q.device)     # runs wherever the inputs live (CPU by default)
     if initial_state is not None:
         S = S + initial_state.to(dtype)
     outs = []

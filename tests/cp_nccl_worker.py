@@ -25,9 +25,11 @@ def main():
     per = T // world
     sl = slice(rank * per, T if rank == world - 1 else (rank + 1) * per)
     sh = {n: (t[:, sl] if n in ("q", "k", "v", "g", "beta") else t).to(dev).requires_grad_(True) for n, t in inp.items()}
-    o, ht = chunk_kda_cp(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], initial_state=sh["initial_state"],
-                         output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True,
-                         lower_bound=-5.0, A_log=sh["A_log"], dt_bias=sh["dt_bias"])
+    # the state before the first token is given on rank 0 only; the exchange carries it to the other ranks
+    o, ht = chunk_kda_cp(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"],
+                         initial_state=sh["initial_state"] if rank == 0 else None, output_final_state=True,
+                         use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+                         A_log=sh["A_log"], dt_bias=sh["dt_bias"])
     assert (ht is not None) == (rank == world - 1)
     loss = (o.float() * do[:, sl].to(dev).float()).sum()
     if ht is not None:

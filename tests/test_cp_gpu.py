@@ -39,12 +39,15 @@ def test_cp_emulated_ranks_match_oracle(world, T, gate_offset, segments):
                                     inp["g"][:, sl].cuda(), inp["beta"][:, sl].cuda(), 128 ** -0.5, True, True, True, -5.0,
                                     inp["A_log"].cuda(), inp["dt_bias"].cuda(), segments=segments))
     trans = [b.transition() for b in backends]               # (C | M) per shard; some segments are empty here
-    X_all = torch.stack(trans)                               # the emulated collective: every rank sees the same tensor
+    h0 = inp["initial_state"].cuda()
+    # the emulated collective: every rank sees the same tensor; rank 0's pair carries the initial state
+    X_all = torch.stack([backends[0].absorb_initial_state(trans[0], h0)] + trans[1:])
 
     outs, final = [], None
     for r, b in enumerate(backends):
         b.transition = lambda t=trans[r]: t           # already computed above
-        o, ht = cp_forward(b, lambda x: X_all, r, world, inp["initial_state"].cuda(), True)
+        # the state before the first token is handed to rank 0 ONLY
+        o, ht = cp_forward(b, lambda x: X_all, r, world, h0 if r == 0 else None, True)
         outs.append(o)
         final = ht if ht is not None else final
     torch.cuda.synchronize()
@@ -70,7 +73,8 @@ def test_cp_transition_is_the_affine_map_of_the_shard():
                       use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
     pred = torch.matmul(M.double(), d["initial_state"][0].double()) + C.double()
     assert err_ratio(ht[0].double().cpu(), pred.cpu()) <= 2e-3
-    folded = b.incoming(torch.stack([C, M])[None].repeat(2, 1, 1, 1, 1), 1, d["initial_state"])[0]
+    X0 = b.absorb_initial_state(torch.stack([C, M]), d["initial_state"])       # what rank 0 would publish
+    folded = b.incoming(X0[None].repeat(2, 1, 1, 1, 1), 1, None)[0]            # what rank 1 folds from it
     assert err_ratio(pred.cpu(), folded.double().cpu()) <= 1e-5
 
 
@@ -119,12 +123,13 @@ def test_cp_backward_emulated_ranks_match_oracle_autograd(world, T, segments):
         backends.append(CudaBackend(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], 128 ** -0.5, *flags, A_log, dt_bias,
                                     segments=segments))
     trans = [b.transition() for b in backends]
-    X_all = torch.stack(trans)
+    h0 = inp["initial_state"].cuda()
+    X_all = torch.stack([backends[0].absorb_initial_state(trans[0], h0)] + trans[1:])
     states = []
     for r, b in enumerate(backends):
         b.transition = lambda t=trans[r]: t
         aux = {}
-        cp_forward(b, lambda x: X_all, r, world, inp["initial_state"].cuda(), True, aux)
+        cp_forward(b, lambda x: X_all, r, world, h0 if r == 0 else None, True, aux)
         sh = shards[r]
         states.append(CPBackwardState(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], A_log, dt_bias, aux["s_in"], aux["X_all"],
                                       128 ** -0.5, flags, r, world))

@@ -29,7 +29,7 @@ class OracleBackend:
         sl = slice(self.bounds[i], self.bounds[i + 1])
         return self.q[:, sl], self.k[:, sl], self.v[:, sl], self.a[:, sl], self.beta[:, sl]
 
-    def transition(self):
+    def transition(self, local_only=False):
         self.C_seg, self.M_seg = [], []
         C_tot, M_tot = torch.zeros(self.H, 128, 128), torch.eye(128).expand(self.H, 128, 128).clone()
         for i in range(self.n_segments):
@@ -43,8 +43,13 @@ class OracleBackend:
             C_tot, M_tot = M[0] @ C_tot + C[0], M[0] @ M_tot
         return torch.stack([C_tot, M_tot])
 
+    def absorb_initial_state(self, X, initial_state):
+        return torch.stack([X[1] @ initial_state.reshape(self.H, 128, 128) + X[0], X[1]])
+
     def incoming(self, X_all, rank, initial_state):
-        S = torch.zeros(self.H, 128, 128) if initial_state is None else initial_state.reshape(self.H, 128, 128).clone()
+        S = torch.zeros(self.H, 128, 128)
+        if rank == 0 and initial_state is not None:
+            S = initial_state.reshape(self.H, 128, 128).clone()
         for j in range(rank):
             S = X_all[j, 1] @ S + X_all[j, 0]
         states = [S]
@@ -79,7 +84,9 @@ def _worker(rank, world, port, T, H, out_dir, segmented):
         shard = {n: (t[:, lo:hi] if n in ("q", "k", "v", "g", "beta") else t) for n, t in inp.items()}
         n_loc = hi - lo
         bounds = [0, 64, n_loc] if segmented else None       # same segment count on every rank
-        o, ht = cp_forward(OracleBackend(shard, bounds), gather_with_group(None), rank, world, inp["initial_state"], True)
+        # the state before the first token is given on rank 0 ONLY: the exchange has to carry it to the others
+        h0 = inp["initial_state"] if rank == 0 else None
+        o, ht = cp_forward(OracleBackend(shard, bounds), gather_with_group(None), rank, world, h0, True)
         assert (ht is not None) == (rank == world - 1)
         torch.save((o, ht), os.path.join(out_dir, f"rank{rank}.pt"))
     finally:

@@ -142,3 +142,54 @@ def test_c_side_chunk_tables_match_the_python_ones():
     bad = torch.tensor([0, 10, 5], dtype=torch.int32)
     assert lib.cula_kda_num_chunks(bad.data_ptr(), 2) < 0
     assert lib.cula_kda_num_chunks(torch.tensor([3, 10], dtype=torch.int32).data_ptr(), 1) < 0
+
+
+def test_varlen_tables_are_cached_by_identity_not_by_address():
+    """Two different int64 cu_seqlens of equal length, one after the other, the first one freed in between: the
+    allocator is free to hand the second one the same address, and the tables must still be rebuilt."""
+    from cula_b200.utils import get_varlen_tables
+    for dtype in (torch.int64, torch.int32):
+        a = torch.tensor([0, 100, 300, 1000], dtype=dtype)
+        tab_a = get_varlen_tables(a)
+        assert get_varlen_tables(a) is tab_a                      # the same tensor: served from the cache
+        assert tab_a.num_chunks == 2 + 4 + 11
+        addr = a.data_ptr()
+        del a
+        for _ in range(50):                                       # provoke reuse of the freed address
+            b = torch.tensor([0, 64, 128, 1000], dtype=dtype)
+            tab_b = get_varlen_tables(b)
+            assert tab_b is not tab_a
+            assert tab_b.num_chunks == 1 + 1 + 14 and tab_b.chunk_offsets.tolist() == [0, 1, 2, 16]
+            if b.data_ptr() == addr:
+                break
+            del b
+    c = torch.tensor([0, 10, 20], dtype=torch.int32)
+    tab_c = get_varlen_tables(c)
+    c[1] = 15                                                     # an in-place edit bumps the version: rebuilt
+    assert get_varlen_tables(c) is not tab_c
+
+
+def test_cp_context_kwarg_dispatches_to_the_context_parallel_path(monkeypatch):
+    """``chunk_kda(..., cp_context=ctx)`` keeps the reference's one-line call (cula/kda/chunk.py:348-355) and hands
+    the shard to ``chunk_kda_cp`` with the group the context carries."""
+    import cula_b200.kda.cp as cp
+    seen = {}
+
+    def fake(q, k, v, g, beta, **kw):
+        seen.update(kw)
+        return "o", None
+    monkeypatch.setattr(cp, "chunk_kda_cp", fake)
+    q, k, v, g, beta = _inputs(T=64)
+    ctx = cp.KDACPContext(group="the-group", segments=3)
+    out = chunk_kda(q, k, v, g, beta, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=torch.zeros(1),
+                    cp_context=ctx)
+    assert out == ("o", None)
+    assert seen["group"] == "the-group" and seen["segments"] == 3 and seen["lower_bound"] == -5.0 and "A_log" in seen
+
+
+def test_gate_mode_follows_lower_bound():
+    from cula_b200.kda.chunk import GATE_LOWER_BOUND, GATE_NONE, GATE_SOFTPLUS, _gate_mode
+    assert _gate_mode(False, True, -5.0) == GATE_NONE
+    assert _gate_mode(True, True, -5.0) == GATE_LOWER_BOUND
+    assert _gate_mode(True, False, -5.0) == GATE_LOWER_BOUND      # keyed on lower_bound alone, as fla's gate is
+    assert _gate_mode(True, False, None) == GATE_SOFTPLUS

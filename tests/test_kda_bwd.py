@@ -180,3 +180,71 @@ def test_backward_with_more_scan_ctas_than_sms():
     dht = 0.1 * torch.randn(5, 16, 128, 128, generator=gen)
     ref, got = run_both(inp, do, dht)
     assert_grads(ref, got, HEADLINE_TOL, "wide grid")
+
+
+def test_disable_recompute_keeps_the_forward_intermediates():
+    """With ``disable_recompute=True`` the autograd node holds the forward intermediates and backward launches no
+    forward kernel; without it backward re-runs the two forward launches. Both give the same gradients."""
+    import cula_b200.kda.chunk as chunk_mod
+    from cula_b200.kda import chunk_kda
+    inp = make_inputs(2, 200, 2, seed=3, gate_offset=-7.0, h0_std=0.5)
+    gen = torch.Generator().manual_seed(4)
+    do = torch.randn(2, 200, 2, 128, generator=gen).to(torch.bfloat16).cuda()
+    grads = {}
+    for keep in (True, False):
+        dev = {n: t.detach().cuda().requires_grad_(True) for n, t in inp.items()}
+        o, _ = chunk_kda(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], initial_state=dev["initial_state"],
+                         output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True,
+                         lower_bound=-5.0, A_log=dev["A_log"], dt_bias=dev["dt_bias"], disable_recompute=keep)
+        node = o.grad_fn
+        assert (node.kept is not None) == keep
+        if keep:
+            assert all(node.kept[n] is not None for n in ("tiles", "akk", "mkk", "h32", "vnew"))
+        before = chunk_mod.FORWARD_CALLS
+        o.backward(do)
+        torch.cuda.synchronize()
+        assert chunk_mod.FORWARD_CALLS - before == (0 if keep else 1)
+        grads[keep] = {n: t.grad.float().cpu() for n, t in dev.items()}
+    for n in grads[True]:
+        assert torch.equal(grads[True][n], grads[False][n]), n
+    # nothing is kept when no input asks for a gradient or grad mode is off
+    d = {n: t.cuda() for n, t in inp.items()}
+    with torch.no_grad():
+        o, _ = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                         safe_gate=True, lower_bound=-5.0, A_log=d["A_log"], dt_bias=d["dt_bias"], disable_recompute=True)
+    assert o.grad_fn is None
+
+
+@pytest.mark.parametrize("disable_recompute", [False, True])
+def test_backward_long_sequence_all_gradients(disable_recompute):
+    """One 8,192-token sequence (the length of the forward+backward configuration), weak gates so that the state and
+    its gradient travel across all 128 chunks, non-zero initial state and final-state gradient: every gradient,
+    dA_log and ddt_bias included, against autograd of the fp32 token recurrence (run on the CUDA device by torch so
+    that 8,192 dependent steps finish in seconds)."""
+    from cula_b200.kda import check_status, chunk_kda
+    B, T, H = 1, 8192, 2
+    inp = make_inputs(B, T, H, seed=21, gate_offset=-8.0, h0_std=0.1)
+    gen = torch.Generator().manual_seed(22)
+    inp["dt_bias"] = 0.1 * torch.randn(H * 128, generator=gen)
+    do = torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16)
+    dht = 0.1 * torch.randn(B, H, 128, 128, generator=gen)
+    names = list(GRADS)
+    ref_in = {n: inp[n].detach().float().cuda().requires_grad_(True) for n in names}
+    o, ht = chunk_kda_oracle(ref_in["q"], ref_in["k"], ref_in["v"], ref_in["g"], ref_in["beta"],
+                             initial_state=ref_in["initial_state"], output_final_state=True, use_qk_l2norm_in_kernel=True,
+                             use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=ref_in["A_log"],
+                             dt_bias=ref_in["dt_bias"])
+    ((o * do.cuda().float()).sum() + (ht * dht.cuda()).sum()).backward()
+    dev_in = {n: inp[n].detach().cuda().requires_grad_(True) for n in names}
+    o2, ht2 = chunk_kda(dev_in["q"], dev_in["k"], dev_in["v"], dev_in["g"], dev_in["beta"],
+                        initial_state=dev_in["initial_state"], output_final_state=True, use_qk_l2norm_in_kernel=True,
+                        use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=dev_in["A_log"],
+                        dt_bias=dev_in["dt_bias"], disable_recompute=disable_recompute)
+    ((o2.float() * do.cuda().float()).sum() + (ht2 * dht.cuda()).sum()).backward()
+    torch.cuda.synchronize()
+    check_status()
+    assert err_ratio(o.detach().cpu(), o2.detach().float().cpu()) <= 5e-3
+    assert err_ratio(ht.detach().cpu(), ht2.detach().cpu()) <= 2e-3
+    ref = {n: t.grad.cpu() for n, t in ref_in.items()}
+    got = {n: t.grad.float().cpu() for n, t in dev_in.items()}
+    assert_grads(ref, got, {"default": 5e-3, "A_log": 8e-3, "dt_bias": 8e-3}, "T8192")

@@ -227,3 +227,63 @@ def test_intermediate_states_do_not_depend_on_the_scan_variant():
     torch.cuda.synchronize()
     assert torch.equal(o, torch.cat([p[0] for p in parts])) and torch.equal(ht, torch.cat([p[1] for p in parts]))
     assert torch.equal(h, torch.cat([p[2] for p in parts]))
+
+
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+def test_two_different_cu_seqlens_of_equal_length_back_to_back(dtype):
+    """The index tables are cached per cu_seqlens tensor; a second tensor with the same number of sequences but
+    other boundaries (int64 ones are converted, so the caller's tensor may be freed and its address reused) must
+    get its own tables."""
+    H, T = 2, 400
+    inp = make_inputs(1, T, H, seed=13, gate_offset=-7.0)
+    for bounds in ([0, 100, 300, 400], [0, 64, 130, 400], [0, 190, 191, 400]):
+        cu = torch.tensor(bounds, dtype=dtype)
+        o, ht = run_chunk_kda(inp, cu_seqlens=cu)
+        o_ref, ht_ref = oracle_fwd(inp, cu_seqlens=torch.tensor(bounds, dtype=torch.int32))
+        assert_fwd_close(o, ht, o_ref, ht_ref, ht_tol=2e-3, tag=f"{bounds}")
+        del cu
+
+
+def test_values_outside_the_fp16_range_are_reported():
+    """|v| beyond the fp16 range cannot be carried by the tile pack: the kernel reports it through the status word,
+    ``check_status`` raises, and so does the next ``chunk_kda`` call on the device."""
+    from cula_b200.kda import check_status, chunk_kda
+    inp = make_inputs(1, 128, 2, seed=14, gate_offset=-7.0)
+    d = {k: v.cuda() for k, v in inp.items() if v is not None}
+    kw = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=d["A_log"],
+              dt_bias=d["dt_bias"])
+    torch.cuda.synchronize()
+    check_status()
+    big = d["v"].clone()
+    big[0, 70, 1, 5] = 3.0e5
+    chunk_kda(d["q"], d["k"], big, d["g"], d["beta"], **kw)
+    with pytest.raises(RuntimeError, match="fp16 range"):
+        check_status()
+    check_status()                                   # cleared by the raise
+    chunk_kda(d["q"], d["k"], big, d["g"], d["beta"], **kw)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="fp16 range"):
+        chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], **kw)      # surfaced by the following call
+    o, _ = chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], **kw)   # and the device is usable afterwards
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.isfinite(o).all()
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait on a barrier that nothing ever completes must run out after its (here: short) limit, set the
+    time-out status and let the kernel return -- the same bounded wait every pipeline of the library uses."""
+    import time
+    from cula_b200 import _native
+    lib = _native.lib()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    t0 = time.perf_counter()
+    _native.check(lib.cula_kda_selftest_bounded_wait(status.data_ptr(), 2000, stream), "selftest")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert int(status.item()) == 1
+    # the context is intact: an ordinary forward still works
+    inp = make_inputs(1, 64, 1, seed=1, gate_offset=-6.0)
+    o, ht = run_chunk_kda(inp)
+    assert torch.isfinite(o).all()
