@@ -206,7 +206,10 @@ def test_disable_recompute_keeps_the_forward_intermediates():
         assert chunk_mod.FORWARD_CALLS - before == (0 if keep else 1)
         grads[keep] = {n: t.grad.float().cpu() for n, t in dev.items()}
     for n in grads[True]:
-        assert torch.equal(grads[True][n], grads[False][n]), n
+        if n in ("A_log", "dt_bias"):           # atomic sums: equal up to the order of the additions
+            assert err_ratio(grads[True][n], grads[False][n]) < 1e-5, n
+        else:
+            assert torch.equal(grads[True][n], grads[False][n]), n
     # nothing is kept when no input asks for a gradient or grad mode is off
     d = {n: t.cuda() for n, t in inp.items()}
     with torch.no_grad():
