@@ -11,7 +11,7 @@ if ROOT not in sys.path:
 
 GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 GOLDEN_CASES = ["strong_gate_T130", "weak_gate_T200_h0", "softplus_gate_T96", "pre_gated_T63",
-                "varlen_15_70_64_37"]
+                "varlen_15_70_64_37", "uniform_qkv_masked_gate_T150"]
 
 
 def pytest_configure(config):

@@ -27,6 +27,9 @@ CASES = [
     ("softplus_gate_T96", 2, 96, 1, True, True, False, -4.0, 0.5, None),
     ("pre_gated_T63", 1, 63, 1, False, False, True, 0.0, 1.0, None),
     ("varlen_15_70_64_37", 1, 186, 1, True, True, True, -6.0, 0.5, [15, 70, 64, 37]),
+    # the distributions of the reference's own grid (tests/test_kda.py:77-98): q, k, v ~ U(0,1) (all-positive,
+    # highly correlated keys), log-sigmoid gates of which half are exactly 0 (no decay), h0 ~ N(0,1)
+    ("uniform_qkv_masked_gate_T150", 1, 150, 2, False, False, True, "uniform", 1.0, None),
 ]
 
 
@@ -42,7 +45,11 @@ def main():
     for ci, (name, B, T, H, l2, gate_in, safe, goff, h0_std, lens) in enumerate(CASES):
         gen = torch.Generator().manual_seed(1000 + ci)
         rn = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float32)
-        q, k, v = (rn(B, T, H, K).to(torch.bfloat16) for _ in range(3))
+        uniform = goff == "uniform"
+        if uniform:
+            q, k, v = (torch.rand(B, T, H, K, generator=gen).to(torch.bfloat16) for _ in range(3))
+        else:
+            q, k, v = (rn(B, T, H, K).to(torch.bfloat16) for _ in range(3))
         if not l2:  # the caller normalises beforehand, as tests/test_kda.py:117-118 does
             q, k = (F.normalize(x.float(), p=2, dim=-1).to(torch.bfloat16) for x in (q, k))
         if gate_in:
@@ -51,6 +58,8 @@ def main():
             dt_bias = 0.2 * rn(H * K)
         else:  # gate already in log space, fp32, clamped to the safe range as tests/test_kda.py:88-91
             g = (F.logsigmoid(rn(B, T, H, K)) / 1.0).clamp(-5, 0)
+            if uniform:
+                g = g * (torch.rand(B, T, H, K, generator=gen) > 0.5)
             A_log = dt_bias = None
         beta = torch.sigmoid(rn(B, T, H)).to(torch.bfloat16)
         N = B if lens is None else len(lens)
