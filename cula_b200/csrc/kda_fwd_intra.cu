@@ -2,7 +2,7 @@
 //   gate activation + per-chunk cumulative sum (log2 domain), q/k L2 normalisation,
 //   the gated 64x64 Gram matrices Aqk / L (one M=128 x N=160 TF32 UMMA chain, accumulators in TMEM),
 //   Akk = (I + L)^-1 (blocked 16 -> 32 -> 64 inverse in fp32),
-//   [w | u] = Akk [beta k 2^g | beta v] (one M=128 x N=256 FP16 UMMA chain),
+//   [w | u] = Akk [beta k 2^g | beta v] (two M=128 x N=128 FP16 UMMA chains),
 //   kg = k 2^(g_last - g), qg = scale q 2^g,
 // and writes the tile pack the state scan consumes (layout in kda_common.cuh).
 //
@@ -18,38 +18,63 @@
 // is [q-hat ; k-hat] scaled by their own block anchors (128 rows). Column block I of the 128 x 160
 // product is valid on the rows of block I only; the epilogue reads exactly those.
 //
-// Two CTAs are resident per SM (107 KB shared memory, 256 TMEM columns each), so one CTA's MUFU-heavy
+// Two CTAs are resident per SM (96 KB shared memory, 256 TMEM columns each), so one CTA's CUDA-core
 // operand generation overlaps the other's MMA, inverse and epilogues.
 #include "kda_common.cuh"
 #include "kda_params.h"
 #include "umma.cuh"
 
+// Optional per-phase cycle counters (compile with -DKDA_PHASE_TIMERS): thread 0 of every CTA adds the clock64() spent
+// between consecutive marks into [gridDim.x][16] long long placed right after the p.mkk_out array (profiling builds only).
+#ifdef KDA_PHASE_TIMERS
+#define PHASE_MARK(i)                                                                 \
+    do {                                                                              \
+        if (tid == 0) {                                                               \
+            const long long now_ = clock64();                                         \
+            atomicAdd(reinterpret_cast<unsigned long long*>(p.mkk_out + (size_t)p.num_tiles * 4096) + blockIdx.x * 16 + (i), \
+                      (unsigned long long)(now_ - phase_t0_));   /* a reduction: nothing waits for it */          \
+            phase_t0_ = now_;                                                         \
+        }                                                                             \
+    } while (0)
+#else
+#define PHASE_MARK(i) do {} while (0)
+#endif
+
 namespace kda {
 
-constexpr int INTRA_THREADS = 256;              // 256 or 512 (the thread mappings below follow it)
+constexpr int INTRA_THREADS = 256;              // 8 warps; warp w owns token rows 8w .. 8w+7 in the first phases
 constexpr int NWARPS = INTRA_THREADS / 32;
-constexpr int RS = 512 / INTRA_THREADS;          // 64-row slots per thread in the (row, 8-lane) mapping
-constexpr int RSTEP = INTRA_THREADS / 8;         // row distance between a thread's slots
-constexpr int NIT = 1024 / INTRA_THREADS;        // (row, 16-lane) items per thread
-constexpr int NPART = INTRA_THREADS / 128;       // row segments of the column scan
+constexpr int NIT = 1024 / INTRA_THREADS;        // (row, 16-lane) items per thread when v is staged
+constexpr int INFO_THREAD = 224;                 // the thread that works out the next tile's geometry
 
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr int SM_OPA = 0;                 // A operand of one 64-channel half: [2 k-atoms][128 rows][128 B], SW128
 constexpr int SM_OPB = 32768;             // B operand: [2 k-atoms][160 rows][128 B], SW128
-constexpr int SM_G = 73728;               // G [64][128] fp32
-constexpr int SM_MISC = 106496;           // beta[64], barriers, tmem base, segment totals of the column scan
-constexpr int SM_TOTAL = 108544;
-static_assert(SM_MISC + 512 + NPART * 128 * 4 <= SM_TOTAL, "segment totals must fit the misc region");
+constexpr int SM_XS = 73728;              // X = beta k 2^g, fp16 [2 mn-atoms][64 tokens][128 B], SW128 (MN-major B operand)
+constexpr int SM_MISC = 90112;            // per-tile scalars (beta[2][64], alpha[2], dt_bias[2][128]: this tile's and the
+                                          // next tile's), barriers, tmem base, abort flag
+constexpr int SM_BIAS = SM_MISC + 1024;   // [2][128] fp32
+constexpr int SM_TOT = SM_MISC + 2048;    // [8][128] fp32: sum of the log2 decays of each 8-row group
+constexpr int SM_A16 = SM_TOT + 4096;     // [4][128] fp32: log2 decay of the first row of each 16-row block
+// per-channel tables built once per tile from the two arrays above (by 128 threads, one channel each)
+constexpr int SM_PRE = SM_A16 + 2048;     // [8][128] sum of the groups before group w
+constexpr int SM_R = SM_PRE + 4096;       // [5][128] r_0..r_3: cumulative log2 decay at the first row of each block; r_4 = g_last
+constexpr int SM_CG = SM_R + 2560;        // [4][128] 2^(r_I)
+constexpr int SM_CB = SM_CG + 2048;       // [4][128] 2^(r_I - r_{I+1})
+constexpr int SM_CK = SM_CB + 2048;       // [4][128] 2^(g_last - r_{I+1})
+constexpr int SM_C2 = SM_CK + 2048;       // [128]    2^(r_2 - r_1)
+constexpr int SM_C3 = SM_C2 + 512;        // [2][128] 2^(r_3 - r_{I+1}), I = 0, 1
+constexpr int SM_TOTAL = SM_C3 + 1024;
 constexpr int KATOM_A = 16384, KATOM_B = 20480;
 // regions reused once the Gram MMAs have completed
-constexpr int SM_XS = SM_OPA;             // X = beta k 2^g, fp16 [2 mn-atoms][64 tokens][128 B], SW128 (MN-major B operand)
-constexpr int SM_YS = SM_OPA + 16384;     // Y = beta v, same layout
+constexpr int SM_YS = SM_OPA;             // Y = beta v, same layout as X
 constexpr int LROW = 68;                  // padded fp32 row of the 64x64 matrices
 constexpr int SM_LF = SM_OPB;             // L fp32 [64][68]
 constexpr int SM_AINV = SM_OPB + 17408;   // (I+L)^-1 fp32 [64][68]
 constexpr int SM_TM = SM_OPB + 34816;     // scratch for the block products [32][36]
 constexpr int TROW = 36;
-constexpr int SM_AKK16 = SM_G;            // Akk fp16, stacked twice: [128][128 B], SW128 (K-major A operand)
+constexpr int SM_AKK16 = SM_LF;           // Akk fp16, stacked twice: [128][128 B], SW128 (K-major A operand); L is dead by then
+static_assert(SM_TM + 32 * TROW * 4 <= SM_XS, "inverse scratch must fit the B operand region");
 
 
 __device__ __forceinline__ uint64_t sdesc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -104,24 +129,62 @@ __device__ __forceinline__ void mma_tile_3xtf32(const float* A, int lda, const f
     }
 }
 
+// ---- packed fp32 pairs (one instruction per two lanes of arithmetic on sm_100) ----
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 r;
+    asm("{.reg .b64 ra, rb, rc; mov.b64 ra, {%2, %3}; mov.b64 rb, {%4, %5}; mul.rn.f32x2 rc, ra, rb; mov.b64 {%0, %1}, rc;}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 r;
+    asm("{.reg .b64 ra, rb, rc; mov.b64 ra, {%2, %3}; mov.b64 rb, {%4, %5}; add.rn.f32x2 rc, ra, rb; mov.b64 {%0, %1}, rc;}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 r;
+    asm("{.reg .b64 ra, rb, rc, rd; mov.b64 ra, {%2, %3}; mov.b64 rb, {%4, %5}; mov.b64 rc, {%6, %7}; "
+        "fma.rn.f32x2 rd, ra, rb, rc; mov.b64 {%0, %1}, rd;}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return r;
+}
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return add2(a, make_float2(-b.x, -b.y)); }
+__device__ __forceinline__ float2 ex2_2(float2 a) { return make_float2(fast_exp2(a.x), fast_exp2(a.y)); }
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+// round to tf32 (ties away from zero) by adding half an ulp of the 10-bit mantissa; the tensor core ignores the
+// 13 low bits. Cheaper than cvt.rna.tf32, and the operands here are finite and far from the top of the range.
+__device__ __forceinline__ float rnd_tf32(float x) { return __uint_as_float(__float_as_uint(x) + 0x1000u); }
+__device__ __forceinline__ float4 tf32x4(float2 a, float2 b) {
+    return make_float4(rnd_tf32(a.x), rnd_tf32(a.y), rnd_tf32(b.x), rnd_tf32(b.y));
+}
+__device__ __forceinline__ uint2 f16x4(float2 a, float2 b) { return make_uint2(pack_f16(a.x, a.y), pack_f16(b.x, b.y)); }
+
 __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const IntraParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sm_u32 = smem_u32(sm);
-    float* sG = reinterpret_cast<float*>(sm + SM_G);
-    float* sBeta = reinterpret_cast<float*>(sm + SM_MISC);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SM_MISC + 256);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + SM_MISC + 288);
-    float* sHalf = reinterpret_cast<float*>(sm + SM_MISC + 512);      // [NPART][128] segment totals
+    float* sBetaBuf = reinterpret_cast<float*>(sm + SM_MISC);            // [2][64]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SM_MISC + 512);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + SM_MISC + 544);
+    volatile int* sAbort = reinterpret_cast<volatile int*>(sm + SM_MISC + 552);
+    float* sAlpha = reinterpret_cast<float*>(sm + SM_MISC + 560);        // [2] exp(A_log[h])
+    int4* sInfo = reinterpret_cast<int4*>(sm + SM_MISC + 576);           // [2] {first token row, valid rows, head, tile slot}
+    float* sBiasBuf = reinterpret_cast<float*>(sm + SM_BIAS);            // [2][128]
+    float* sTot = reinterpret_cast<float*>(sm + SM_TOT);
+    float* sA16 = reinterpret_cast<float*>(sm + SM_A16);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t tok_stride = (size_t)p.H * DK;
-    const int l8 = tid & 7, rq = tid >> 3;
+    // first phases: warp w owns rows 8w..8w+7 (all of them in 16-row block I = w / 2); lane (r2, cq) owns rows
+    // 8w + 4 r2 + j, j = 0..3, and channels 64 hf + 4 cq + e, e = 0..3, of both 64-channel halves hf
+    const int r2 = lane >> 4, cq = lane & 15, I = warp >> 1, row0 = 8 * warp + 4 * r2;
 
     if (tid == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
         mbar_init(&bars[2], 1);
+        *sAbort = 0;
         fence_mbar_init();
     }
     if (warp == 0) umma::tmem_alloc(tmem_slot, 256);
@@ -129,63 +192,121 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+#ifdef KDA_PHASE_TIMERS
+    long long phase_t0_ = clock64();
+#endif
 
-    uint2 qraw[RS][4], kraw[RS][4];
-    uint2 graw[NIT][2];             // bf16 gate rows of the (row, 16-lane) mapping; fp32 gates are loaded in place
-    auto fetch_rows = [&](int t_id) {
-        const int c2 = t_id / p.H, h2 = t_id - c2 * p.H;
-        const ChunkInfo ci2 = chunk_info(c2, p.cu_seqlens, p.chunk_indices, p.T);
-        const size_t base2 = (size_t)ci2.row0 * tok_stride + (size_t)h2 * DK;
-        const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q);
-        const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(p.k);
-#pragma unroll
-        for (int rs = 0; rs < RS; ++rs) {
-            const int row = rq + RSTEP * rs;
-#pragma unroll
-            for (int grp = 0; grp < 4; ++grp) {
-                uint2 qv = make_uint2(0, 0), kv = make_uint2(0, 0);
-                if (row < ci2.valid) {
-                    size_t off = base2 + (size_t)row * tok_stride + 32 * grp + 4 * l8;
-                    qv = *reinterpret_cast<const uint2*>(qp + off);
-                    kv = *reinterpret_cast<const uint2*>(kp + off);
-                }
-                qraw[rs][grp] = qv;
-                kraw[rs][grp] = kv;
+    // One thread waits (bounded) for the tensor-core completion barrier; everybody else parks on the CTA barrier.
+    // On a time-out the status word is set and the whole CTA leaves the tile loop together (TMEM is freed below).
+    auto wait_mma = [&](int which, uint32_t parity) -> bool {
+        if (tid == 0) {
+            if (!mbar_wait(&bars[which], parity)) {
+                atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+                *sAbort = 1;
             }
+            umma::fence_before_sync();
         }
-        if (!p.g_fp32) {
-#pragma unroll
-            for (int n = 0; n < NIT; ++n) {
-                const int row = (tid >> 4) + (INTRA_THREADS / 16) * n;
-                graw[n][0] = graw[n][1] = make_uint2(0, 0);
-                if (row < ci2.valid) {
-                    const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.g) + base2 + (size_t)row * tok_stride + 4 * (tid & 15);
-                    graw[n][0] = *reinterpret_cast<const uint2*>(gp);
-                    graw[n][1] = *reinterpret_cast<const uint2*>(gp + 64);
-                }
+        __syncthreads();
+        umma::fence_after_sync();
+        return *sAbort == 0;
+    };
+
+    // The geometry of a tile (integer divisions, table look-ups for a packed batch) is worked out by ONE thread, one
+    // tile ahead, and handed to the others through shared memory.
+    auto publish_info = [&](int t_id, int buf) {
+        if (tid == INFO_THREAD) {
+            int4 v = make_int4(0, 0, 0, 0);
+            if (t_id < p.num_tiles) {
+                const int c2 = t_id / p.H;
+                const ChunkInfo ci2 = chunk_info(c2, p.cu_seqlens, p.chunk_indices, p.T);
+                v = make_int4(ci2.row0, ci2.valid, t_id - c2 * p.H, t_id);
             }
+            sInfo[buf] = v;
         }
     };
-    if ((int)blockIdx.x < p.num_tiles) fetch_rows(blockIdx.x);
+    // Register prefetch: the raw gate rows are fetched one tile ahead (they are the first thing a tile needs); q and k
+    // rows are fetched at the top of their own tile and first used after the gate phase, from L2 (see l2_hints).
+    // Loads are unconditional (nothing may depend on a loaded value before it is used): a padding row reads the last
+    // real row of the chunk instead, and is zeroed where it is used (through its gate, norm and beta factors).
+    uint2 qraw[4][2], kraw[4][2], graw[4][2];     // [row j][half]: 4 bf16 each; fp32 gates are loaded in place instead
+    auto fetch_g = [&](const int4 nf) {
+        if (p.g_fp32) return;
+        const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.g) + (size_t)nf.x * tok_stride + (size_t)nf.z * DK + 4 * cq;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const size_t roff = (size_t)min(row0 + j, nf.y - 1) * tok_stride;
+            graw[j][0] = *reinterpret_cast<const uint2*>(gp + roff);
+            graw[j][1] = *reinterpret_cast<const uint2*>(gp + roff + 64);
+        }
+    };
+    auto fetch_qk = [&](const int4 nf) {
+        const size_t base2 = (size_t)nf.x * tok_stride + (size_t)nf.z * DK + 4 * cq;
+        const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + base2;
+        const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(p.k) + base2;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const size_t roff = (size_t)min(row0 + j, nf.y - 1) * tok_stride;
+            qraw[j][0] = *reinterpret_cast<const uint2*>(qp + roff);
+            qraw[j][1] = *reinterpret_cast<const uint2*>(qp + roff + 64);
+            kraw[j][0] = *reinterpret_cast<const uint2*>(kp + roff);
+            kraw[j][1] = *reinterpret_cast<const uint2*>(kp + roff + 64);
+        }
+    };
+    // Per-tile scalars (beta of the 64 rows, dt_bias and exp(A_log) of the head) are fetched one tile ahead by the
+    // first 129 threads into a register each and parked in shared memory before the tile ends, so that no phase of
+    // the next tile starts with a dependent global load.
+    uint32_t sc_next = 0;        // raw bits: nothing may depend on the load before it is parked
+    auto load_scalars = [&](const int4 nf) {
+        const int h2 = nf.z;
+        sc_next = 0;
+        if (tid < BT) {
+            if (tid < nf.y) {
+                const size_t bi = (size_t)(nf.x + tid) * p.H + h2;
+                sc_next = p.beta_fp32 ? reinterpret_cast<const uint32_t*>(p.beta)[bi]
+                                      : (uint32_t)reinterpret_cast<const uint16_t*>(p.beta)[bi];
+            }
+        } else if (tid < BT + DK) {
+            if (p.gate_mode != GATE_NONE && p.dt_bias) sc_next = __float_as_uint(p.dt_bias[h2 * DK + tid - BT]);
+        } else if (tid == BT + DK) {
+            if (p.gate_mode != GATE_NONE) sc_next = __float_as_uint(p.A_log[h2]);
+        }
+    };
+    auto park_scalars = [&](int buf) {
+        if (tid < BT) sBetaBuf[buf * BT + tid] = p.beta_fp32 ? __uint_as_float(sc_next) : __uint_as_float(sc_next << 16);
+        else if (tid < BT + DK) sBiasBuf[buf * DK + tid - BT] = __uint_as_float(sc_next);
+        else if (tid == BT + DK) sAlpha[buf] = p.gate_mode != GATE_NONE ? __expf(__uint_as_float(sc_next)) : 0.f;
+    };
+    publish_info(blockIdx.x, 0);
+    __syncthreads();
+    if ((int)blockIdx.x < p.num_tiles) {
+        fetch_g(sInfo[0]);
+        load_scalars(sInfo[0]);
+        park_scalars(0);
+    }
+    __syncthreads();
 
     // persistent over (chunk, head) tiles; the completion barriers flip phase once per tile
     for (int tile_id = blockIdx.x, iter = 0; tile_id < p.num_tiles; tile_id += gridDim.x, ++iter) {
     const uint32_t par = iter & 1;
-    const int c = tile_id / p.H, h = tile_id - c * p.H;
-    const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
+    const float* sBeta = sBetaBuf + par * BT;
+    const int4 info = sInfo[par];
+    struct { int row0, valid; } ci = {info.x, info.y};
+    const int h = info.z;
     const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DK;
-    unsigned char* tile = p.tiles + ((size_t)c * p.H + h) * TP_BYTES;
+    unsigned char* tile = p.tiles + (size_t)tile_id * TP_BYTES;       // tile slot = chunk * H + head = tile_id
+    publish_info(tile_id + gridDim.x, par ^ 1);      // visible to everybody after the next barrier
+    fetch_qk(info);
 
-    // q, k, g rows of this tile are already in registers: they were fetched while the previous tile was in its
-    // epilogues (first tile: before the loop). Thread (rq, l8): rows rq (+RSTEP), channels 32*grp + 4*l8 .. +3.
-    if (tid < 256) {   // pull this tile's v rows and the next tile's inputs towards L2 (two 128-byte lines per row)
+    // the gate rows of this tile are already in registers: they were fetched while the previous tile was in its
+    // epilogues (first tile: before the loop).
+    auto l2_hints = [&]() {   // pull this tile's v rows and the next tile's inputs towards L2 (two 128-byte lines per row)
         const int row = tid >> 2, part = tid & 3;
         if (part < 2 && row < ci.valid)
             prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.v) + base + (size_t)row * tok_stride + 64 * part);
-        const int nt = tile_id + gridDim.x;
-        if (nt < p.num_tiles) {
-            const int nc = nt / p.H, nh = nt - nc * p.H;
-            const ChunkInfo ni = chunk_info(nc, p.cu_seqlens, p.chunk_indices, p.T);
+        const int4 nf = sInfo[par ^ 1];
+        if (nf.y > 0) {
+            struct { int row0, valid; } ni = {nf.x, nf.y};
+            const int nh = nf.z;
             if (row < ni.valid) {
                 const size_t nb = (size_t)(ni.row0 + row) * tok_stride + (size_t)nh * DK + 64 * (part & 1);
                 if (part < 2) {
@@ -199,185 +320,223 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 }
             }
         }
-    }
-
-    // ---- 1a. gate activation with wide, coalesced loads: item (row, pc) covers channels 4pc..4pc+3 and
-    //          64+4pc..64+4pc+3; the activated log2 decay goes to sG (zero for padding rows) ----
+    };
+    // ---- 1. gate activation (log2 domain) and the cumulative sum over the thread's four rows, then over the
+    //         warp's eight rows with one exchange between the two lane halves; padding rows contribute 0 ----
+    float2 G[4][4];            // [row j][pair]: pairs 0,1 = channels 4cq..4cq+3, pairs 2,3 = 64+4cq..64+4cq+3
     {
-        const float alpha = p.gate_mode != GATE_NONE ? __expf(p.A_log[h]) : 0.f;
-        const int pc = tid & 15;
-        float bias[8];
+        PHASE_MARK(15);                 // what the compiler placed at the top of a tile (index and address arithmetic)
+        const float alpha = sAlpha[par];
+        float2 bias[4];
+        {
+            const float4 b0 = *reinterpret_cast<const float4*>(sBiasBuf + par * DK + 4 * cq);
+            const float4 b1 = *reinterpret_cast<const float4*>(sBiasBuf + par * DK + 64 + 4 * cq);
+            bias[0] = make_float2(b0.x, b0.y); bias[1] = make_float2(b0.z, b0.w);
+            bias[2] = make_float2(b1.x, b1.y); bias[3] = make_float2(b1.z, b1.w);
+        }
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-            bias[e] = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] : 0.f;
-        float gv[NIT][8];
-#pragma unroll
-        for (int n = 0; n < NIT; ++n) {
-            const int row = (tid >> 4) + (INTRA_THREADS / 16) * n;
-            const size_t off = base + (size_t)row * tok_stride + 4 * pc;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) gv[n][e] = 0.f;
-            if (row < ci.valid) {
-                if (p.g_fp32) {
-                    const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
-                    const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
-                    gv[n][0] = lo.x; gv[n][1] = lo.y; gv[n][2] = lo.z; gv[n][3] = lo.w;
-                    gv[n][4] = hi.x; gv[n][5] = hi.y; gv[n][6] = hi.z; gv[n][7] = hi.w;
-                } else {
-                    const uint2 lo = graw[n][0], hi = graw[n][1];
-                    float2 f;
-                    f = unpack_bf16(lo.x); gv[n][0] = f.x; gv[n][1] = f.y;
-                    f = unpack_bf16(lo.y); gv[n][2] = f.x; gv[n][3] = f.y;
-                    f = unpack_bf16(hi.x); gv[n][4] = f.x; gv[n][5] = f.y;
-                    f = unpack_bf16(hi.y); gv[n][6] = f.x; gv[n][7] = f.y;
+        for (int j = 0; j < 4; ++j) {
+            const bool live = row0 + j < ci.valid;
+            float2 gv[4];
+            if (p.g_fp32) {
+                float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+                if (live) {
+                    const float* gp = reinterpret_cast<const float*>(p.g) + base + (size_t)(row0 + j) * tok_stride + 4 * cq;
+                    lo = *reinterpret_cast<const float4*>(gp);
+                    hi = *reinterpret_cast<const float4*>(gp + 64);
                 }
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < NIT; ++n) {
-            const int row = (tid >> 4) + (INTRA_THREADS / 16) * n;
-            if (p.gate_mode == GATE_LOWER_BOUND) {
-                // lower_bound * sigmoid(alpha x) / ln2 with one ex2 and one rcp (flush-to-zero approximations)
-                const float c0 = -alpha * RCP_LN2, c1 = (row < ci.valid) ? p.lower_bound * RCP_LN2 : 0.f;
-                float a[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) a[e] = c1 * fast_rcp(1.f + fast_exp2(c0 * (gv[n][e] + bias[e])));
-                *reinterpret_cast<float4*>(sG + row * DK + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
-                *reinterpret_cast<float4*>(sG + row * DK + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
+                gv[0] = make_float2(lo.x, lo.y); gv[1] = make_float2(lo.z, lo.w);
+                gv[2] = make_float2(hi.x, hi.y); gv[3] = make_float2(hi.z, hi.w);
             } else {
-                // other gate forms: rolled, element by element (keeps the long softplus code out of line)
-                const float keep = (row < ci.valid) ? RCP_LN2 : 0.f;
+                gv[0] = unpack_bf16(graw[j][0].x); gv[1] = unpack_bf16(graw[j][0].y);
+                gv[2] = unpack_bf16(graw[j][1].x); gv[3] = unpack_bf16(graw[j][1].y);
+            }
+            if (p.gate_mode == GATE_LOWER_BOUND) {
+                // lower_bound * sigmoid(alpha x) / ln2 with one ex2 and one rcp per element (flush-to-zero approximations)
+                const float2 c0 = splat2(-alpha * RCP_LN2), c1 = splat2(live ? p.lower_bound * RCP_LN2 : 0.f);
 #pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    sG[row * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] =
-                        keep * gate_activation(gv[n][e], alpha, bias[e], p.gate_mode, p.lower_bound);
+                for (int x = 0; x < 4; ++x) {
+                    const float2 e = add2(ex2_2(mul2(c0, add2(gv[x], bias[x]))), splat2(1.f));
+                    G[j][x] = mul2(c1, make_float2(fast_rcp(e.x), fast_rcp(e.y)));
+                }
+            } else {
+                const float keep = live ? RCP_LN2 : 0.f;
+#pragma unroll
+                for (int x = 0; x < 4; ++x)
+                    G[j][x] = make_float2(keep * gate_activation(gv[x].x, alpha, bias[x].x, p.gate_mode, p.lower_bound),
+                                          keep * gate_activation(gv[x].y, alpha, bias[x].y, p.gate_mode, p.lower_bound));
             }
         }
-    }
-    __syncthreads();
-    // ---- 1b. cumulative sum down the rows: thread (part, d) scans its 64/NPART rows in shared memory ----
-    {
-        const int d = tid & 127, part = tid >> 7;
-        float run = 0.f;
+        PHASE_MARK(0); // gate activation
 #pragma unroll
-        for (int r = 0; r < 64 / NPART; ++r) {
-            const int row = part * (64 / NPART) + r;
-            run += sG[row * DK + d];
-            sG[row * DK + d] = run;
+        for (int j = 1; j < 4; ++j)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) G[j][x] = add2(G[j][x], G[j - 1][x]);
+        float2 oth[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            oth[x].x = __shfl_xor_sync(0xffffffffu, G[3][x].x, 16);
+            oth[x].y = __shfl_xor_sync(0xffffffffu, G[3][x].y, 16);
         }
-        sHalf[part * DK + d] = run;
-    }
-    // ---- 2. L2 norms from the rows held in registers, beta ----
-    float rstd_q[RS], rstd_k[RS], bet[RS];
-#pragma unroll
-    for (int rs = 0; rs < RS; ++rs) {
-        const int row = rq + RSTEP * rs;
-        float sq = 0.f, sk = 0.f;
-#pragma unroll
-        for (int grp = 0; grp < 4; ++grp) {
-            float2 a = unpack_bf16(qraw[rs][grp].x), b = unpack_bf16(qraw[rs][grp].y);
-            sq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
-            a = unpack_bf16(kraw[rs][grp].x); b = unpack_bf16(kraw[rs][grp].y);
-            sk += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
-        }
-        float b = 0.f;
-        if (row < ci.valid) {
-            size_t bi = (size_t)(ci.row0 + row) * p.H + h;
-            b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
-                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
-        }
-        bet[rs] = b;
-        if (l8 == 0) sBeta[row] = b;
-        if (p.use_l2norm) {
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        if (r2 == 0) {       // group total and, for the first warp of a 16-row block, the value at the block's first row
+            float* td = sTot + warp * DK + 4 * cq;
+            *reinterpret_cast<float4*>(td) = make_float4(G[3][0].x + oth[0].x, G[3][0].y + oth[0].y, G[3][1].x + oth[1].x, G[3][1].y + oth[1].y);
+            *reinterpret_cast<float4*>(td + 64) = make_float4(G[3][2].x + oth[2].x, G[3][2].y + oth[2].y, G[3][3].x + oth[3].x, G[3][3].y + oth[3].y);
+            if ((warp & 1) == 0) {
+                float* ad = sA16 + I * DK + 4 * cq;
+                *reinterpret_cast<float4*>(ad) = make_float4(G[0][0].x, G[0][0].y, G[0][1].x, G[0][1].y);
+                *reinterpret_cast<float4*>(ad + 64) = make_float4(G[0][2].x, G[0][2].y, G[0][3].x, G[0][3].y);
             }
-            rstd_q[rs] = rsqrtf(sq + 1e-6f);
-            rstd_k[rs] = rsqrtf(sk + 1e-6f);
         } else {
-            rstd_q[rs] = rstd_k[rs] = 1.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) G[j][x] = add2(G[j][x], oth[x]);
         }
     }
-    __syncthreads();
-    if (tid >= 128) {   // later row segments add the totals of the earlier ones
-        const int d = tid & 127, part = tid >> 7;
-        float t0 = 0.f;
-        for (int q = 0; q < part; ++q) t0 += sHalf[q * DK + d];
-#pragma unroll 8
-        for (int r = 0; r < 64 / NPART; ++r) sG[(part * (64 / NPART) + r) * DK + d] += t0;
+    PHASE_MARK(2);      // in-warp cumulative sum, totals
+    // ---- 2. L2 norms of the thread's four q and k rows (sum over the 16 lanes that share the rows), beta ----
+    float rstd_q[4], rstd_k[4], bet[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float2 sq = make_float2(0.f, 0.f), sk = sq;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            float2 a = unpack_bf16(qraw[j][hf].x), b = unpack_bf16(qraw[j][hf].y);
+            sq = fma2(a, a, sq); sq = fma2(b, b, sq);
+            a = unpack_bf16(kraw[j][hf].x); b = unpack_bf16(kraw[j][hf].y);
+            sk = fma2(a, a, sk); sk = fma2(b, b, sk);
+        }
+        bet[j] = sBeta[row0 + j];
+        if (p.use_l2norm) {
+            float s1 = sq.x + sq.y, s2 = sk.x + sk.y;
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) {
+                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+            }
+            rstd_q[j] = rsqrtf(s1 + 1e-6f);
+            rstd_k[j] = rsqrtf(s2 + 1e-6f);
+        } else {
+            rstd_q[j] = rstd_k[j] = 1.f;
+        }
+        if (row0 + j >= ci.valid) rstd_q[j] = rstd_k[j] = 0.f;      // padding rows: q = k = 0
     }
-    __syncthreads();
-    if (tid < DK) reinterpret_cast<float*>(tile + TP_DECAY)[tid] = fast_exp2(sG[63 * DK + tid]);
+    PHASE_MARK(14);     // norms, beta
+    __syncthreads();          // group totals and block-start values are visible
+    PHASE_MARK(1);      // barrier
+    if (tid < DK) {
+        // one channel per thread: prefix sums of the group totals, the block anchors, and every per-(block, channel)
+        // constant of the operand generation below (15 exponentials per channel instead of several per element)
+        float run = 0.f, P[NWARPS];
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            P[w] = run;
+            reinterpret_cast<float*>(sm + SM_PRE)[w * DK + tid] = run;
+            run += sTot[w * DK + tid];
+        }
+        const float r[5] = {sA16[tid], P[2] + sA16[DK + tid], P[4] + sA16[2 * DK + tid], P[6] + sA16[3 * DK + tid], run};
+        reinterpret_cast<float*>(tile + TP_DECAY)[tid] = fast_exp2(run);      // 2^(g_last): the decay of the whole chunk
+#pragma unroll
+        for (int b = 0; b < 5; ++b) reinterpret_cast<float*>(sm + SM_R)[b * DK + tid] = r[b];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            reinterpret_cast<float*>(sm + SM_CG)[b * DK + tid] = fast_exp2(r[b]);
+            // >= 1, <= 2^116 under the safe gate; the clamp keeps an unbounded gate from making inf * 0
+            reinterpret_cast<float*>(sm + SM_CB)[b * DK + tid] = fast_exp2(fminf(r[b] - r[b + 1], 126.f));
+            reinterpret_cast<float*>(sm + SM_CK)[b * DK + tid] = fast_exp2(run - r[b + 1]);
+        }
+        reinterpret_cast<float*>(sm + SM_C2)[tid] = fast_exp2(r[2] - r[1]);
+        reinterpret_cast<float*>(sm + SM_C3)[tid] = fast_exp2(r[3] - r[1]);
+        reinterpret_cast<float*>(sm + SM_C3)[DK + tid] = fast_exp2(r[3] - r[2]);
+    }
+    __syncthreads();          // tables are visible
+    PHASE_MARK(2);      // tables (same slot as the in-warp scan)
 
-    // ---- 3. operand generation + Gram MMAs, one 64-channel half at a time ----
-    uint2 xpk[RS][4];
+    // ---- 3. operand generation + Gram MMAs, one 64-channel half at a time. Per element only two exponentials:
+    //         eA = 2^(g_i - r_I) and f = 2^(r_N - g_i) (r_I: log2 decay at the first row of the element's 16-row
+    //         block, r_N: at the first row of the next block, or g_last for the last block; both factors <= 1).
+    //         Every other factor is one of them times a per-(block, channel) constant from the tables:
+    //           2^(g_i)        = eA 2^(r_I)               -> qg, x
+    //           2^(r_I - g_i)  = f 2^(r_I - r_N)          -> own-block copy of the B operand
+    //           2^(g_last-g_i) = f 2^(g_last - r_N)       -> kg
+    //           2^(r_J - g_i)  = f 2^(r_J - r_N), J > I+1 -> copies anchored at later blocks ----
 #pragma unroll 1
     for (int hf = 0; hf < 2; ++hf) {       // rolled: register arrays are picked with selects on static indices
-        if (hf == 1) {   // operand buffers are reused: wait until the first half's MMAs have read them
-            if (!mbar_wait(&bars[0], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
-            umma::fence_after_sync();
-        }
+        if (hf == 1 && !wait_mma(0, par)) break;   // operand buffers are reused: the first half's MMAs must have read them
+        if (hf == 1) PHASE_MARK(4);                // MMA issue + wait for the first half
+        // rI, rN: the two anchors minus the sum of the groups before this warp's rows, so that they can be compared
+        // with the thread's group-local cumulative sums directly
+        float2 rI[2], rN[2], cG[2], cB[2], cK[2], c2[2], c3[2];
+        {
+            const int co = 64 * hf + 4 * cq;
+            auto ld = [&](int off, float2 (&dst)[2]) {
+                const float4 t = *reinterpret_cast<const float4*>(sm + off + 4 * co);
+                dst[0] = make_float2(t.x, t.y); dst[1] = make_float2(t.z, t.w);
+            };
+            float2 pre[2];
+            ld(SM_PRE + warp * DK * 4, pre);
+            ld(SM_R + I * DK * 4, rI);
+            ld(SM_R + (I + 1) * DK * 4, rN);
+            ld(SM_CG + I * DK * 4, cG);
+            ld(SM_CB + I * DK * 4, cB);
+            ld(SM_CK + I * DK * 4, cK);
+            ld(SM_C2, c2);                            // used by block 0 only
+            ld(SM_C3 + (I & 1) * DK * 4, c3);         // used by blocks 0 and 1
 #pragma unroll
-        for (int rs = 0; rs < RS; ++rs) {
-            const int row = rq + RSTEP * rs, I = row >> 4, r7 = row & 7;
-#pragma unroll
-            for (int it = 0; it < 2; ++it) {
-                const int grp = hf * 2 + it, d0 = 32 * grp + 4 * l8;
-                const float4 Gi = *reinterpret_cast<const float4*>(sG + row * DK + d0);
-                const float4 rI = *reinterpret_cast<const float4*>(sG + 16 * I * DK + d0);
-                const float4 gL = *reinterpret_cast<const float4*>(sG + 63 * DK + d0);
-                const float gi[4] = {Gi.x, Gi.y, Gi.z, Gi.w}, ri[4] = {rI.x, rI.y, rI.z, rI.w};
-                const float gl[4] = {gL.x, gL.y, gL.z, gL.w};
-                float qv[4], kv[4];
-                {
-                    const uint2 qsel = hf ? qraw[rs][2 + it] : qraw[rs][it];
-                    const uint2 ksel = hf ? kraw[rs][2 + it] : kraw[rs][it];
-                    float2 a = unpack_bf16(qsel.x), b = unpack_bf16(qsel.y);
-                    qv[0] = a.x * rstd_q[rs]; qv[1] = a.y * rstd_q[rs]; qv[2] = b.x * rstd_q[rs]; qv[3] = b.y * rstd_q[rs];
-                    a = unpack_bf16(ksel.x); b = unpack_bf16(ksel.y);
-                    kv[0] = a.x * rstd_k[rs]; kv[1] = a.y * rstd_k[rs]; kv[2] = b.x * rstd_k[rs]; kv[3] = b.y * rstd_k[rs];
-                }
-                float qa[4], ka[4], kown[4], kg[4], qg[4], xx[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float eA = fast_exp2(gi[e] - ri[e]);      // <= 1
-                    const float eB = fast_exp2(fminf(ri[e] - gi[e], 120.f));   // >= 1, <= 2^116 under the safe gate; the clamp
-                                                                               // keeps an unbounded gate from making inf * 0
-                    const float eG = fast_exp2(gi[e]);              // 2^(g_i)
-                    qa[e] = qv[e] * eA;
-                    ka[e] = kv[e] * eA;
-                    kown[e] = kv[e] * eB;
-                    kg[e] = kv[e] * fast_exp2(gl[e] - gi[e]);
-                    qg[e] = p.scale * qv[e] * eG;
-                    xx[e] = bet[rs] * kv[e] * eG;
-                }
-                const uint32_t sw = (uint32_t)((l8 ^ r7) << 4);
-                unsigned char* opa = sm + SM_OPA + it * KATOM_A + sw;
-                unsigned char* opb = sm + SM_OPB + it * KATOM_B + sw;
-                *reinterpret_cast<float4*>(opa + row * 128) = tf32x4(qa[0], qa[1], qa[2], qa[3]);
-                *reinterpret_cast<float4*>(opa + (row + 64) * 128) = tf32x4(ka[0], ka[1], ka[2], ka[3]);
-                *reinterpret_cast<float4*>(opb + (8 * I * (I + 1) + row) * 128) = tf32x4(kown[0], kown[1], kown[2], kown[3]);
-#pragma unroll
-                for (int Ip = 1; Ip < 4; ++Ip) {
-                    if (Ip > I) {     // copy anchored at the first row of the later block Ip: factor 2^(r_Ip - g_j) <= 1
-                        const float4 rp = *reinterpret_cast<const float4*>(sG + 16 * Ip * DK + d0);
-                        *reinterpret_cast<float4*>(opb + (8 * Ip * (Ip + 1) + row) * 128) =
-                            tf32x4(kv[0] * fast_exp2(rp.x - gi[0]), kv[1] * fast_exp2(rp.y - gi[1]),
-                                   kv[2] * fast_exp2(rp.z - gi[2]), kv[3] * fast_exp2(rp.w - gi[3]));
-                    }
-                }
-                const int goff = swz256(row, d0);
-                *reinterpret_cast<uint2*>(tile + TP_KG + goff) = make_uint2(pack_f16(kg[0], kg[1]), pack_f16(kg[2], kg[3]));
-                *reinterpret_cast<uint2*>(tile + TP_QG + goff) = make_uint2(pack_f16(qg[0], qg[1]), pack_f16(qg[2], qg[3]));
-                const uint2 xv = make_uint2(pack_f16(xx[0], xx[1]), pack_f16(xx[2], xx[3]));
-                if (hf) xpk[rs][2 + it] = xv; else xpk[rs][it] = xv;
+            for (int x = 0; x < 2; ++x) {
+                rI[x] = sub2(rI[x], pre[x]);
+                rN[x] = sub2(rN[x], pre[x]);
             }
+        }
+        const int atom = cq >> 3;
+        unsigned char* opa = sm + SM_OPA + atom * KATOM_A;
+        unsigned char* opb = sm + SM_OPB + atom * KATOM_B;
+        unsigned char* xs = sm + SM_XS + hf * 8192;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int row = row0 + j;
+            const uint32_t sw = (uint32_t)(((cq & 7) ^ (row & 7)) << 4);
+            const uint2 qsel = hf ? qraw[j][1] : qraw[j][0];
+            const uint2 ksel = hf ? kraw[j][1] : kraw[j][0];
+            const float2 gi[2] = {hf ? G[j][2] : G[j][0], hf ? G[j][3] : G[j][1]};     // group-local cumulative sums
+            const float2 rq2 = splat2(rstd_q[j]), rk2 = splat2(rstd_k[j]);
+            const float2 qh[2] = {mul2(unpack_bf16(qsel.x), rq2), mul2(unpack_bf16(qsel.y), rq2)};
+            const float2 kh[2] = {mul2(unpack_bf16(ksel.x), rk2), mul2(unpack_bf16(ksel.y), rk2)};
+            float2 qa[2], ka[2], ko[2], kg[2], qg[2], xx[2], kf[2], k2[2], k3[2];
+            const float2 sc2 = splat2(p.scale), be2 = splat2(bet[j]);
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const float2 eA = ex2_2(sub2(gi[x], rI[x]));      // <= 1
+                const float2 f = ex2_2(sub2(rN[x], gi[x]));       // <= 1
+                qa[x] = mul2(qh[x], eA);
+                ka[x] = mul2(kh[x], eA);
+                kf[x] = mul2(kh[x], f);                           // k 2^(r_N - g_i): the copy anchored at the next block
+                ko[x] = mul2(kf[x], cB[x]);
+                kg[x] = mul2(kf[x], cK[x]);
+                k2[x] = mul2(kf[x], c2[x]);
+                k3[x] = mul2(kf[x], c3[x]);
+                const float2 qG = mul2(qa[x], cG[x]);             // q 2^(g_i)
+                qg[x] = mul2(qG, sc2);
+                xx[x] = mul2(mul2(ka[x], cG[x]), be2);
+            }
+            *reinterpret_cast<float4*>(opa + row * 128 + sw) = tf32x4(qa[0], qa[1]);
+            *reinterpret_cast<float4*>(opa + (row + 64) * 128 + sw) = tf32x4(ka[0], ka[1]);
+            *reinterpret_cast<float4*>(opb + (8 * I * (I + 1) + row) * 128 + sw) = tf32x4(ko[0], ko[1]);
+            // copies anchored at the first row of the later blocks: factor 2^(r_J - g_i) <= 1
+            if (I < 3) *reinterpret_cast<float4*>(opb + (8 * (I + 1) * (I + 2) + row) * 128 + sw) = tf32x4(kf[0], kf[1]);
+            if (I == 0) *reinterpret_cast<float4*>(opb + (8 * 2 * 3 + row) * 128 + sw) = tf32x4(k2[0], k2[1]);
+            if (I < 2) *reinterpret_cast<float4*>(opb + (8 * 3 * 4 + row) * 128 + sw) = tf32x4(k3[0], k3[1]);
+            const int goff = swz256(row, 64 * hf + 4 * cq);
+            *reinterpret_cast<uint2*>(tile + TP_KG + goff) = f16x4(kg[0], kg[1]);
+            *reinterpret_cast<uint2*>(tile + TP_QG + goff) = f16x4(qg[0], qg[1]);
+            // X = beta k 2^g as the MN-major B operand of the W/U product: [token][64 channels of this half], SW128
+            *reinterpret_cast<uint2*>(xs + row * 128 + ((((cq >> 1) ^ (row & 7))) << 4) + (cq & 1) * 8) = f16x4(xx[0], xx[1]);
         }
         fence_proxy_async();
         umma::fence_before_sync();
         __syncthreads();
+        PHASE_MARK(3 + 2 * hf);      // operand generation of this half (3, 5)
         if (tid == 0) {
             umma::fence_after_sync();
             const uint32_t idesc = umma::make_idesc(umma::FMT_TF32, 128, 160, false, false);
@@ -389,23 +548,17 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             }
             umma::commit(&bars[hf]);
         }
+        if (hf == 0) l2_hints();          // while the first half's MMAs run
     }
-    if (!mbar_wait(&bars[1], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
-    umma::fence_after_sync();
+    if (*sAbort || !wait_mma(1, par)) break;
+    PHASE_MARK(6);      // MMA issue + wait for the second half
 
-    // ---- 4. X and Y = beta v into shared memory (all threads); Gram epilogue: warp w reads TMEM lane
+    // ---- 4. Y = beta v into shared memory (all threads); Gram epilogue: warp w reads TMEM lane
     //         quadrant w&3 and handles the 16-row block (w&1)*2 + (w>>2) living in its lower/upper half ----
-#pragma unroll
-    for (int rs = 0; rs < RS; ++rs) {
-        const int row = rq + RSTEP * rs;
-#pragma unroll
-        for (int grp = 0; grp < 4; ++grp) {
-            const int chunk = 4 * (grp & 1) + (l8 >> 1);
-            *reinterpret_cast<uint2*>(sm + SM_XS + (grp >> 1) * 8192 + row * 128 + ((chunk ^ (row & 7)) << 4) + (l8 & 1) * 8) =
-                xpk[rs][grp];
-        }
+    if (tile_id + (int)gridDim.x < p.num_tiles) {          // land during the epilogues
+        fetch_g(sInfo[par ^ 1]);
+        load_scalars(sInfo[par ^ 1]);
     }
-    if (tile_id + (int)gridDim.x < p.num_tiles) fetch_rows(tile_id + gridDim.x);   // lands during the epilogues
     float* sL = reinterpret_cast<float*>(sm + SM_LF);
     float* sAi = reinterpret_cast<float*>(sm + SM_AINV);
     float* sT = reinterpret_cast<float*>(sm + SM_TM);
@@ -415,9 +568,10 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 #pragma unroll
         for (int n = 0; n < NIT; ++n) {
             const int idx = tid + INTRA_THREADS * n, j = idx >> 4, ch = idx & 15;
-            raw[n] = make_uint4(0, 0, 0, 0);
-            if (j < ci.valid) raw[n] = *reinterpret_cast<const uint4*>(vp + base + (size_t)j * tok_stride + 8 * ch);
+            // a padding row reads the last real row; its beta is 0, so Y = beta v is 0 there
+            raw[n] = *reinterpret_cast<const uint4*>(vp + base + (size_t)min(j, ci.valid - 1) * tok_stride + 8 * ch);
         }
+        PHASE_MARK(12);     // next tile's loads and this tile's v loads issued
         {
             const int qd = warp & 3, bsel = (warp >> 2) & 1, gpar = warp >> 3;   // gpar splits the column groups (16 warps)
             const int blk = (qd & 1) * 2 + bsel;            // 16-row block handled by this warp
@@ -458,7 +612,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                             *reinterpret_cast<float4*>(sL + row * LROW + 16 * gcol + 4 * q4) =
                                 make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
                         if (p.mkk_out) {     // the same Gram entries without beta, for the backward pass
-                            float* mo = p.mkk_out + ((size_t)c * p.H + h) * BT * BT + row * BT + 16 * gcol;
+                            float* mo = p.mkk_out + (size_t)tile_id * BT * BT + row * BT + 16 * gcol;
 #pragma unroll
                             for (int q4 = 0; q4 < 4; ++q4) {
                                 float mv[4];
@@ -474,6 +628,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 }
             }
         }
+        PHASE_MARK(13);     // Gram epilogue
 #pragma unroll
         for (int n = 0; n < NIT; ++n) {
             const int idx = tid + INTRA_THREADS * n, j = idx >> 4, ch = idx & 15;
@@ -489,8 +644,10 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 make_uint4(o4[0], o4[1], o4[2], o4[3]);
         }
     }
+    park_scalars(par ^ 1);
     umma::fence_before_sync();
     __syncthreads();
+    PHASE_MARK(7);      // v loads, Gram epilogue, Y staging
 
     // ---- 5. Akk = (I + L)^-1: 16x16 diagonal blocks by substitution (64 threads; the others clear the
     //         blocks above the diagonal), then 16->32->64 block merges X = -D2inv (C D1inv) as split-TF32
@@ -552,6 +709,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
     }
     __syncthreads();
+    PHASE_MARK(8);      // triangular inverse
     {   // Akk -> fp16 K-major operand (and fp32 to HBM when the backward pass wants it)
         constexpr int CPT = 4096 / INTRA_THREADS;              // columns per thread: 16 or 8
         const int row = tid / (64 / CPT), c0 = (tid % (64 / CPT)) * CPT;
@@ -571,7 +729,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             *reinterpret_cast<uint4*>(dstk + 8192) = pk;        // rows 64..127 of the A operand repeat Akk
         }
         if (p.akk_out) {
-            float* ao = p.akk_out + ((size_t)c * p.H + h) * BT * BT + row * BT + c0;
+            float* ao = p.akk_out + (size_t)tile_id * BT * BT + row * BT + c0;
 #pragma unroll
             for (int q4 = 0; q4 < CPT / 4; ++q4)
                 *reinterpret_cast<float4*>(ao + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
@@ -581,21 +739,26 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     umma::fence_before_sync();
     __syncthreads();
 
-    // ---- 6. [w | u] = Akk [X | Y]: one M=128 x N=256 x K=64 product. A = Akk stacked twice (K-major), so TMEM
-    //         lanes 0..63 and 64..127 both hold the 64 token rows; B = [X | Y] as four MN-major 64-channel atoms ----
+    // ---- 6. [w | u] = Akk [X | Y]: two M=128 x N=128 x K=64 products into TMEM columns 0..127 (w) and 128..255 (u).
+    //         A = Akk stacked twice (K-major), so TMEM lanes 0..63 and 64..127 both hold the 64 token rows;
+    //         B = X, then Y, each as two MN-major 64-channel atoms ----
     if (tid == 0) {
         umma::fence_after_sync();
-        const uint32_t idesc = umma::make_idesc(umma::FMT_F16, 128, 256, false, true);
+        const uint32_t idesc = umma::make_idesc(umma::FMT_F16, 128, 128, false, true);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t ad = sdesc_sw128(sm_u32 + SM_AKK16 + ks * 32, 16, 1024);
-            const uint64_t bd = sdesc_sw128(sm_u32 + SM_XS + ks * 2048, 8192, 1024);
-            umma::mma_f16(tmem, ad, bd, idesc, ks != 0);
+        for (int part = 0; part < 2; ++part) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint64_t ad = sdesc_sw128(sm_u32 + SM_AKK16 + ks * 32, 16, 1024);
+                const uint64_t bd = sdesc_sw128(sm_u32 + (part ? SM_YS : SM_XS) + ks * 2048, 8192, 1024);
+                umma::mma_f16(tmem + 128 * part, ad, bd, idesc, ks != 0);
+            }
         }
         umma::commit(&bars[2]);
     }
-    if (!mbar_wait(&bars[2], par)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
-    umma::fence_after_sync();
+    PHASE_MARK(9);      // Akk pack + W/U MMA issue
+    if (!wait_mma(2, par)) break;
+    PHASE_MARK(10);     // W/U MMA wait
 
     // ---- 7. epilogue: lane = token, columns = channels; lanes 0..63 write w, the duplicate lanes 64..127 write u;
     //         each thread converts 64/(NWARPS/8) channels to fp16 and stores 16 bytes at a time ----
@@ -630,6 +793,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     umma::fence_before_sync();
     __syncthreads();      // TMEM columns and shared memory are free for the next tile
     umma::fence_after_sync();
+    PHASE_MARK(11);     // W/U epilogue
     }  // tile loop
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
 }
