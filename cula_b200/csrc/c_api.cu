@@ -39,9 +39,10 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
     if (gate_mode < 0 || gate_mode > 2 || (gate_mode != 0 && !d_A_log)) return CULA_KDA_EINVAL;
     if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
     if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
-    if (misaligned(d_q) || misaligned(d_k) || misaligned(d_v) || misaligned(d_g) || misaligned(d_tiles) ||
-        misaligned(d_akk) || misaligned(d_mkk))
+    if (misaligned(d_q) || misaligned(d_k) || misaligned(d_v) || misaligned(d_tiles) || misaligned(d_akk) || misaligned(d_mkk) ||
+        (!(g_is_fp32 & CULA_KDA_G_PER_HEAD) && misaligned(d_g)))
         return CULA_KDA_EALIGN;
+    if (g_is_fp32 & ~(CULA_KDA_G_FP32 | CULA_KDA_G_PER_HEAD)) return CULA_KDA_EINVAL;
     kda::IntraParams p{};
     p.q = d_q; p.k = d_k; p.v = d_v; p.g = d_g; p.beta = d_beta;
     p.A_log = d_A_log; p.dt_bias = d_dt_bias;
@@ -50,7 +51,8 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
     p.akk_out = d_akk;
     p.mkk_out = d_mkk;
     p.status = d_status;
-    p.T = T; p.H = H; p.g_fp32 = g_is_fp32; p.beta_fp32 = beta_is_fp32;
+    p.T = T; p.H = H; p.g_fp32 = g_is_fp32 & CULA_KDA_G_FP32; p.g_per_head = (g_is_fp32 & CULA_KDA_G_PER_HEAD) != 0;
+    p.beta_fp32 = beta_is_fp32;
     p.use_l2norm = use_qk_l2norm; p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
     return kda_launch_fwd_intra(&p, num_chunks, static_cast<cudaStream_t>(stream));
 }
@@ -217,15 +219,17 @@ extern "C" int cula_kda_bwd_gated(const void* d_q, const void* d_k, const void* 
     if (gate_mode < 0 || gate_mode > 2 || (gate_mode != 0 && !d_A_log)) return CULA_KDA_EINVAL;
     if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
     if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
-    if (misaligned(d_q) || misaligned(d_k) || misaligned(d_g) || misaligned(d_akk) || misaligned(d_mkk) ||
-        misaligned(d_scratch) || misaligned(d_dq) || misaligned(d_dk) || misaligned(d_dg))
+    const bool per_head = (g_is_fp32 & CULA_KDA_G_PER_HEAD) != 0;
+    if (g_is_fp32 & ~(CULA_KDA_G_FP32 | CULA_KDA_G_PER_HEAD)) return CULA_KDA_EINVAL;
+    if (misaligned(d_q) || misaligned(d_k) || misaligned(d_akk) || misaligned(d_mkk) || misaligned(d_scratch) || misaligned(d_dq) ||
+        misaligned(d_dk) || (!per_head && (misaligned(d_g) || misaligned(d_dg))))
         return CULA_KDA_EALIGN;
     kda::BwdGatedParams p{};
     p.q = d_q; p.k = d_k; p.g = d_g; p.beta = d_beta; p.A_log = d_A_log; p.dt_bias = d_dt_bias; p.akk = d_akk;
     p.mkk = d_mkk; p.scratch = d_scratch; p.gscale = d_gscale; p.dq = d_dq; p.dk = d_dk; p.dg = d_dg; p.dbeta = d_dbeta;
     p.dA_log = d_dA_log; p.ddt_bias = d_ddt_bias; p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices;
-    p.T = T; p.H = H; p.g_fp32 = g_is_fp32; p.beta_fp32 = beta_is_fp32; p.use_l2norm = use_qk_l2norm;
-    p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
+    p.T = T; p.H = H; p.g_fp32 = g_is_fp32 & CULA_KDA_G_FP32; p.g_per_head = per_head; p.beta_fp32 = beta_is_fp32;
+    p.use_l2norm = use_qk_l2norm; p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
     return kda_launch_bwd_gated(&p, num_chunks, static_cast<cudaStream_t>(stream));
 }
 

@@ -127,7 +127,13 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
 #pragma unroll
         for (int e = 0; e < 8; ++e) gv[e] = 0.f;
         if (row < ci.valid) {
-            if (p.g_fp32) {
+            if (p.g_per_head) {        // one gate per (token, head), shared by all channels
+                const size_t gi = (size_t)(ci.row0 + row) * p.H + h;
+                const float gs = p.g_fp32 ? reinterpret_cast<const float*>(p.g)[gi]
+                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.g)[gi]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) gv[e] = gs;
+            } else if (p.g_fp32) {
                 const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
                 const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
                 gv[0] = lo.x; gv[1] = lo.y; gv[2] = lo.z; gv[3] = lo.w; gv[4] = hi.x; gv[5] = hi.y; gv[6] = hi.z; gv[7] = hi.w;
@@ -428,6 +434,8 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
                     const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(part ? p.k : p.q) + o;
                     prefetch_l2(src);
                     prefetch_l2(src + 64);
+                } else if (p.g_per_head) {
+                    // a few bytes per row: no hint
                 } else if (p.g_fp32) {
                     const float* src = reinterpret_cast<const float*>(p.g) + o + 64 * (part - 2);
                     prefetch_l2(src);
@@ -572,10 +580,16 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
 #pragma unroll
         for (int n = 0; n < 64 / BG_PASS_ROWS; ++n) {
             const int row = (tid >> 4) + BG_PASS_ROWS * n;
-            if (row >= ci.valid) continue;
+            if (row >= ci.valid) continue;       // uniform over the 16 lanes that share a row
             const size_t off = base + (size_t)row * tok_stride + 4 * pc;
             float gv[8], dx[8];
-            if (p.g_fp32) {
+            if (p.g_per_head) {
+                const size_t gi = (size_t)(ci.row0 + row) * p.H + h;
+                const float gs = p.g_fp32 ? reinterpret_cast<const float*>(p.g)[gi]
+                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.g)[gi]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) gv[e] = gs;
+            } else if (p.g_fp32) {
                 const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
                 const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
                 gv[0] = lo.x; gv[1] = lo.y; gv[2] = lo.z; gv[3] = lo.w; gv[4] = hi.x; gv[5] = hi.y; gv[6] = hi.z; gv[7] = hi.w;
@@ -609,7 +623,17 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
                 }
                 dx[e] = v;
             }
-            if (p.g_fp32) {
+            if (p.g_per_head) {        // the gate is shared by the 128 channels: its gradient is their sum
+                float sum = ((dx[0] + dx[1]) + (dx[2] + dx[3])) + ((dx[4] + dx[5]) + (dx[6] + dx[7]));
+                const unsigned half_mask = lane < 16 ? 0x0000ffffu : 0xffff0000u;     // the other half may hold a padding row
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) sum += __shfl_xor_sync(half_mask, sum, o);
+                if (pc == 0) {
+                    const size_t gi = (size_t)(ci.row0 + row) * p.H + h;
+                    if (p.g_fp32) reinterpret_cast<float*>(p.dg)[gi] = sum;
+                    else reinterpret_cast<__nv_bfloat16*>(p.dg)[gi] = __float2bfloat16_rn(sum);
+                }
+            } else if (p.g_fp32) {
                 *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dg) + off) = make_float4(dx[0], dx[1], dx[2], dx[3]);
                 *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dg) + off + 64) = make_float4(dx[4], dx[5], dx[6], dx[7]);
             } else {

@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     // real row of the chunk instead, and is zeroed where it is used (through its gate, norm and beta factors).
     uint2 qraw[4][2], kraw[4][2], graw[4][2];     // [row j][half]: 4 bf16 each; fp32 gates are loaded in place instead
     auto fetch_g = [&](const int4 nf) {
-        if (p.g_fp32) return;
+        if (p.g_fp32 || p.g_per_head) return;
         const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.g) + (size_t)nf.x * tok_stride + (size_t)nf.z * DK + 4 * cq;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -312,6 +312,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 if (part < 2) {
                     prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.q) + nb);
                     prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.k) + nb);
+                } else if (p.g_per_head) {
+                    // a few bytes per row: not worth a hint
                 } else if (p.g_fp32) {
                     prefetch_l2(reinterpret_cast<const float*>(p.g) + nb);
                     prefetch_l2(reinterpret_cast<const float*>(p.g) + nb + 32);
@@ -338,7 +340,15 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         for (int j = 0; j < 4; ++j) {
             const bool live = row0 + j < ci.valid;
             float2 gv[4];
-            if (p.g_fp32) {
+            if (p.g_per_head) {        // one gate per (token, head): every channel gets the same value
+                float gs = 0.f;
+                if (live) {
+                    const size_t gi = (size_t)(ci.row0 + row0 + j) * p.H + h;
+                    gs = p.g_fp32 ? reinterpret_cast<const float*>(p.g)[gi]
+                                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.g)[gi]);
+                }
+                gv[0] = gv[1] = gv[2] = gv[3] = make_float2(gs, gs);
+            } else if (p.g_fp32) {
                 float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
                 if (live) {
                     const float* gp = reinterpret_cast<const float*>(p.g) + base + (size_t)(row0 + j) * tok_stride + 4 * cq;

@@ -15,7 +15,7 @@ struct IntraParams {
     const void* q;            // [B*T, H, 128] bf16
     const void* k;            // [B*T, H, 128] bf16
     const void* v;            // [B*T, H, 128] bf16
-    const void* g;            // [B*T, H, 128] bf16 or fp32
+    const void* g;            // [B*T, H, 128] bf16 or fp32 ([B*T, H] when g_per_head)
     const void* beta;         // [B*T, H] bf16 or fp32
     const float* A_log;       // [H] or null
     const float* dt_bias;     // [H*128] or null
@@ -29,6 +29,7 @@ struct IntraParams {
     int H;
     int num_tiles;            // num_chunks * H (filled in by the launcher)
     int g_fp32;
+    int g_per_head;           // 1: g is [B*T, H], one gate per (token, head) shared by all 128 channels (scalar-gate variant)
     int beta_fp32;
     int use_l2norm;
     int gate_mode;
@@ -122,6 +123,7 @@ struct BwdGatedParams {
     int T;
     int H;
     int g_fp32;
+    int g_per_head;               // 1: g and dg are [B*T, H] (one gate per token and head)
     int beta_fp32;
     int use_l2norm;
     int gate_mode;

@@ -76,6 +76,12 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+def _g_flags(g):
+    """Element type and layout bits of the gate tensor (CULA_KDA_G_FP32, CULA_KDA_G_PER_HEAD): a 3-D ``g`` is one
+    gate per (token, head), the scalar-gate variant."""
+    return int(g.dtype == torch.float32) | (2 if g.dim() == 3 else 0)
+
+
 def _gate_mode(use_gate_in_kernel, safe_gate, lower_bound):
     if not use_gate_in_kernel:
         return GATE_NONE
@@ -114,7 +120,7 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     mkk = torch.empty(num_chunks * H, CHUNK, CHUNK, dtype=torch.float32, device=dev) if store_for_backward else None
     gate_mode = _gate_mode(use_gate_in_kernel, safe_gate, lower_bound)
     _native.check(lib.cula_kda_fwd_intra(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32),
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), _g_flags(g),
         beta.data_ptr(), int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias),
         cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
         float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), _ptr(mkk), _status_word(dev).data_ptr(), stream),
@@ -190,7 +196,7 @@ def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, c
     dA = torch.zeros(H, dtype=torch.float32, device=dev) if use_gate_in_kernel else None
     dbias = torch.zeros(H * K, dtype=torch.float32, device=dev) if (use_gate_in_kernel and dt_bias is not None) else None
     _native.check(lib.cula_kda_bwd_gated(
-        q.data_ptr(), k.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32), beta.data_ptr(),
+        q.data_ptr(), k.data_ptr(), g.data_ptr(), _g_flags(g), beta.data_ptr(),
         int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias), saved["akk"].data_ptr(), saved["mkk"].data_ptr(),
         scratch.data_ptr(), work.data_ptr(), dq.data_ptr(), dk.data_ptr(), dg.data_ptr(), dbeta.data_ptr(), _ptr(dA),
         _ptr(dbias), cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,

@@ -27,6 +27,11 @@ extern "C" {
 
 #define CULA_KDA_NOALLOC_MAX_TILES 256   /* capacity of cula_kda_fwd_noalloc: num_chunks * H */
 
+/* bits of the g_is_fp32 argument: element type and layout of the gate tensor (and of its gradient) */
+#define CULA_KDA_G_FP32 1       /* fp32 elements (bf16 otherwise) */
+#define CULA_KDA_G_PER_HEAD 2   /* [B*T, H]: one gate per (token, head) shared by all 128 key channels -- the scalar-gate
+                                   (gated delta rule, "GDN") variant of the same pipeline; [B*T, H, 128] otherwise */
+
 #define CULA_KDA_GATE_NONE 0         /* g already holds the natural-log decay (use_gate_in_kernel=False) */
 #define CULA_KDA_GATE_SOFTPLUS 1     /* a = -exp(A_log[h]) * softplus(g + dt_bias[h,:]) */
 #define CULA_KDA_GATE_LOWER_BOUND 2  /* a = lower_bound * sigmoid(exp(A_log[h]) * (g + dt_bias[h,:])) (safe_gate) */

@@ -14,6 +14,9 @@ GOLDEN_CASES = ["strong_gate_T130", "weak_gate_T200_h0", "softplus_gate_T96", "p
                 "varlen_15_70_64_37", "uniform_qkv_masked_gate_T150"]
 
 
+GDN_GOLDEN_CASES = ["gdn_pre_gated_T150_h0", "gdn_gate_in_kernel_varlen_40_100_65"]
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
 

@@ -33,6 +33,14 @@ CASES = [
 ]
 
 
+# Scalar-gate variant (gated delta rule): name, B, T, H, use_l2norm, use_gate_in_kernel, h0_std, seq lens or None.
+# Oracle: fla.ops.gated_delta_rule.naive.naive_recurrent_gated_delta_rule and fla.ops.gated_delta_rule.gate.naive_gdn_gate.
+GDN_CASES = [
+    ("gdn_pre_gated_T150_h0", 1, 150, 2, True, False, 0.5, None),
+    ("gdn_gate_in_kernel_varlen_40_100_65", 1, 205, 2, False, True, 0.5, [40, 100, 65]),
+]
+
+
 def bits(x):
     return x.view(torch.int16).numpy().view(np.uint16) if x.dtype == torch.bfloat16 else x.numpy()
 
@@ -113,5 +121,58 @@ def main():
         print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB", file=sys.stderr)
 
 
+def main_gdn():
+    from fla.ops.gated_delta_rule.gate import naive_gdn_gate
+    from fla.ops.gated_delta_rule.naive import naive_recurrent_gated_delta_rule
+
+    K = V = 128
+    for ci, (name, B, T, H, l2, gate_in, h0_std, lens) in enumerate(GDN_CASES):
+        gen = torch.Generator().manual_seed(2000 + ci)
+        rn = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float32)
+        q, k, v = (rn(B, T, H, K).to(torch.bfloat16) for _ in range(3))
+        if not l2:
+            q, k = (F.normalize(x.float(), p=2, dim=-1).to(torch.bfloat16) for x in (q, k))
+        if gate_in:
+            g = (-2.0 + rn(B, T, H)).to(torch.bfloat16)
+            A_log, dt_bias = 0.3 * rn(H), 0.2 * rn(H)
+        else:
+            g = F.logsigmoid(rn(B, T, H)) / 4.0            # fp32 log decay
+            A_log = dt_bias = None
+        beta = torch.sigmoid(rn(B, T, H)).to(torch.bfloat16)
+        N = B if lens is None else len(lens)
+        h0 = h0_std * rn(N, H, K, V)
+        do = rn(B, T, H, V).to(torch.bfloat16)
+        dht = 0.3 * rn(N, H, K, V)
+        leaves = dict(q=q, k=k, v=v, g=g, beta=beta, h0=h0)
+        if gate_in:
+            leaves.update(A_log=A_log, dt_bias=dt_bias)
+        req = {n: t.clone().float().requires_grad_(True) for n, t in leaves.items()}
+        qn = F.normalize(req["q"], p=2, dim=-1) if l2 else req["q"]
+        kn = F.normalize(req["k"], p=2, dim=-1) if l2 else req["k"]
+        a = naive_gdn_gate(req["g"], req["A_log"], req["dt_bias"]) if gate_in else req["g"]
+        bounds = [0, T] if lens is None else np.concatenate([[0], np.cumsum(lens)]).tolist()
+        os_, hs_ = [], []
+        for n in range(len(bounds) - 1):
+            s, e = bounds[n], bounds[n + 1]
+            h_in = req["h0"] if lens is None else req["h0"][n:n + 1]
+            o_n, h_n = naive_recurrent_gated_delta_rule(qn[:, s:e], kn[:, s:e], req["v"][:, s:e], req["beta"][:, s:e], a[:, s:e],
+                                                        initial_state=h_in, output_final_state=True)
+            os_.append(o_n)
+            hs_.append(h_n)
+        o, ht = torch.cat(os_, 1), torch.cat(hs_, 0)
+        ((o * do.float()).sum() + (ht * dht).sum()).backward()
+        out = dict(B=B, T=T, H=H, use_l2norm=l2, use_gate_in_kernel=gate_in, safe_gate=False, lower_bound=np.float32(np.nan),
+                   cu_seqlens=np.asarray(bounds if lens is not None else [], dtype=np.int32),
+                   do=bits(do), dht=dht.numpy(), o=o.detach().numpy(), ht=ht.detach().numpy())
+        for n, t in leaves.items():
+            out["in_" + n] = bits(t)
+            out["in_" + n + "_is_bf16"] = t.dtype == torch.bfloat16
+            out["d" + n] = req[n].grad.numpy()
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **out)
+        print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB", file=sys.stderr)
+
+
 if __name__ == "__main__":
     main()
+    main_gdn()

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN_CASES, load_golden
+from conftest import GDN_GOLDEN_CASES, GOLDEN_CASES, load_golden
 from oracle import c_oracle
 from oracle.naive_kda import chunk_kda_oracle, err_ratio, kda_gate
 
@@ -55,3 +55,35 @@ def test_gate_forms():
 
 def test_c_oracle_thread_count():
     assert c_oracle.num_threads() >= 1
+
+
+@pytest.mark.parametrize("name", GDN_GOLDEN_CASES)
+def test_scalar_gate_oracle_matches_golden(name):
+    """The gated-delta-rule restatement against outputs and gradients of the third-party naive function."""
+    from oracle.naive_gdn import chunk_gdn_oracle
+    case, inp, exp = load_golden(name)
+    leaves = {n: inp[n].float().requires_grad_(True) for n in ("q", "k", "v", "g", "beta", "A_log", "dt_bias", "h0") if n in inp}
+    o, ht = chunk_gdn_oracle(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], initial_state=leaves["h0"],
+                             output_final_state=True, use_qk_l2norm_in_kernel=case["use_l2norm"],
+                             cu_seqlens=case["cu_seqlens"], use_gate_in_kernel=case["use_gate_in_kernel"],
+                             A_log=leaves.get("A_log"), dt_bias=leaves.get("dt_bias"))
+    ((o * inp["do"].float()).sum() + (ht * inp["dht"]).sum()).backward()
+    assert err_ratio(exp["o"], o.detach()) < 1e-6 and err_ratio(exp["ht"], ht.detach()) < 1e-6
+    for n, t in leaves.items():
+        assert err_ratio(exp["d" + n], t.grad) < 2e-6, n
+
+
+def test_scalar_gate_is_the_per_channel_recurrence_with_equal_gates():
+    """The kernels run the scalar-gate variant as KDA with one gate value for all channels: the two oracles agree."""
+    from oracle.naive_gdn import naive_recurrent_gdn
+    from oracle.naive_kda import naive_recurrent_kda
+    gen = torch.Generator().manual_seed(0)
+    B, T, H = 2, 40, 2
+    q, k, v = (torch.randn(B, T, H, 128, generator=gen) for _ in range(3))
+    k = torch.nn.functional.normalize(k, dim=-1)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=gen))
+    beta = torch.rand(B, T, H, generator=gen)
+    h0 = torch.randn(B, H, 128, 128, generator=gen)
+    o1, s1 = naive_recurrent_gdn(q, k, v, g, beta, None, h0, True)
+    o2, s2 = naive_recurrent_kda(q, k, v, g[..., None].expand(B, T, H, 128), beta, None, h0, True)
+    assert err_ratio(o1, o2) < 1e-6 and err_ratio(s1, s2) < 1e-6
