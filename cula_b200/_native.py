@@ -34,6 +34,10 @@ SIGNATURES = {
     "cula_kda_noalloc_max_tiles": (_i, []),
     "cula_kda_fwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _fp, _fp, _fp, _vp, _fp, _ip, _ip, _ip,
                                   _i, _i, _i, _i, _f, _i, _i, _f, _ip, _vp]),
+    "cula_kda_gate_fwd": (_i, [_vp, _i, _fp, _fp, _vp, _i, ctypes.c_longlong, _i, _i, _i, _f, _vp]),
+    "cula_kda_gate_bwd": (_i, [_vp, _i, _fp, _fp, _vp, _i, _vp, _fp, _fp, ctypes.c_longlong, _i, _i, _i, _f, _vp]),
+    "cula_kda_beta_sigmoid_fwd": (_i, [_vp, _i, _fp, ctypes.c_longlong, _vp]),
+    "cula_kda_beta_sigmoid_bwd": (_i, [_vp, _i, _fp, _vp, ctypes.c_longlong, _vp]),
     "cula_kda_selftest_bounded_wait": (_i, [_ip, _i, _vp]),
     "cula_kda_strerror": (ctypes.c_char_p, [_i]),
 }

@@ -52,7 +52,7 @@ extern "C" int cula_kda_fwd_intra(const void* d_q, const void* d_k, const void* 
     p.mkk_out = d_mkk;
     p.status = d_status;
     p.T = T; p.H = H; p.g_fp32 = g_is_fp32 & CULA_KDA_G_FP32; p.g_per_head = (g_is_fp32 & CULA_KDA_G_PER_HEAD) != 0;
-    p.beta_fp32 = beta_is_fp32;
+    p.beta_fp32 = beta_is_fp32 & CULA_KDA_BETA_FP32; p.beta_logit = (beta_is_fp32 & CULA_KDA_BETA_LOGIT) != 0;
     p.use_l2norm = use_qk_l2norm; p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
     return kda_launch_fwd_intra(&p, num_chunks, static_cast<cudaStream_t>(stream));
 }
@@ -202,7 +202,8 @@ extern "C" int cula_kda_bwd_dense(const float* d_h32, const float* d_ds, const v
     kda::BwdDenseParams p{};
     p.h32 = d_h32; p.ds = d_ds; p.vnew = d_vnew; p.dvn = d_dvn; p.d_o = d_do; p.v = d_v; p.beta = d_beta;
     p.akk = d_akk; p.gscale = d_gscale; p.dv = d_dv; p.scratch = d_scratch;
-    p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices; p.T = T; p.H = H; p.beta_fp32 = beta_is_fp32;
+    p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices; p.T = T; p.H = H;
+    p.beta_fp32 = beta_is_fp32 & CULA_KDA_BETA_FP32; p.beta_logit = (beta_is_fp32 & CULA_KDA_BETA_LOGIT) != 0;
     return kda_launch_bwd_dense(&p, num_chunks, static_cast<cudaStream_t>(stream));
 }
 
@@ -228,9 +229,45 @@ extern "C" int cula_kda_bwd_gated(const void* d_q, const void* d_k, const void* 
     p.q = d_q; p.k = d_k; p.g = d_g; p.beta = d_beta; p.A_log = d_A_log; p.dt_bias = d_dt_bias; p.akk = d_akk;
     p.mkk = d_mkk; p.scratch = d_scratch; p.gscale = d_gscale; p.dq = d_dq; p.dk = d_dk; p.dg = d_dg; p.dbeta = d_dbeta;
     p.dA_log = d_dA_log; p.ddt_bias = d_ddt_bias; p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices;
-    p.T = T; p.H = H; p.g_fp32 = g_is_fp32 & CULA_KDA_G_FP32; p.g_per_head = per_head; p.beta_fp32 = beta_is_fp32;
+    p.T = T; p.H = H; p.g_fp32 = g_is_fp32 & CULA_KDA_G_FP32; p.g_per_head = per_head;
+    p.beta_fp32 = beta_is_fp32 & CULA_KDA_BETA_FP32; p.beta_logit = (beta_is_fp32 & CULA_KDA_BETA_LOGIT) != 0;
     p.use_l2norm = use_qk_l2norm; p.gate_mode = gate_mode; p.lower_bound = lower_bound; p.scale = scale;
     return kda_launch_bwd_gated(&p, num_chunks, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kda_launch_gate(const kda::GateArgs* a, int backward, cudaStream_t stream);
+extern "C" int kda_launch_beta_sigmoid(const void* x, int x_fp32, const float* dy, void* out, long long n, int backward,
+                                       cudaStream_t stream);
+
+extern "C" int cula_kda_gate_fwd(const void* d_g, int g_is_fp32, const float* d_A_log, const float* d_dt_bias, void* d_y,
+                                 int y_is_fp32, long long M, int H, int K, int use_lower_bound, float lower_bound, void* stream) {
+    if (M == 0) return 0;
+    if (!d_g || !d_A_log || !d_y || M < 0 || H <= 0 || K < 32 || K % 8 != 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_g) || misaligned(d_y)) return CULA_KDA_EALIGN;
+    kda::GateArgs a{d_g, d_A_log, d_dt_bias, nullptr, d_y, nullptr, nullptr, M, H, K, g_is_fp32, y_is_fp32, 0, use_lower_bound, lower_bound};
+    return kda_launch_gate(&a, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_gate_bwd(const void* d_g, int g_is_fp32, const float* d_A_log, const float* d_dt_bias, const void* d_dy,
+                                 int dy_is_fp32, void* d_dg, float* d_dA_log, float* d_ddt_bias, long long M, int H, int K,
+                                 int use_lower_bound, float lower_bound, void* stream) {
+    if (M == 0) return 0;
+    if (!d_g || !d_A_log || !d_dy || !d_dg || M < 0 || H <= 0 || K < 32 || K % 8 != 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_g) || misaligned(d_dy) || misaligned(d_dg)) return CULA_KDA_EALIGN;
+    kda::GateArgs a{d_g, d_A_log, d_dt_bias, d_dy, d_dg, d_dA_log, d_ddt_bias, M, H, K, g_is_fp32, 0, dy_is_fp32, use_lower_bound, lower_bound};
+    return kda_launch_gate(&a, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_beta_sigmoid_fwd(const void* d_x, int x_is_fp32, float* d_y, long long n, void* stream) {
+    if (n == 0) return 0;
+    if (!d_x || !d_y || n < 0) return CULA_KDA_EINVAL;
+    return kda_launch_beta_sigmoid(d_x, x_is_fp32, nullptr, d_y, n, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_beta_sigmoid_bwd(const void* d_x, int x_is_fp32, const float* d_dy, void* d_dx, long long n, void* stream) {
+    if (n == 0) return 0;
+    if (!d_x || !d_dy || !d_dx || n < 0) return CULA_KDA_EINVAL;
+    return kda_launch_beta_sigmoid(d_x, x_is_fp32, d_dy, d_dx, n, 1, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kda_launch_selftest_wait(int* status, int limit, cudaStream_t stream);

@@ -74,6 +74,7 @@ __device__ __forceinline__ void bd_tile(const BwdDenseParams& p, float* sm, cons
             size_t bi = (size_t)(ci.row0 + tid) * p.H + h;
             b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
+            if (p.beta_logit) b = __fdividef(1.f, 1.f + __expf(-b));
         }
         sm[BD_BETA + tid] = b;
     }

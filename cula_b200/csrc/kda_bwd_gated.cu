@@ -188,6 +188,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
             size_t bi = (size_t)(ci.row0 + tid) * p.H + h;
             b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
+            if (p.beta_logit) b = __fdividef(1.f, 1.f + __expf(-b));
         }
         sBeta[tid] = b;
         sDbeta[tid] = scr[SCR_DBU + tid];
@@ -708,7 +709,8 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     }
     if (tid < ci.valid) {
         const size_t bi = (size_t)(ci.row0 + tid) * p.H + h;
-        const float v = sDbeta[tid] * gs_inv;
+        float v = sDbeta[tid] * gs_inv;
+        if (p.beta_logit) v *= sBeta[tid] * (1.f - sBeta[tid]);       // chain rule through the in-kernel sigmoid
         if (p.beta_fp32) reinterpret_cast<float*>(p.dbeta)[bi] = v;
         else reinterpret_cast<__nv_bfloat16*>(p.dbeta)[bi] = __float2bfloat16_rn(v);
     }

@@ -271,8 +271,12 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             if (p.gate_mode != GATE_NONE) sc_next = __float_as_uint(p.A_log[h2]);
         }
     };
-    auto park_scalars = [&](int buf) {
-        if (tid < BT) sBetaBuf[buf * BT + tid] = p.beta_fp32 ? __uint_as_float(sc_next) : __uint_as_float(sc_next << 16);
+    auto park_scalars = [&](int buf, int valid_rows) {
+        if (tid < BT) {
+            float b = p.beta_fp32 ? __uint_as_float(sc_next) : __uint_as_float(sc_next << 16);
+            if (p.beta_logit) b = (tid < valid_rows) ? __fdividef(1.f, 1.f + __expf(-b)) : 0.f;    // padding rows stay 0
+            sBetaBuf[buf * BT + tid] = b;
+        }
         else if (tid < BT + DK) sBiasBuf[buf * DK + tid - BT] = __uint_as_float(sc_next);
         else if (tid == BT + DK) sAlpha[buf] = p.gate_mode != GATE_NONE ? __expf(__uint_as_float(sc_next)) : 0.f;
     };
@@ -281,7 +285,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     if ((int)blockIdx.x < p.num_tiles) {
         fetch_g(sInfo[0]);
         load_scalars(sInfo[0]);
-        park_scalars(0);
+        park_scalars(0, sInfo[0].y);
     }
     __syncthreads();
 
@@ -654,7 +658,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                 make_uint4(o4[0], o4[1], o4[2], o4[3]);
         }
     }
-    park_scalars(par ^ 1);
+    park_scalars(par ^ 1, sInfo[par ^ 1].y);
     umma::fence_before_sync();
     __syncthreads();
     PHASE_MARK(7);      // v loads, Gram epilogue, Y staging

@@ -86,7 +86,7 @@ extern "C" int cula_kda_fwd_noalloc(const void* d_q, const void* d_k, const void
     kda::IntraParams ip{};
     ip.q = d_q; ip.k = d_k; ip.v = d_v; ip.g = d_g; ip.beta = d_beta; ip.A_log = d_A_log; ip.dt_bias = d_dt_bias;
     ip.cu_seqlens = d_cu_seqlens; ip.chunk_indices = d_chunk_indices; ip.tiles = tiles; ip.akk_out = nullptr;
-    ip.mkk_out = nullptr; ip.status = d_status; ip.T = T; ip.H = H; ip.g_fp32 = g_is_fp32; ip.beta_fp32 = beta_is_fp32;
+    ip.mkk_out = nullptr; ip.status = d_status; ip.T = T; ip.H = H; ip.g_fp32 = g_is_fp32 & 1; ip.g_per_head = (g_is_fp32 >> 1) & 1; ip.beta_fp32 = beta_is_fp32 & 1; ip.beta_logit = (beta_is_fp32 >> 1) & 1;
     ip.use_l2norm = use_qk_l2norm; ip.gate_mode = gate_mode; ip.lower_bound = lower_bound; ip.scale = scale;
     rc = kda_launch_fwd_intra(&ip, num_chunks, s);
     if (rc != 0) return rc;

@@ -31,6 +31,7 @@ struct IntraParams {
     int g_fp32;
     int g_per_head;           // 1: g is [B*T, H], one gate per (token, head) shared by all 128 channels (scalar-gate variant)
     int beta_fp32;
+    int beta_logit;           // 1: beta holds the raw logits; sigmoid is applied in-kernel
     int use_l2norm;
     int gate_mode;
     float lower_bound;
@@ -99,6 +100,7 @@ struct BwdDenseParams {
     int T;
     int H;
     int beta_fp32;
+    int beta_logit;               // 1: beta holds the raw logits
 };
 
 struct BwdGatedParams {
@@ -125,10 +127,27 @@ struct BwdGatedParams {
     int g_fp32;
     int g_per_head;               // 1: g and dg are [B*T, H] (one gate per token and head)
     int beta_fp32;
+    int beta_logit;               // 1: beta holds the raw logits; dbeta is then the gradient w.r.t. the logits
     int use_l2norm;
     int gate_mode;
     float lower_bound;
     float scale;
+};
+
+// stand-alone gate activation (forward and backward)
+struct GateArgs {
+    const void* g;        // [M, H*K] bf16 or fp32
+    const float* A_log;   // [H]
+    const float* dt_bias; // [H*K] or null
+    const void* dy;       // [M, H*K] gradient w.r.t. the output (backward), bf16 or fp32
+    void* out;            // forward: y; backward: dg (dtype of g)
+    float* dA_log;        // [H] (backward, accumulated with atomics; zero it first) or null
+    float* ddt_bias;      // [H*K] (backward, accumulated with atomics) or null
+    long long M;          // tokens
+    int H, K;
+    int g_fp32, out_fp32, dy_fp32;
+    int use_lower_bound;
+    float lower_bound;
 };
 
 }  // namespace kda

@@ -82,6 +82,11 @@ def _g_flags(g):
     return int(g.dtype == torch.float32) | (2 if g.dim() == 3 else 0)
 
 
+def _beta_flags(beta, beta_logit):
+    """Element type bit and logit bit of the beta tensor (CULA_KDA_BETA_FP32, CULA_KDA_BETA_LOGIT)."""
+    return int(beta.dtype == torch.float32) | (2 if beta_logit else 0)
+
+
 def _gate_mode(use_gate_in_kernel, safe_gate, lower_bound):
     if not use_gate_in_kernel:
         return GATE_NONE
@@ -92,7 +97,7 @@ def _gate_mode(use_gate_in_kernel, safe_gate, lower_bound):
 
 def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
                   use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias,
-                  store_states=False, store_akk=False, store_for_backward=False, want_output=True):
+                  store_states=False, store_akk=False, store_for_backward=False, want_output=True, beta_logit=False):
     """Forward orchestration (the role of cula/kda/chunk_fwd.py:39-152): the chunk-parallel stage
     writes one tile pack per (chunk, head); the scan consumes them, carries the fp32 state and
     writes ``o``. Returns a dict with o, final_state and the intermediates kept for backward."""
@@ -121,7 +126,7 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
     gate_mode = _gate_mode(use_gate_in_kernel, safe_gate, lower_bound)
     _native.check(lib.cula_kda_fwd_intra(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), _g_flags(g),
-        beta.data_ptr(), int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias),
+        beta.data_ptr(), _beta_flags(beta, beta_logit), _ptr(A_log), _ptr(dt_bias),
         cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
         float(lower_bound if lower_bound is not None else 0.0), tiles.data_ptr(), _ptr(akk), _ptr(mkk), _status_word(dev).data_ptr(), stream),
         "cula_kda_fwd_intra")
@@ -148,7 +153,8 @@ def chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu
 
 
 def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, cu_seqlens_cpu,
-                  use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias, saved=None):
+                  use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias, saved=None,
+                  beta_logit=False):
     """Backward orchestration (the role of cula/kda/chunk_bwd.py:432-604). ``saved`` holds the forward
     intermediates (tiles, akk, mkk, h32, vnew) when they were kept; otherwise they are recomputed here, as the
     reference does by default (cula/kda/chunk_bwd.py:459-500)."""
@@ -160,7 +166,7 @@ def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, c
     if saved is None:
         saved = chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, False, cu_seqlens, cu_seqlens_cpu,
                               use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound, A_log, dt_bias,
-                              store_for_backward=True, want_output=False)
+                              store_for_backward=True, want_output=False, beta_logit=beta_logit)
     if cu_seqlens is not None:
         tab = get_varlen_tables(cu_seqlens, cu_seqlens_cpu)
         n_seqs, num_chunks = tab.n_seqs, tab.num_chunks
@@ -188,7 +194,7 @@ def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, c
     dv = zeros(v.shape, dtype=v.dtype, device=dev)
     scratch = torch.empty(num_chunks * H, lib.cula_kda_bwd_scratch_floats(), dtype=torch.float32, device=dev)
     _native.check(lib.cula_kda_bwd_dense(saved["h32"].data_ptr(), ds.data_ptr(), saved["vnew"].data_ptr(), dvn.data_ptr(),
-                                         do.data_ptr(), v.data_ptr(), beta.data_ptr(), int(beta.dtype == torch.float32),
+                                         do.data_ptr(), v.data_ptr(), beta.data_ptr(), _beta_flags(beta, beta_logit),
                                          saved["akk"].data_ptr(), work.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
                                          cu_p, ci_p, num_chunks, T, H, stream), "cula_kda_bwd_dense")
     dq, dk = zeros(q.shape, dtype=q.dtype, device=dev), zeros(k.shape, dtype=k.dtype, device=dev)
@@ -197,7 +203,7 @@ def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, c
     dbias = torch.zeros(H * K, dtype=torch.float32, device=dev) if (use_gate_in_kernel and dt_bias is not None) else None
     _native.check(lib.cula_kda_bwd_gated(
         q.data_ptr(), k.data_ptr(), g.data_ptr(), _g_flags(g), beta.data_ptr(),
-        int(beta.dtype == torch.float32), _ptr(A_log), _ptr(dt_bias), saved["akk"].data_ptr(), saved["mkk"].data_ptr(),
+        _beta_flags(beta, beta_logit), _ptr(A_log), _ptr(dt_bias), saved["akk"].data_ptr(), saved["mkk"].data_ptr(),
         scratch.data_ptr(), work.data_ptr(), dq.data_ptr(), dk.data_ptr(), dg.data_ptr(), dbeta.data_ptr(), _ptr(dA),
         _ptr(dbias), cu_p, ci_p, num_chunks, T, H, float(scale), int(use_qk_l2norm_in_kernel), gate_mode,
         float(lower_bound if lower_bound is not None else 0.0), stream), "cula_kda_bwd_gated")
@@ -213,7 +219,7 @@ class ChunkKDAFunction(torch.autograd.Function):
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
                 use_qk_l2norm_in_kernel, use_gate_in_kernel, cu_seqlens, cu_seqlens_cpu, safe_gate, lower_bound,
-                disable_recompute, return_intermediate_states, keep_intermediates):
+                disable_recompute, return_intermediate_states, keep_intermediates, beta_logit=False):
         q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
         if A_log is not None:
             A_log = A_log.float().contiguous()
@@ -226,7 +232,7 @@ class ChunkKDAFunction(torch.autograd.Function):
             out = chunk_kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                                 cu_seqlens_cpu, use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound,
                                 A_log, dt_bias, store_states=return_intermediate_states,
-                                store_for_backward=bool(keep_intermediates))
+                                store_for_backward=bool(keep_intermediates), beta_logit=beta_logit)
             _mirror_status(q.device)
         if return_intermediate_states:
             assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
@@ -246,6 +252,7 @@ class ChunkKDAFunction(torch.autograd.Function):
         ctx.cu_seqlens_cpu = cu_seqlens_cpu
         ctx.scale = scale
         ctx.flags = (use_qk_l2norm_in_kernel, use_gate_in_kernel, safe_gate, lower_bound)
+        ctx.beta_logit = beta_logit
         return out["o"], out["final_state"]
 
     @staticmethod
@@ -256,20 +263,20 @@ class ChunkKDAFunction(torch.autograd.Function):
         with torch.cuda.device(q.device):
             dq, dk, dv, dg, dbeta, dA, dbias, dh0 = chunk_kda_bwd(
                 q, k, v, g, beta, ctx.scale, initial_state, do, dht, cu_seqlens, ctx.cu_seqlens_cpu, l2, gate_in,
-                safe_gate, lower_bound, A_log, dt_bias, saved=ctx.kept)
+                safe_gate, lower_bound, A_log, dt_bias, saved=ctx.kept, beta_logit=ctx.beta_logit)
         if dA is not None and A_log is not None:
             dA = dA.to(A_log.dtype).view_as(A_log)
         if dbias is not None and dt_bias is not None:
             dbias = dbias.to(dt_bias.dtype).view_as(dt_bias)
-        # gradients for: q, k, v, g, beta, A_log, dt_bias, scale, initial_state, then 10 non-tensor arguments
-        return (dq, dk, dv, dg, dbeta, dA, dbias, None, dh0) + (None,) * 10
+        # gradients for: q, k, v, g, beta, A_log, dt_bias, scale, initial_state, then 11 non-tensor arguments
+        return (dq, dk, dv, dg, dbeta, dA, dbias, None, dh0) + (None,) * 11
 
 
 @torch.compiler.disable
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
               use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, cu_seqlens=None, cu_seqlens_cpu=None,
               safe_gate=False, lower_bound=None, disable_recompute=False, return_intermediate_states=False,
-              cp_context=None, **kwargs):
+              cp_context=None, use_beta_sigmoid_in_kernel=False, **kwargs):
     r"""Chunkwise KDA forward (+ autograd backward).
 
     Args mirror ``cula.kda.chunk_kda`` (cula/kda/chunk.py:218-346):
@@ -287,6 +294,9 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         cu_seqlens: int32 ``[N+1]`` for a packed batch (then B must be 1); cu_seqlens_cpu: optional host copy.
         disable_recompute: keep forward intermediates for backward instead of recomputing them.
         return_intermediate_states: inference only; also return h ``[B, NT, H, 128, 128]`` bf16.
+        use_beta_sigmoid_in_kernel: (extension) ``beta`` holds raw logits; ``sigmoid`` is applied in-kernel and the
+            backward pass returns the gradient w.r.t. the logits, so the activated beta never round-trips HBM (the
+            fusion of ``fused_beta_sigmoid`` into the call).
         cp_context: a :class:`cula_b200.kda.cp.KDACPContext` (process group of the context-parallel ranks); the call
             is then this rank's shard of ONE sequence and runs through ``chunk_kda_cp`` (the reference takes
             flash-linear-attention's ``FLACPContext`` here, cula/kda/chunk.py:348-355).
@@ -351,4 +361,5 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         t is not None and t.requires_grad for t in (q, k, v, g, beta, A_log, dt_bias, initial_state))
     return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
                                   use_qk_l2norm_in_kernel, use_gate_in_kernel, cu_seqlens, cu_seqlens_cpu, safe_gate,
-                                  lower_bound, disable_recompute, return_intermediate_states, keep)
+                                  lower_bound, disable_recompute, return_intermediate_states, keep,
+                                  bool(use_beta_sigmoid_in_kernel))

@@ -32,6 +32,11 @@ extern "C" {
 #define CULA_KDA_G_PER_HEAD 2   /* [B*T, H]: one gate per (token, head) shared by all 128 key channels -- the scalar-gate
                                    (gated delta rule, "GDN") variant of the same pipeline; [B*T, H, 128] otherwise */
 
+/* bits of the beta_is_fp32 argument */
+#define CULA_KDA_BETA_FP32 1    /* fp32 elements (bf16 otherwise) */
+#define CULA_KDA_BETA_LOGIT 2   /* beta holds raw logits: sigmoid is applied in-kernel, and the backward pass returns the
+                                   gradient w.r.t. the logits (fuses fused_beta_sigmoid, fla/ops/kda/gate.py:431) */
+
 #define CULA_KDA_GATE_NONE 0         /* g already holds the natural-log decay (use_gate_in_kernel=False) */
 #define CULA_KDA_GATE_SOFTPLUS 1     /* a = -exp(A_log[h]) * softplus(g + dt_bias[h,:]) */
 #define CULA_KDA_GATE_LOWER_BOUND 2  /* a = lower_bound * sigmoid(exp(A_log[h]) * (g + dt_bias[h,:])) (safe_gate) */
@@ -203,6 +208,25 @@ int cula_kda_fwd_noalloc(const void* d_q, const void* d_k, const void* d_v, cons
                          int num_chunks, int N, int T, int H,
                          float scale, int use_qk_l2norm, int gate_mode, float lower_bound,
                          int* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Layer-side elementwise operators next to chunk_kda (for callers that do not let chunk_kda activate the gate itself).
+ * Replace flash-linear-attention's fused_kda_gate (KDAGateFunction, fla/ops/kda/gate.py:282-345; kernels :88-279) and
+ * fused_beta_sigmoid (fla/ops/kda/gate.py:348-432), which callers of the reference use around cula.kda.chunk_kda.
+ * d_g, d_y, d_dy, d_dg: [M, H, K] (M tokens), K a multiple of 8 and >= 32; bf16 or fp32 as flagged.
+ *   use_lower_bound == 0:  y = -exp(A_log[h]) * softplus(g + dt_bias[h,:])
+ *   use_lower_bound != 0:  y = lower_bound * sigmoid(exp(A_log[h]) * (g + dt_bias[h,:]))
+ * Backward writes d_dg in the dtype of g and ACCUMULATES d_dA_log [H] and d_ddt_bias [H*K] (either may be NULL) with
+ * atomics: the caller zeroes them first.
+ * ------------------------------------------------------------------------------------------------------------ */
+int cula_kda_gate_fwd(const void* d_g, int g_is_fp32, const float* d_A_log, const float* d_dt_bias, void* d_y,
+                      int y_is_fp32, long long M, int H, int K, int use_lower_bound, float lower_bound, void* stream);
+int cula_kda_gate_bwd(const void* d_g, int g_is_fp32, const float* d_A_log, const float* d_dt_bias, const void* d_dy,
+                      int dy_is_fp32, void* d_dg, float* d_dA_log, float* d_ddt_bias, long long M, int H, int K,
+                      int use_lower_bound, float lower_bound, void* stream);
+/* y = sigmoid(x) in fp32 over n elements (x bf16 or fp32); backward: dx = dy * y * (1 - y) in the dtype of x. */
+int cula_kda_beta_sigmoid_fwd(const void* d_x, int x_is_fp32, float* d_y, long long n, void* stream);
+int cula_kda_beta_sigmoid_bwd(const void* d_x, int x_is_fp32, const float* d_dy, void* d_dx, long long n, void* stream);
 
 /*
  * Self-test of the bounded waits: launches one warp that waits on a barrier nothing completes; after max_polls

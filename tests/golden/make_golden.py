@@ -173,6 +173,28 @@ def main_gdn():
         print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB", file=sys.stderr)
 
 
+def main_gate():
+    """Stand-alone gate activations: outputs and gradients of the third-party naive_kda_gate /
+    naive_kda_lowerbound_gate (fla/ops/kda/gate.py:26-69) on a small seeded tensor."""
+    from fla.ops.kda.gate import naive_kda_gate, naive_kda_lowerbound_gate
+    gen = torch.Generator().manual_seed(3000)
+    M, H, K = 37, 3, 128
+    g = (2.0 * torch.randn(M, H, K, generator=gen)).to(torch.bfloat16)
+    A_log, dt_bias = 0.5 * torch.randn(H, generator=gen), 0.5 * torch.randn(H * K, generator=gen)
+    dy = torch.randn(M, H, K, generator=gen)
+    out = dict(g=bits(g), A_log=A_log.numpy(), dt_bias=dt_bias.numpy(), dy=dy.numpy())
+    for tag, fn, kw in (("softplus", naive_kda_gate, {}), ("lower_bound", naive_kda_lowerbound_gate, dict(lower_bound=-5.0))):
+        leaves = [t.clone().float().requires_grad_(True) for t in (g, A_log, dt_bias)]
+        y = fn(leaves[0], leaves[1], leaves[2], **kw)
+        (y * dy).sum().backward()
+        out.update({f"{tag}_y": y.detach().numpy(), f"{tag}_dg": leaves[0].grad.numpy(), f"{tag}_dA_log": leaves[1].grad.numpy(),
+                    f"{tag}_ddt_bias": leaves[2].grad.numpy()})
+    path = os.path.join(HERE, "gate_activations.npz")
+    np.savez_compressed(path, **out)
+    print(f"gate_activations: wrote {os.path.getsize(path) / 1024:.0f} KiB", file=sys.stderr)
+
+
 if __name__ == "__main__":
     main()
     main_gdn()
+    main_gate()
