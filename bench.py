@@ -514,6 +514,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _native.lib()                     # fail loudly if the CUDA library is missing
+    # one rank per GPU: keep this rank's threads and its pinned host buffers (allocated below) on the GPU's own
+    # NUMA node, so that the ranks' host<->device copies do not all go through one socket's memory
+    from cula_b200.kda import bind_host_to_gpu
+    host_cpus = bind_host_to_gpu(dev) if world > 1 else sorted(os.sched_getaffinity(0))
 
     B, T, H = WORKLOADS[args.workload]
     inp = make_inputs(B, T, H, seed=rank)          # every rank owns an equally sized shard (weak scaling)
@@ -634,7 +638,7 @@ def main():
         "tflops_frac_of_bf16_peak": tokens / world * H * FLOP_PER_TOKEN_HEAD / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
         "hbm_frac_compulsory": tokens / world * H * BYTES_PER_TOKEN_HEAD / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "host_cores_rank0": len(host_cpus)},
         "gpu_launches": 2 * args.steps,
         "roofline": roofline,
         "cpu_baseline": base,

@@ -38,6 +38,10 @@ SIGNATURES = {
     "cula_kda_gate_bwd": (_i, [_vp, _i, _fp, _fp, _vp, _i, _vp, _fp, _fp, ctypes.c_longlong, _i, _i, _i, _f, _vp]),
     "cula_kda_beta_sigmoid_fwd": (_i, [_vp, _i, _fp, ctypes.c_longlong, _vp]),
     "cula_kda_beta_sigmoid_bwd": (_i, [_vp, _i, _fp, _vp, ctypes.c_longlong, _vp]),
+    "cula_kda_short_conv_fwd": (_i, [_vp, _fp, _fp, _fp, _vp, _fp, _ip, _ip, _i, _i, _i, _i, _i, _vp]),
+    "cula_kda_short_conv_bwd": (_i, [_vp, _fp, _fp, _fp, _vp, _vp, _fp, _fp, _ip, _ip, _i, _i, _i, _i, _i, _vp]),
+    "cula_kda_rms_norm_gated_fwd": (_i, [_vp, _vp, _fp, _vp, _fp, ctypes.c_longlong, _i, _i, _f, _vp]),
+    "cula_kda_rms_norm_gated_bwd": (_i, [_vp, _vp, _fp, _fp, _vp, _vp, _vp, _fp, ctypes.c_longlong, _i, _i, _vp]),
     "cula_kda_selftest_bounded_wait": (_i, [_ip, _i, _vp]),
     "cula_kda_strerror": (ctypes.c_char_p, [_i]),
 }

@@ -270,6 +270,67 @@ extern "C" int cula_kda_beta_sigmoid_bwd(const void* d_x, int x_is_fp32, const f
     return kda_launch_beta_sigmoid(d_x, x_is_fp32, d_dy, d_dx, n, 1, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int kda_launch_short_conv(const kda::ConvArgs* a, int num_chunks, int backward, cudaStream_t stream);
+extern "C" int kda_launch_rms_norm_gated(const kda::NormArgs* a, int backward, cudaStream_t stream);
+
+extern "C" int cula_kda_short_conv_fwd(const void* d_x, const float* d_w, const float* d_bias, const float* d_cache_in, void* d_y,
+                                       float* d_cache_out, const int* d_cu_seqlens, const int* d_chunk_indices,
+                                       int num_chunks, int T, int D, int W, int use_silu, void* stream) {
+    if (num_chunks == 0) return 0;
+    if (!d_x || !d_w || !d_y || num_chunks < 0 || D <= 0 || D % 8 != 0 || W < 1 || W > 4) return CULA_KDA_EINVAL;
+    if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
+    if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_x) || misaligned(d_y)) return CULA_KDA_EALIGN;
+    kda::ConvArgs a{};
+    a.x = static_cast<const __nv_bfloat16*>(d_x); a.w = d_w; a.bias = d_bias; a.cache_in = d_cache_in;
+    a.y = static_cast<__nv_bfloat16*>(d_y); a.cache_out = d_cache_out; a.cu_seqlens = d_cu_seqlens; a.chunk_indices = d_chunk_indices;
+    a.T = T; a.D = D; a.W = W; a.silu = use_silu;
+    return kda_launch_short_conv(&a, num_chunks, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_short_conv_bwd(const void* d_x, const float* d_w, const float* d_bias, const float* d_cache_in,
+                                       const void* d_dy, void* d_dx, float* d_dw, float* d_dbias, const int* d_cu_seqlens,
+                                       const int* d_chunk_indices, int num_chunks, int T, int D, int W, int use_silu, void* stream) {
+    if (num_chunks == 0) return 0;
+    if (!d_x || !d_w || !d_dy || !d_dx || !d_dw || num_chunks < 0 || D <= 0 || D % 8 != 0 || W < 1 || W > 4) return CULA_KDA_EINVAL;
+    if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
+    if (!d_cu_seqlens && T <= 0) return CULA_KDA_EINVAL;
+    if (misaligned(d_x) || misaligned(d_dy) || misaligned(d_dx)) return CULA_KDA_EALIGN;
+    kda::ConvArgs a{};
+    a.x = static_cast<const __nv_bfloat16*>(d_x); a.w = d_w; a.bias = d_bias; a.cache_in = d_cache_in;
+    a.dy = static_cast<const __nv_bfloat16*>(d_dy); a.dx = static_cast<__nv_bfloat16*>(d_dx); a.dw = d_dw; a.dbias = d_dbias;
+    a.cu_seqlens = d_cu_seqlens; a.chunk_indices = d_chunk_indices; a.T = T; a.D = D; a.W = W; a.silu = use_silu;
+    return kda_launch_short_conv(&a, num_chunks, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cula_kda_rms_norm_gated_fwd(const void* d_x, const void* d_g, const float* d_w, void* d_y, float* d_rstd,
+                                           long long R, int D, int use_swish, float eps, void* stream) {
+    if (R == 0) return 0;
+    if (!d_x || !d_g || !d_w || !d_y || !d_rstd || R < 0 || !(D == 128 || D == 256 || D == 512 || D == 1024)) return CULA_KDA_EINVAL;
+    if (misaligned(d_x) || misaligned(d_g) || misaligned(d_y)) return CULA_KDA_EALIGN;
+    kda::NormArgs a{};
+    a.x = static_cast<const __nv_bfloat16*>(d_x); a.g = static_cast<const __nv_bfloat16*>(d_g); a.w = d_w;
+    a.y = static_cast<__nv_bfloat16*>(d_y); a.rstd = d_rstd; a.R = R; a.D = D; a.swish = use_swish; a.eps = eps;
+    const int rc = kda_launch_rms_norm_gated(&a, 0, static_cast<cudaStream_t>(stream));
+    return rc == -1 ? CULA_KDA_EINVAL : rc;
+}
+
+extern "C" int cula_kda_rms_norm_gated_bwd(const void* d_x, const void* d_g, const float* d_w, const float* d_rstd,
+                                           const void* d_dy, void* d_dx, void* d_dg, float* d_dw, long long R, int D,
+                                           int use_swish, void* stream) {
+    if (R == 0) return 0;
+    if (!d_x || !d_g || !d_w || !d_rstd || !d_dy || !d_dx || !d_dg || !d_dw || R < 0 ||
+        !(D == 128 || D == 256 || D == 512 || D == 1024))
+        return CULA_KDA_EINVAL;
+    if (misaligned(d_x) || misaligned(d_g) || misaligned(d_dy) || misaligned(d_dx) || misaligned(d_dg)) return CULA_KDA_EALIGN;
+    kda::NormArgs a{};
+    a.x = static_cast<const __nv_bfloat16*>(d_x); a.g = static_cast<const __nv_bfloat16*>(d_g); a.w = d_w;
+    a.rstd = const_cast<float*>(d_rstd); a.dy = static_cast<const __nv_bfloat16*>(d_dy); a.dx = static_cast<__nv_bfloat16*>(d_dx);
+    a.dg = static_cast<__nv_bfloat16*>(d_dg); a.dw = d_dw; a.R = R; a.D = D; a.swish = use_swish;
+    const int rc = kda_launch_rms_norm_gated(&a, 1, static_cast<cudaStream_t>(stream));
+    return rc == -1 ? CULA_KDA_EINVAL : rc;
+}
+
 extern "C" int kda_launch_selftest_wait(int* status, int limit, cudaStream_t stream);
 
 extern "C" int cula_kda_selftest_bounded_wait(int* d_status, int max_polls, void* stream) {

@@ -116,6 +116,12 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// ---- programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+//      while its predecessor in the stream is still running; it must call pdl_wait() before it touches anything the
+//      predecessor writes. pdl_launch_dependents() in the predecessor lets the dependent grid be scheduled early. ----
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- mbarrier + bulk copy (TMA engine, untiled form) ----
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");

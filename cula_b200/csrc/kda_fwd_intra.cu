@@ -192,6 +192,9 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    // the state scan that follows in the stream may be scheduled as soon as SMs free up, so that its launch and set-up
+    // run under the tail of this kernel; it waits for this whole grid before it reads anything
+    pdl_launch_dependents();
 #ifdef KDA_PHASE_TIMERS
     long long phase_t0_ = clock64();
 #endif

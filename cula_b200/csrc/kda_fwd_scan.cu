@@ -87,6 +87,10 @@ kda_fwd_scan_kernel(const ScanParams p) {
         fence_mbar_init();
     }
     __syncthreads();
+    // Everything this kernel reads (tile packs, initial states) may come from the kernels before it in the stream; with
+    // programmatic stream serialization the CTA can be resident before they have finished, so wait here (a no-op when
+    // the launch does not carry the attribute). Only scheduling, the index arithmetic and the barrier set-up above overlap.
+    pdl_wait();
 
     if (warp == L::CONSUMERS) {
         // ------------------------------- producer warp -------------------------------
@@ -399,6 +403,25 @@ kda_fwd_scan_kernel(const ScanParams p) {
 
 extern "C" int kda_fwd_scan_smem_bytes() { return kda::SCAN_SMEM; }
 
+namespace {
+// Launch with programmatic stream serialization: the grid may be scheduled while the previous kernel of the stream (the
+// chunk-parallel stage) is still draining; every thread calls pdl_wait() before it reads anything.
+template <typename Kernel>
+cudaError_t launch_after_producer(Kernel kernel, dim3 grid, int threads, int smem, cudaStream_t stream, const kda::ScanParams& p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+}  // namespace
+
 extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream) {
     using namespace kda;
     if (p->N <= 0) return 0;
@@ -423,11 +446,13 @@ extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream
         if (both_halves) {
             e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, L2::SMEM);
             if (e != cudaSuccess) return (int)e;
-            kda_fwd_scan_kernel<false, false, 2><<<dim3(1, p->H, p->N), (L2::CONSUMERS + 1) * 32, L2::SMEM, stream>>>(*p);
+            e = launch_after_producer(kda_fwd_scan_kernel<false, false, 2>, dim3(1, p->H, p->N), (L2::CONSUMERS + 1) * 32, L2::SMEM, stream, *p);
+            if (e != cudaSuccess) return (int)e;
         } else {
             e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
             if (e != cudaSuccess) return (int)e;
-            kda_fwd_scan_kernel<false, false><<<grid, SCAN_THREADS, SCAN_SMEM, stream>>>(*p);
+            e = launch_after_producer(kda_fwd_scan_kernel<false, false>, grid, SCAN_THREADS, SCAN_SMEM, stream, *p);
+            if (e != cudaSuccess) return (int)e;
         }
     }
     return (int)cudaGetLastError();

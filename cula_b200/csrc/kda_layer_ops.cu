@@ -1,0 +1,320 @@
+// The two layer operators on either side of chunk_kda in a Kimi-Linear block, as stand-alone streaming kernels:
+//   short causal depthwise convolution + SiLU on the q / k / v projections (kernel width <= 4), forward and backward,
+//   gated RMS norm on the attention output, y = rmsnorm(x) * w * act(g), forward and backward.
+// They replace flash-linear-attention's ShortConvolution / causal_conv1d (fla/modules/convolution.py) and
+// FusedRMSNormGated / rms_norm_gated (fla/modules/fused_norm_gate.py:35-120, 846-869), which the layer that calls the
+// reference's chunk_kda uses (fla/layers/kda.py:147-165, 191, 306). HBM-bound: each element is read and written once
+// (the convolution re-reads a 3-token halo per 64-token chunk).
+#include "kda_common.cuh"
+#include "kda_params.h"
+
+namespace kda {
+
+constexpr int LO_THREADS = 128;
+constexpr int CONV_MAXW = 4;
+
+__device__ __forceinline__ void lo_load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    float2 f;
+    f = unpack_bf16(a.x); v[0] = f.x; v[1] = f.y;
+    f = unpack_bf16(a.y); v[2] = f.x; v[3] = f.y;
+    f = unpack_bf16(a.z); v[4] = f.x; v[5] = f.y;
+    f = unpack_bf16(a.w); v[6] = f.x; v[7] = f.y;
+}
+__device__ __forceinline__ void lo_store8(__nv_bfloat16* p, const float (&v)[8]) {
+    *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Causal depthwise convolution: pre[t, d] = bias[d] + sum_i w[d, i] x[t - (W-1) + i, d],  y = silu(pre) (or pre).
+// Tokens before the start of a sequence come from cache[n, d, :] (the last W inputs of the previous call, newest
+// last) or are zero. One CTA column per 64-token chunk (chunks never straddle sequences: the same tables as the
+// attention kernels), one thread per 8 channels; the thread walks its chunk with a sliding window in registers.
+// ------------------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void conv_load_row(const ConvArgs& a, int seq, int seq_start, int t, int ch, float (&v)[8]) {
+    // token t of the flattened axis, or (t < seq_start) the cached inputs of the previous call, or zero
+    if (t >= seq_start) {
+        lo_load8(a.x + (size_t)t * a.D + ch, v);
+    } else if (a.cache_in && seq_start - t <= a.W) {
+        const float* c = a.cache_in + ((size_t)seq * a.D + ch) * a.W + (a.W - (seq_start - t));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = c[e * a.W];
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    }
+}
+
+template <bool BWD>
+__global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvArgs a) {
+    const int ch = 8 * (blockIdx.x * LO_THREADS + threadIdx.x);
+    if (ch >= a.D) return;
+    const ChunkInfo ci = chunk_info(blockIdx.y, a.cu_seqlens, a.chunk_indices, a.T);
+    const int seq_start = a.cu_seqlens ? a.cu_seqlens[ci.seq] : ci.seq * a.T;
+    const int seq_end = a.cu_seqlens ? a.cu_seqlens[ci.seq + 1] : (ci.seq + 1) * a.T;
+    const int W = a.W, t0 = ci.row0, t1 = ci.row0 + ci.valid;
+    float w[8][CONV_MAXW], b[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+#pragma unroll
+        for (int i = 0; i < CONV_MAXW; ++i) w[e][i] = i < W ? a.w[(size_t)(ch + e) * W + i] : 0.f;   // taps are right-aligned below
+        b[e] = a.bias ? a.bias[ch + e] : 0.f;
+    }
+    // window[k] = x[t - (CONV_MAXW-1) + k]; tap i of a width-W kernel multiplies window[CONV_MAXW - W + i]
+    float win[CONV_MAXW][8];
+#pragma unroll
+    for (int k = 0; k < CONV_MAXW - 1; ++k) conv_load_row(a, ci.seq, seq_start, t0 - (CONV_MAXW - 1) + k, ch, win[k + 1]);
+    if (!BWD) {
+        for (int t = t0; t < t1; ++t) {
+#pragma unroll
+            for (int k = 0; k < CONV_MAXW - 1; ++k)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+            lo_load8(a.x + (size_t)t * a.D + ch, win[CONV_MAXW - 1]);
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float pre = b[e];
+#pragma unroll
+                for (int i = 0; i < CONV_MAXW; ++i)
+                    if (i < W) pre = fmaf(w[e][i], win[CONV_MAXW - W + i][e], pre);
+                o[e] = a.silu ? pre * sigmoid_f(pre) : pre;
+            }
+            lo_store8(a.y + (size_t)t * a.D + ch, o);
+        }
+        if (a.cache_out && t1 == seq_end) {      // the last W inputs of the sequence, newest last, zero-padded on the left
+            float* c = a.cache_out + ((size_t)ci.seq * a.D + ch) * W;
+#pragma unroll
+            for (int i = 0; i < CONV_MAXW; ++i)
+                if (i < W) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) c[e * W + i] = win[CONV_MAXW - W + i][e];
+                }
+        }
+    } else {
+        // walk three tokens past the chunk (inside the sequence): dx[u] = sum_i w[i] dpre[u + (W-1) - i] needs them
+        float dwin[CONV_MAXW][8];       // dwin[k] = dpre[t - (CONV_MAXW-1) + k]
+        float dw_acc[8][CONV_MAXW], db_acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            db_acc[e] = 0.f;
+#pragma unroll
+            for (int i = 0; i < CONV_MAXW; ++i) dw_acc[e][i] = dwin[i][e] = 0.f;
+        }
+        for (int t = t0; t < t1 + (W - 1); ++t) {
+#pragma unroll
+            for (int k = 0; k < CONV_MAXW - 1; ++k)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    win[k][e] = win[k + 1][e];
+                    dwin[k][e] = dwin[k + 1][e];
+                }
+            const bool live = t < seq_end;
+            float dyv[8];
+            if (live) {
+                lo_load8(a.x + (size_t)t * a.D + ch, win[CONV_MAXW - 1]);
+                lo_load8(a.dy + (size_t)t * a.D + ch, dyv);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float dp = 0.f;
+                if (live) {
+                    float pre = b[e];
+#pragma unroll
+                    for (int i = 0; i < CONV_MAXW; ++i)
+                        if (i < W) pre = fmaf(w[e][i], win[CONV_MAXW - W + i][e], pre);
+                    const float s = sigmoid_f(pre);
+                    dp = a.silu ? dyv[e] * s * (1.f + pre * (1.f - s)) : dyv[e];
+                    if (t < t1) {            // parameter gradients: each token counted once, by its own chunk
+                        db_acc[e] += dp;
+#pragma unroll
+                        for (int i = 0; i < CONV_MAXW; ++i)
+                            if (i < W) dw_acc[e][i] = fmaf(dp, win[CONV_MAXW - W + i][e], dw_acc[e][i]);
+                    }
+                }
+                dwin[CONV_MAXW - 1][e] = dp;
+            }
+            const int u = t - (W - 1);
+            if (u >= t0 && u < t1) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int i = 0; i < CONV_MAXW; ++i)
+                        if (i < W) acc = fmaf(w[e][i], dwin[CONV_MAXW - 1 - i][e], acc);     // dpre[u + (W-1) - i] = dpre[t - i]
+                    o[e] = acc;
+                }
+                lo_store8(a.dx + (size_t)u * a.D + ch, o);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+#pragma unroll
+            for (int i = 0; i < CONV_MAXW; ++i)
+                if (i < W) atomicAdd(&a.dw[(size_t)(ch + e) * W + i], dw_acc[e][i]);
+            if (a.dbias) atomicAdd(&a.dbias[ch + e], db_acc[e]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Gated RMS norm over rows of D elements (D a multiple of 256, <= 1024... or 128): one warp per row.
+//   n = x * rstd, rstd = rsqrt(mean(x^2) + eps);  y = n * w * act(g), act = sigmoid or swish.
+// ------------------------------------------------------------------------------------------------------------------
+
+template <int VPL, bool BWD>       // VPL: 8-element vectors per lane (D = 256 * VPL), or D = 128 with half of ... see launcher
+__global__ void __launch_bounds__(LO_THREADS) kda_rms_norm_gated_kernel(const NormArgs a) {
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = (long long)blockIdx.x * (LO_THREADS / 32) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (LO_THREADS / 32);
+    const int per_lane = a.D / 32;                 // 4 (D = 128) or 8 * VPL
+    const bool narrow = per_lane == 4;
+    float wv[VPL][8], dw_acc[VPL][8];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int col = narrow ? 4 * lane + (e & 3) : 256 * v + 8 * lane + e;
+            wv[v][e] = a.w[col];
+            dw_acc[v][e] = 0.f;
+        }
+    for (long long row = warp0; row < a.R; row += nwarps) {
+        const size_t base = (size_t)row * a.D;
+        float xv[VPL][8], gv[VPL][8];
+        if (narrow) {       // 4 elements per lane: the upper half of the 8-wide vectors stays zero
+            const uint2 xr = *reinterpret_cast<const uint2*>(a.x + base + 4 * lane);
+            const uint2 gr = *reinterpret_cast<const uint2*>(a.g + base + 4 * lane);
+            float2 f;
+            f = unpack_bf16(xr.x); xv[0][0] = f.x; xv[0][1] = f.y;
+            f = unpack_bf16(xr.y); xv[0][2] = f.x; xv[0][3] = f.y;
+            f = unpack_bf16(gr.x); gv[0][0] = f.x; gv[0][1] = f.y;
+            f = unpack_bf16(gr.y); gv[0][2] = f.x; gv[0][3] = f.y;
+#pragma unroll
+            for (int e = 4; e < 8; ++e) xv[0][e] = gv[0][e] = 0.f;
+        } else {
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                lo_load8(a.x + base + 256 * v + 8 * lane, xv[v]);
+                lo_load8(a.g + base + 256 * v + 8 * lane, gv[v]);
+            }
+        }
+        float rstd;
+        if (!BWD) {
+            float ss = 0.f;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss = fmaf(xv[v][e], xv[v][e], ss);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            rstd = rsqrtf(ss / (float)a.D + a.eps);
+            if (lane == 0) a.rstd[row] = rstd;
+        } else {
+            rstd = a.rstd[row];
+        }
+        float out[VPL][8];
+        if (!BWD) {
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float s = sigmoid_f(gv[v][e]);
+                    out[v][e] = xv[v][e] * rstd * wv[v][e] * (a.swish ? gv[v][e] * s : s);
+                }
+        } else {
+            float dyv[VPL][8], dn[VPL][8], dgo[VPL][8], dot = 0.f;
+            if (narrow) {
+                const uint2 dr = *reinterpret_cast<const uint2*>(a.dy + base + 4 * lane);
+                float2 f;
+                f = unpack_bf16(dr.x); dyv[0][0] = f.x; dyv[0][1] = f.y;
+                f = unpack_bf16(dr.y); dyv[0][2] = f.x; dyv[0][3] = f.y;
+#pragma unroll
+                for (int e = 4; e < 8; ++e) dyv[0][e] = 0.f;
+            } else {
+#pragma unroll
+                for (int v = 0; v < VPL; ++v) lo_load8(a.dy + base + 256 * v + 8 * lane, dyv[v]);
+            }
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float gg = gv[v][e], s = sigmoid_f(gg), n = xv[v][e] * rstd;
+                    const float act = a.swish ? gg * s : s;
+                    const float dact = a.swish ? s * (1.f + gg * (1.f - s)) : s * (1.f - s);
+                    const float z = n * wv[v][e];
+                    const float dz = dyv[v][e] * act;
+                    dgo[v][e] = dyv[v][e] * z * dact;
+                    dw_acc[v][e] = fmaf(dz, n, dw_acc[v][e]);
+                    dn[v][e] = dz * wv[v][e];
+                    dot = fmaf(dn[v][e], n, dot);
+                }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const float mean_dot = dot / (float)a.D;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) out[v][e] = rstd * (dn[v][e] - xv[v][e] * rstd * mean_dot);
+            if (narrow) {
+                *reinterpret_cast<uint2*>(a.dg + base + 4 * lane) = make_uint2(pack_bf16(dgo[0][0], dgo[0][1]), pack_bf16(dgo[0][2], dgo[0][3]));
+            } else {
+#pragma unroll
+                for (int v = 0; v < VPL; ++v) lo_store8(a.dg + base + 256 * v + 8 * lane, dgo[v]);
+            }
+        }
+        __nv_bfloat16* dst = BWD ? a.dx : a.y;
+        if (narrow) {
+            *reinterpret_cast<uint2*>(dst + base + 4 * lane) = make_uint2(pack_bf16(out[0][0], out[0][1]), pack_bf16(out[0][2], out[0][3]));
+        } else {
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) lo_store8(dst + base + 256 * v + 8 * lane, out[v]);
+        }
+    }
+    if (BWD) {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if (narrow && e >= 4) continue;
+                const int col = narrow ? 4 * lane + e : 256 * v + 8 * lane + e;
+                atomicAdd(&a.dw[col], dw_acc[v][e]);
+            }
+    }
+}
+
+}  // namespace kda
+
+extern "C" int kda_launch_short_conv(const kda::ConvArgs* a, int num_chunks, int backward, cudaStream_t stream) {
+    using namespace kda;
+    if (num_chunks <= 0) return 0;
+    dim3 grid((a->D / 8 + LO_THREADS - 1) / LO_THREADS, num_chunks);
+    if (backward) kda_short_conv_kernel<true><<<grid, LO_THREADS, 0, stream>>>(*a);
+    else kda_short_conv_kernel<false><<<grid, LO_THREADS, 0, stream>>>(*a);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int kda_launch_rms_norm_gated(const kda::NormArgs* a, int backward, cudaStream_t stream) {
+    using namespace kda;
+    if (a->R <= 0) return 0;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long long blocks = (a->R + LO_THREADS / 32 - 1) / (LO_THREADS / 32);
+    const long long cap = (backward ? 4LL : 16LL) * sms;     // backward: fewer, longer-lived CTAs keep the dw atomics few
+    if (blocks > cap) blocks = cap;
+    const int vpl = a->D == 128 ? 1 : a->D / 256;
+#define KDA_NORM_LAUNCH(V)                                                                                        \
+    do {                                                                                                          \
+        if (backward) kda_rms_norm_gated_kernel<V, true><<<(unsigned)blocks, LO_THREADS, 0, stream>>>(*a);          \
+        else kda_rms_norm_gated_kernel<V, false><<<(unsigned)blocks, LO_THREADS, 0, stream>>>(*a);                  \
+    } while (0)
+    if (vpl == 1) KDA_NORM_LAUNCH(1);
+    else if (vpl == 2) KDA_NORM_LAUNCH(2);
+    else if (vpl == 4) KDA_NORM_LAUNCH(4);
+    else return -1;
+#undef KDA_NORM_LAUNCH
+    return (int)cudaGetLastError();
+}

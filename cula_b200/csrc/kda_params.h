@@ -1,5 +1,6 @@
 // Plain launch-parameter structs shared between the C-ABI layer and the kernels.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -132,6 +133,39 @@ struct BwdGatedParams {
     int gate_mode;
     float lower_bound;
     float scale;
+};
+
+// short causal depthwise convolution (forward and backward)
+struct ConvArgs {
+    const __nv_bfloat16* x;       // [Ttot, D]
+    const float* w;               // [D, W]
+    const float* bias;            // [D] or null
+    const float* cache_in;        // [N, D, W] or null
+    __nv_bfloat16* y;             // [Ttot, D]            (forward)
+    float* cache_out;             // [N, D, W] or null    (forward)
+    const __nv_bfloat16* dy;      // [Ttot, D]            (backward)
+    __nv_bfloat16* dx;            // [Ttot, D]            (backward)
+    float* dw;                    // [D, W] accumulated with atomics (backward)
+    float* dbias;                 // [D] accumulated with atomics, or null
+    const int* cu_seqlens;        // [N+1] or null
+    const int* chunk_indices;     // [NT][2] or null
+    int T, D, W, silu;
+};
+
+// gated RMS norm (forward and backward)
+struct NormArgs {
+    const __nv_bfloat16* x;   // [R, D]
+    const __nv_bfloat16* g;   // [R, D]
+    const float* w;           // [D]
+    __nv_bfloat16* y;         // [R, D]          (forward)
+    float* rstd;              // [R]             (forward: written; backward: read)
+    const __nv_bfloat16* dy;  // [R, D]          (backward)
+    __nv_bfloat16* dx;        // [R, D]
+    __nv_bfloat16* dg;        // [R, D]
+    float* dw;                // [D] accumulated with atomics
+    long long R;
+    int D, swish;
+    float eps;
 };
 
 // stand-alone gate activation (forward and backward)

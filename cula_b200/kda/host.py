@@ -19,6 +19,45 @@ from ..utils import CHUNK
 from .chunk import chunk_kda
 
 
+def bind_host_to_gpu(device=None):
+    """Restrict this process to the CPU cores that sit next to ``device`` (same NUMA node / PCIe root) and return them.
+
+    With one process per GPU, host buffers that are allocated and pinned AFTER this call land in the memory of that
+    node (first-touch policy), so each rank's host<->device copies stay on its own socket instead of all ranks sharing
+    one node's memory controllers and inter-socket links. The core list comes from NVML (the ideal CPU affinity of the
+    device), else from the device's ``local_cpulist`` in sysfs; it is intersected with the cores the process may already
+    use, and nothing changes when that would leave no core. Only this process's own affinity mask is touched."""
+    import os
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    allowed = os.sched_getaffinity(0)
+    cpus = set()
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        props = torch.cuda.get_device_properties(dev)
+        bus_id = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+        words = (max(allowed) // 64) + 1
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1}
+    except Exception:
+        cpus = set()
+    if not cpus:
+        try:
+            props = torch.cuda.get_device_properties(dev)
+            path = f"/sys/bus/pci/devices/{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0/local_cpulist"
+            for part in open(path).read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        except Exception:
+            cpus = set()
+    chosen = cpus & allowed
+    if chosen and chosen != allowed:
+        os.sched_setaffinity(0, chosen)
+        return sorted(chosen)
+    return sorted(allowed)
+
+
 _STREAMS: dict = {}     # device -> (upload stream, download stream), created once: stream creation costs ~10 us each
 _BUFFERS: dict = {}     # (device, shapes, dtypes) -> the two device-side segment buffer sets
 

@@ -228,6 +228,34 @@ int cula_kda_gate_bwd(const void* d_g, int g_is_fp32, const float* d_A_log, cons
 int cula_kda_beta_sigmoid_fwd(const void* d_x, int x_is_fp32, float* d_y, long long n, void* stream);
 int cula_kda_beta_sigmoid_bwd(const void* d_x, int x_is_fp32, const float* d_dy, void* d_dx, long long n, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * The two layer operators on either side of chunk_kda in a Kimi-Linear block (fla/layers/kda.py:147-165, 191, 306).
+ *
+ * Short causal depthwise convolution (+ SiLU) of the q / k / v projections; replaces ShortConvolution / causal_conv1d
+ * (fla/modules/convolution.py: causal_conv1d(x, weight, bias, residual, initial_state, output_final_state,
+ * activation, cu_seqlens, ...)). d_x, d_y, d_dy, d_dx: [tokens, D] bf16 (D % 8 == 0); d_w [D, W] fp32, W <= 4, tap
+ * W-1 multiplies the current token; d_bias [D] or NULL; d_cache_in / d_cache_out [N, D, W] fp32 or NULL: the last W
+ * inputs of every sequence, newest last (what a decode step continues from). Same packed-batch tables as the
+ * attention kernels (NULL, NULL for a fixed-length batch of sequences of T tokens); num_chunks as there.
+ * Backward ACCUMULATES d_dw [D, W] and d_dbias [D] (may be NULL) with atomics: the caller zeroes them.
+ *
+ * Gated RMS norm of the attention output; replaces FusedRMSNormGated / rms_norm_gated
+ * (fla/modules/fused_norm_gate.py:846-869): y = x * rsqrt(mean(x^2) + eps) * w * act(g), act = sigmoid
+ * (use_swish == 0) or g * sigmoid(g). Rows of D in {128, 256, 512, 1024} bf16; d_rstd [R] fp32 is written by the
+ * forward pass and read by the backward pass, which ACCUMULATES d_dw [D] with atomics.
+ * ------------------------------------------------------------------------------------------------------------ */
+int cula_kda_short_conv_fwd(const void* d_x, const float* d_w, const float* d_bias, const float* d_cache_in, void* d_y,
+                            float* d_cache_out, const int* d_cu_seqlens, const int* d_chunk_indices,
+                            int num_chunks, int T, int D, int W, int use_silu, void* stream);
+int cula_kda_short_conv_bwd(const void* d_x, const float* d_w, const float* d_bias, const float* d_cache_in,
+                            const void* d_dy, void* d_dx, float* d_dw, float* d_dbias, const int* d_cu_seqlens,
+                            const int* d_chunk_indices, int num_chunks, int T, int D, int W, int use_silu, void* stream);
+int cula_kda_rms_norm_gated_fwd(const void* d_x, const void* d_g, const float* d_w, void* d_y, float* d_rstd,
+                                long long R, int D, int use_swish, float eps, void* stream);
+int cula_kda_rms_norm_gated_bwd(const void* d_x, const void* d_g, const float* d_w, const float* d_rstd,
+                                const void* d_dy, void* d_dx, void* d_dg, float* d_dw, long long R, int D,
+                                int use_swish, void* stream);
+
 /*
  * Self-test of the bounded waits: launches one warp that waits on a barrier nothing completes; after max_polls
  * polls (1 .. 2^22) the wait gives up, *d_status is set to 1 (the time-out status every kernel above reports through
