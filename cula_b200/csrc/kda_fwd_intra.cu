@@ -13,12 +13,14 @@
 //
 // Exponent handling ("safe gate"): 2^(g_i - g_j) is never formed directly inside an MMA operand. Row i of
 // 16-row block I is scaled by 2^(g_i - r_I) (<= 1, r_I = g at the first row of the block) and column j by
-// 2^(r_I - g_j), which is <= 1 for earlier blocks and at most 2^(15*5*log2 e) ~ 2^108 inside block I.
+// 2^(r_I - g_j), which is <= 1 for earlier blocks and at most 2^(16*5*log2 e) ~ 2^116 inside block I.
 // So the B operand holds one copy of k-hat per anchor: 16 + 32 + 48 + 64 = 160 rows; the A operand
 // is [q-hat ; k-hat] scaled by their own block anchors (128 rows). Column block I of the 128 x 160
 // product is valid on the rows of block I only; the epilogue reads exactly those.
+// Every factor is built from TWO exponentials per element, 2^(g_i - r_I) and 2^(r_{I+1} - g_i), times constants that
+// depend on (block, channel) only and are tabulated once per tile (phase 3 below).
 //
-// Two CTAs are resident per SM (96 KB shared memory, 256 TMEM columns each), so one CTA's CUDA-core
+// Two CTAs are resident per SM (110 KB shared memory, 256 TMEM columns each), so one CTA's CUDA-core
 // operand generation overlaps the other's MMA, inverse and epilogues.
 #include "kda_common.cuh"
 #include "kda_params.h"
