@@ -31,10 +31,11 @@ constexpr int BD_RED = BD_BETA + 64;      // dbeta_u partials [BD_NQ][64]
 constexpr int BD_FLOATS = BD_RED + BD_NQ * 64;
 constexpr int BD_SMEM = BD_FLOATS * 4;
 
+// Round to tf32 (nearest, ties away from zero -- what cvt.rna.tf32.f32 does for finite values) with two integer
+// instructions: add half an ulp of the 10-bit mantissa, clear the 13 low bits. The PTX conversion is emulated with
+// about twice as many, and this kernel rounds tens of thousands of operands per tile.
 __device__ __forceinline__ float tf32r(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const float (&a)[4], float b0, float b1) {
     asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"

@@ -52,10 +52,11 @@ static_assert(BG_SEG <= 4, "segment totals share the 512 floats of MS_PGL");
 constexpr int BG_FLOATS = BG_MISC + MS_END;
 constexpr int BG_SMEM = BG_FLOATS * 4;
 
+// Round to tf32 (nearest, ties away from zero -- what cvt.rna.tf32.f32 does for finite values) with two integer
+// instructions: add half an ulp of the 10-bit mantissa, clear the 13 low bits. The PTX conversion is emulated with
+// about twice as many, and this kernel rounds tens of thousands of operands per tile.
 __device__ __forceinline__ float bg_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 __device__ __forceinline__ void bg_mma(float (&d)[4], const float (&a)[4], float b0, float b1) {
     asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -66,9 +67,12 @@ __device__ __forceinline__ void bg_mma(float (&d)[4], const float (&a)[4], float
 // The same with the B operand carried as a tf32 hi/lo pair (two MMAs): B is then exact to ~2^-22. Used for the Gram
 // VJPs, where every pair (i, j) adds +x to the gate gradient of row i and -x to that of row j through two different
 // products; the reverse cumulative sum relies on those two cancelling, so they must agree far better than tf32.
+__device__ __forceinline__ float bg_tf32_lo(float x) {      // the low part of a split: truncation is enough (error 2^-21 of the value)
+    return __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+}
 __device__ __forceinline__ void bg_mma_split(float (&d)[4], const float (&a)[4], float b0, float b1) {
     const float h0 = bg_tf32(b0), h1 = bg_tf32(b1);
-    bg_mma(d, a, bg_tf32(b0 - h0), bg_tf32(b1 - h1));
+    bg_mma(d, a, bg_tf32_lo(b0 - h0), bg_tf32_lo(b1 - h1));
     bg_mma(d, a, h0, h1);
 }
 // natural-log decay a(x) of one raw gate value and (optionally) da/dx and the A_log-gradient integrand
@@ -478,7 +482,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
                     const float rI = rIv[nt];
                     const float b0 = __bfloat162float(sK[j0 * QS + d]) * k0s * fast_exp2(fminf(rI - sG[j0 * GS + d], 120.f));
                     const float b1 = __bfloat162float(sK[j1 * QS + d]) * k1s * fast_exp2(fminf(rI - sG[j1 * GS + d], 120.f));
-                    const float h0 = bg_tf32(b0), h1 = bg_tf32(b1), l0 = bg_tf32(b0 - h0), l1 = bg_tf32(b1 - h1);
+                    const float h0 = bg_tf32(b0), h1 = bg_tf32(b1), l0 = bg_tf32_lo(b0 - h0), l1 = bg_tf32_lo(b1 - h1);
                     bg_mma(accP[nt], aP, l0, l1);
                     bg_mma(accP[nt], aP, h0, h1);
                     bg_mma(accR[nt], aR, l0, l1);

@@ -82,18 +82,6 @@ static_assert(SM_TM + 32 * TROW * 4 <= SM_XS, "inverse scratch must fit the B op
 __device__ __forceinline__ uint64_t sdesc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return umma::make_sdesc(addr, lbo, sbo) | (2ull << 61);
 }
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
-}
-__device__ __forceinline__ float4 tf32x4(float a, float b, float c, float d) {
-    return make_float4(to_tf32(a), to_tf32(b), to_tf32(c), to_tf32(d));
-}
-__device__ __forceinline__ float load_gate_raw(const void* g, int g_fp32, size_t idx) {
-    return g_fp32 ? reinterpret_cast<const float*>(g)[idx]
-                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g)[idx]);
-}
 // kept out of line: it is instantiated per element group and the softplus path is long (instruction-cache footprint)
 __device__ __noinline__ float gate_activation(float graw, float alpha, float bias, int gate_mode, float lower_bound) {
     if (gate_mode == GATE_NONE) return graw;
@@ -105,8 +93,8 @@ __device__ __noinline__ float gate_activation(float graw, float alpha, float bia
 // D(16x8) += A(16 x 8*KT) * B(8*KT x 8) with A, B fp32 in shared memory (row-major, strides lda/ldb),
 // evaluated as three TF32 MMAs per k-step on the hi/lo split of both operands.
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(x - __uint_as_float(hi)));
+    hi = (__float_as_uint(x) + 0x1000u) & 0xffffe000u;                 // nearest, ties away (what cvt.rna.tf32 gives)
+    lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;       // the residual: truncation is enough
 }
 __device__ __forceinline__ void mma_tf32_16x8x8(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
