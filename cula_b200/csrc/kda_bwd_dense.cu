@@ -63,7 +63,9 @@ __device__ __forceinline__ void bd_tile(const BwdDenseParams& p, float* sm, cons
     const __nv_bfloat16* Vg = reinterpret_cast<const __nv_bfloat16*>(p.v);
     float* scr = p.scratch + tile_idx * (size_t)BWD_SCRATCH_FLOATS;
 
-    // A (fp32 [64][64]) and beta once
+    // A (fp32 [64][64]) and beta once. The staging loops are unrolled so that all loads of a thread are in flight
+    // together (rolled, every iteration pays a full memory latency before its conversions and stores).
+#pragma unroll
     for (int i = tid; i < 64 * 16; i += BD_THREADS) {
         const int row = i >> 4, c4 = (i & 15) * 4;
         const float4 a = *reinterpret_cast<const float4*>(p.akk + tile_idx * 4096 + row * 64 + c4);
@@ -94,6 +96,7 @@ __device__ __forceinline__ void bd_tile(const BwdDenseParams& p, float* sm, cons
     for (int vh = 0; vh < 2; ++vh) {
         __syncthreads();        // previous half's fragments are no longer read
         // ---- stage this value half ----
+#pragma unroll
         for (int i = tid; i < 128 * 16; i += BD_THREADS) {
             const int row = i >> 4, c4 = (i & 15) * 4;
             const float4 a = *reinterpret_cast<const float4*>(Sg + row * DV + vh * 64 + c4);

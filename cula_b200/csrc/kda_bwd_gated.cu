@@ -18,6 +18,22 @@
 #include "kda_common.cuh"
 #include "kda_params.h"
 
+// Optional per-phase cycle counters (compile with -DKDA_PHASE_TIMERS): thread 0 of every CTA adds the clock64() spent
+// between consecutive marks to a device array that kda_bwd_gated_read_timers() copies out (profiling builds only).
+#ifdef KDA_PHASE_TIMERS
+__device__ unsigned long long kda_bwd_gated_timers[16];
+#define BG_MARK(i)                                                                        \
+    do {                                                                                  \
+        if (threadIdx.x == 0) {                                                           \
+            const long long now_ = clock64();                                             \
+            atomicAdd(&kda_bwd_gated_timers[i], (unsigned long long)(now_ - bg_t0_));     \
+            bg_t0_ = now_;                                                                \
+        }                                                                                 \
+    } while (0)
+#else
+#define BG_MARK(i) do {} while (0)
+#endif
+
 namespace kda {
 
 constexpr int BG_THREADS = 512;
@@ -107,6 +123,9 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g8 = lane >> 2, t4 = lane & 3;
+#ifdef KDA_PHASE_TIMERS
+    long long bg_t0_ = clock64();
+#endif
     const int c = tile / p.H, h = tile - c * p.H;
     const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
     const size_t tile_idx = (size_t)tile;
@@ -121,44 +140,80 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     for (int e = 0; e < 8; ++e)
         bias[e] = (p.gate_mode != GATE_NONE && p.dt_bias) ? p.dt_bias[h * DK + 64 * (e >> 2) + 4 * pc + (e & 3)] : 0.f;
 
-    // ---- 1a. wide loads: gate activation -> sG (log2 domain, zero for padding rows); q, k -> bf16 copies + norms ----
+    // ---- 1a. wide loads: gate activation -> sG (log2 domain, zero for padding rows); q, k -> bf16 copies + norms.
+    //          All global loads of the two passes are issued before the first use (a load that is consumed right away
+    //          costs a full memory latency per pass); a padding row reads the last real row and is zeroed afterwards.
+    //          The raw gate rows stay in registers for the gate VJP at the end of the tile. ----
+    constexpr int NPASS = 64 / BG_PASS_ROWS;
+    float gvs[NPASS][8];
+    uint2 qs0[NPASS], qs1[NPASS], ks0[NPASS], ks1[NPASS];
 #pragma unroll
-    for (int n = 0; n < 64 / BG_PASS_ROWS; ++n) {
-        const int row = (tid >> 4) + BG_PASS_ROWS * n;
-        const size_t off = base + (size_t)row * tok_stride + 4 * pc;
-        float gv[8];
-        uint2 q0 = make_uint2(0, 0), q1 = q0, k0 = q0, k1 = q0;
+    for (int n = 0; n < NPASS; ++n) {
+        const int row = (tid >> 4) + BG_PASS_ROWS * n, lrow = min(row, ci.valid - 1);
+        const size_t off = base + (size_t)lrow * tok_stride + 4 * pc;
+        if (p.g_per_head) {        // one gate per (token, head), shared by all channels
+            const size_t gi = (size_t)(ci.row0 + lrow) * p.H + h;
+            const float gs = p.g_fp32 ? reinterpret_cast<const float*>(p.g)[gi]
+                                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.g)[gi]);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) gv[e] = 0.f;
-        if (row < ci.valid) {
-            if (p.g_per_head) {        // one gate per (token, head), shared by all channels
-                const size_t gi = (size_t)(ci.row0 + row) * p.H + h;
-                const float gs = p.g_fp32 ? reinterpret_cast<const float*>(p.g)[gi]
-                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.g)[gi]);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) gv[e] = gs;
-            } else if (p.g_fp32) {
-                const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
-                const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
-                gv[0] = lo.x; gv[1] = lo.y; gv[2] = lo.z; gv[3] = lo.w; gv[4] = hi.x; gv[5] = hi.y; gv[6] = hi.z; gv[7] = hi.w;
-            } else {
-                const uint2 lo = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off);
-                const uint2 hi = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off + 64);
-                float2 f;
-                f = unpack_bf16(lo.x); gv[0] = f.x; gv[1] = f.y;
-                f = unpack_bf16(lo.y); gv[2] = f.x; gv[3] = f.y;
-                f = unpack_bf16(hi.x); gv[4] = f.x; gv[5] = f.y;
-                f = unpack_bf16(hi.y); gv[6] = f.x; gv[7] = f.y;
-            }
-            q0 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off);
-            q1 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off + 64);
-            k0 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + off);
-            k1 = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + off + 64);
+            for (int e = 0; e < 8; ++e) gvs[n][e] = gs;
+        } else if (p.g_fp32) {
+            const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
+            const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
+            gvs[n][0] = lo.x; gvs[n][1] = lo.y; gvs[n][2] = lo.z; gvs[n][3] = lo.w;
+            gvs[n][4] = hi.x; gvs[n][5] = hi.y; gvs[n][6] = hi.z; gvs[n][7] = hi.w;
+        } else {
+            const uint2 lo = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off);
+            const uint2 hi = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off + 64);
+            // kept as packed bits until used: nothing depends on the loads yet
+            gvs[n][0] = __uint_as_float(lo.x); gvs[n][1] = __uint_as_float(lo.y);
+            gvs[n][2] = __uint_as_float(hi.x); gvs[n][3] = __uint_as_float(hi.y);
         }
+        qs0[n] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off);
+        qs1[n] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off + 64);
+        ks0[n] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + off);
+        ks1[n] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + off + 64);
+    }
+    // the other per-tile inputs of this phase, fetched now as raw bits: beta, the beta-gradient partial of the dense
+    // stage, and (I + L)^-1
+    uint32_t beta_bits = 0;
+    float dbu_pre = 0.f;
+    if (tid < 64) {
+        const size_t bi = (size_t)(ci.row0 + min(tid, ci.valid - 1)) * p.H + h;
+        beta_bits = p.beta_fp32 ? reinterpret_cast<const uint32_t*>(p.beta)[bi] : (uint32_t)reinterpret_cast<const uint16_t*>(p.beta)[bi];
+        dbu_pre = scr[SCR_DBU + tid];
+    }
+    float4 a_pre[64 * 16 / BG_THREADS];
+#pragma unroll
+    for (int n = 0; n < 64 * 16 / BG_THREADS; ++n) {
+        const int i = tid + BG_THREADS * n;
+        a_pre[n] = *reinterpret_cast<const float4*>(p.akk + tile_idx * 4096 + (i >> 4) * 64 + (i & 15) * 4);
+    }
+    const bool g_packed = !p.g_per_head && !p.g_fp32;       // gvs[n][0..3] hold 8 bf16 values
+    auto gate_row = [&](int n, float (&gv)[8]) {
+        if (g_packed) {
+            float2 f;
+            f = unpack_bf16(__float_as_uint(gvs[n][0])); gv[0] = f.x; gv[1] = f.y;
+            f = unpack_bf16(__float_as_uint(gvs[n][1])); gv[2] = f.x; gv[3] = f.y;
+            f = unpack_bf16(__float_as_uint(gvs[n][2])); gv[4] = f.x; gv[5] = f.y;
+            f = unpack_bf16(__float_as_uint(gvs[n][3])); gv[6] = f.x; gv[7] = f.y;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) gv[e] = gvs[n][e];
+        }
+    };
+#pragma unroll
+    for (int n = 0; n < NPASS; ++n) {
+        const int row = (tid >> 4) + BG_PASS_ROWS * n;
+        const bool live = row < ci.valid;
+        float gv[8];
+        gate_row(n, gv);
+        const uint2 zero2 = make_uint2(0, 0);
+        const uint2 q0 = live ? qs0[n] : zero2, q1 = live ? qs1[n] : zero2, k0 = live ? ks0[n] : zero2, k1 = live ? ks1[n] : zero2;
         float a[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e)
-            a[e] = (row < ci.valid) ? RCP_LN2 * bg_gate(gv[e], bias[e], alpha, p.gate_mode, p.lower_bound) : 0.f;
+            a[e] = live ? RCP_LN2 * bg_gate(gv[e], bias[e], alpha, p.gate_mode, p.lower_bound) : 0.f;
         *reinterpret_cast<float4*>(sG + row * GS + 4 * pc) = make_float4(a[0], a[1], a[2], a[3]);
         *reinterpret_cast<float4*>(sG + row * GS + 64 + 4 * pc) = make_float4(a[4], a[5], a[6], a[7]);
         *reinterpret_cast<uint2*>(sQ + row * QS + 4 * pc) = q0;
@@ -189,21 +244,21 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     if (tid < 64) {
         float b = 0.f;
         if (tid < ci.valid) {
-            size_t bi = (size_t)(ci.row0 + tid) * p.H + h;
-            b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
-                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
+            b = p.beta_fp32 ? __uint_as_float(beta_bits) : __uint_as_float(beta_bits << 16);
             if (p.beta_logit) b = __fdividef(1.f, 1.f + __expf(-b));
         }
         sBeta[tid] = b;
-        sDbeta[tid] = scr[SCR_DBU + tid];
+        sDbeta[tid] = dbu_pre;
     }
     if (tid < 128) sCol[tid] = 0.f;
-    for (int i = tid; i < 64 * 16; i += BG_THREADS) {
-        const int row = i >> 4, c4 = (i & 15) * 4;
-        const float4 a = *reinterpret_cast<const float4*>(p.akk + tile_idx * 4096 + row * 64 + c4);
+#pragma unroll
+    for (int n = 0; n < 64 * 16 / BG_THREADS; ++n) {
+        const int i = tid + BG_THREADS * n, row = i >> 4, c4 = (i & 15) * 4;
+        const float4 a = a_pre[n];
         *reinterpret_cast<float4*>(sA + row * AR + c4) = make_float4(bg_tf32(a.x), bg_tf32(a.y), bg_tf32(a.z), bg_tf32(a.w));
     }
     __syncthreads();
+    BG_MARK(0);   // loads, gate, norms
     // ---- 1b. cumulative sum down the rows (a row segment per thread, then the earlier segments' totals are added) ----
     {
         const int d = tid & 127, seg = tid >> 7;
@@ -225,7 +280,9 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     }
     __syncthreads();
 
-    // ---- 2. stage dW (acc1) and X = beta k-hat 2^G (acc3), both rounded to tf32 ----
+    BG_MARK(1);   // cumulative sum
+    // ---- 2. stage dW (acc1) and X = beta k-hat 2^G (acc3), both rounded to tf32 (unrolled: loads in flight together) ----
+#pragma unroll
     for (int i = tid; i < 64 * 32; i += BG_THREADS) {
         const int row = i >> 5, c4 = (i & 31) * 4;
         const float4 w = *reinterpret_cast<const float4*>(scr + SCR_DW + row * DK + c4);
@@ -239,6 +296,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     }
     __syncthreads();
 
+    BG_MARK(2);   // stage dW, X
     const int mt = warp & 3, nh = warp >> 2;     // 16-row tile and column group of this warp in the GEMM phases
     const int r0 = 16 * mt + g8, r1 = r0 + 8;
 
@@ -271,6 +329,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         }
     }
     __syncthreads();
+    BG_MARK(3);   // dA
     // ---- 4a. T1 = dA A^T -> c1 ----
     {
         float acc[BG_NT64][4];
@@ -334,12 +393,14 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         }
     }
     __syncthreads();
+    BG_MARK(4);   // T1, dL
     if (tid < 64) {
         float v = 0.f;
 #pragma unroll
         for (int x = 0; x < BG_NQ; ++x) v += pBeta[x * 64 + tid];
         sDbeta[tid] += v;
     }
+#pragma unroll
     for (int x = tid; x < 64 * 16; x += BG_THREADS) {      // cP = scale * dPs -> c1 (T1 is no longer needed)
         const int row = x >> 4, c4 = (x & 15) * 4;
         const float4 v = *reinterpret_cast<const float4*>(scr + SCR_DPS + row * BT + c4);
@@ -352,6 +413,18 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         float zw[BG_NT128][4];
 #pragma unroll
         for (int nt = 0; nt < BG_NT128; ++nt) zw[nt][0] = zw[nt][1] = zw[nt][2] = zw[nt][3] = 0.f;
+        // the scratch-record entries this thread combines with Zw below: fetched now, so that the loads run under the MMAs
+        float2 dqg_pre[BG_NT128][2], dkg_pre[BG_NT128][2];
+#pragma unroll
+        for (int nt = 0; nt < BG_NT128; ++nt) {
+            const int col = 8 * BG_NT128 * nh + 8 * nt + 2 * t4;
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = rr ? r1 : r0;
+                dqg_pre[nt][rr] = *reinterpret_cast<const float2*>(scr + SCR_DQG + row * DK + col);
+                dkg_pre[nt][rr] = *reinterpret_cast<const float2*>(scr + SCR_DKG + row * DK + col);
+            }
+        }
         for (int ks = 2 * mt; ks < 8; ++ks) {
             const int k0 = 8 * ks;
             const float fa[4] = {sA[(k0 + t4) * AR + r0], sA[(k0 + t4) * AR + r1], sA[(k0 + t4 + 4) * AR + r0], sA[(k0 + t4 + 4) * AR + r1]};
@@ -374,8 +447,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
             for (int rr = 0; rr < 2; ++rr) {
                 const int row = rr ? r1 : r0;
                 const float2 gi = *reinterpret_cast<const float2*>(sG + row * GS + col);
-                const float2 dqg = *reinterpret_cast<const float2*>(scr + SCR_DQG + row * DK + col);
-                const float2 dkg = *reinterpret_cast<const float2*>(scr + SCR_DKG + row * DK + col);
+                const float2 dqg = dqg_pre[nt][rr], dkg = dkg_pre[nt][rr];
                 const float2 qf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + row * QS + col));
                 const float2 kf = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + row * QS + col));
                 const float gg[2] = {gi.x, gi.y}, gls[2] = {gl.x, gl.y}, dq2[2] = {dqg.x, dqg.y}, dk2[2] = {dkg.x, dkg.y};
@@ -424,6 +496,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     }
     __syncthreads();
 
+    BG_MARK(5);   // Zw, accumulator initial values
     // ---- next tile of this CTA: pull its inputs into L2 while the Gram phase computes (the first tile comes cold) ----
     if (next_tile >= 0) {
         const int cn = next_tile / p.H, hn = next_tile - cn * p.H;
@@ -456,6 +529,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         }
     }
 
+    BG_MARK(6);   // L2 hints
     // ---- 6. VJPs of the gated Gram matrices. Warp w owns 128 / BG_WARPS key channels for all 64 rows; the same
     //         thread owns the same (row, channel) cells in the row-side and column-side updates: no synchronisation ----
     {
@@ -511,6 +585,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
                 }
             }
         }
+        BG_MARK(7);   // Gram VJP, row side
 #pragma unroll 1
         for (int J = 0; J < 4; ++J) {                     // column side: columns of block J against rows i >= 16J
             float accC[BG_NT6][4];
@@ -555,6 +630,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         }
     }
     __syncthreads();
+    BG_MARK(8);   // Gram VJP, column side
 
     // ---- 7a. reverse cumulative sum of dG down the rows, in place (a row segment per thread, then the later segments' totals) ----
     {
@@ -576,6 +652,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         }
     }
     __syncthreads();
+    BG_MARK(9);   // reverse cumulative sum
     // ---- 7b. gate VJP with wide accesses: dg, per-channel sums for d dt_bias, the A_log sum ----
     float dA_part = 0.f;
     {
@@ -588,25 +665,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
             if (row >= ci.valid) continue;       // uniform over the 16 lanes that share a row
             const size_t off = base + (size_t)row * tok_stride + 4 * pc;
             float gv[8], dx[8];
-            if (p.g_per_head) {
-                const size_t gi = (size_t)(ci.row0 + row) * p.H + h;
-                const float gs = p.g_fp32 ? reinterpret_cast<const float*>(p.g)[gi]
-                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.g)[gi]);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) gv[e] = gs;
-            } else if (p.g_fp32) {
-                const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off);
-                const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.g) + off + 64);
-                gv[0] = lo.x; gv[1] = lo.y; gv[2] = lo.z; gv[3] = lo.w; gv[4] = hi.x; gv[5] = hi.y; gv[6] = hi.z; gv[7] = hi.w;
-            } else {
-                const uint2 lo = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off);
-                const uint2 hi = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.g) + off + 64);
-                float2 f;
-                f = unpack_bf16(lo.x); gv[0] = f.x; gv[1] = f.y;
-                f = unpack_bf16(lo.y); gv[2] = f.x; gv[3] = f.y;
-                f = unpack_bf16(hi.x); gv[4] = f.x; gv[5] = f.y;
-                f = unpack_bf16(hi.y); gv[6] = f.x; gv[7] = f.y;
-            }
+            gate_row(n, gv);             // the raw gate values loaded at the top of the tile
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int d = 64 * (e >> 2) + 4 * pc + (e & 3);
@@ -673,6 +732,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         }
     }
 
+    BG_MARK(10);  // gate VJP, dg
     // ---- 8. L2-norm VJP and stores of dq, dk (a warp per row); dbeta ----
     for (int r = 0; r < 64 / BG_WARPS; ++r) {
         const int row = warp * (64 / BG_WARPS) + r;
@@ -718,6 +778,7 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         if (p.beta_fp32) reinterpret_cast<float*>(p.dbeta)[bi] = v;
         else reinterpret_cast<__nv_bfloat16*>(p.dbeta)[bi] = __float2bfloat16_rn(v);
     }
+    BG_MARK(11);  // L2-norm VJP, dq, dk, dbeta
 }
 
 // Persistent: CTA b handles tiles b, b + gridDim.x, ... so that the next tile's inputs can be prefetched.
@@ -731,6 +792,17 @@ __global__ void __launch_bounds__(BG_THREADS, 1) kda_bwd_gated_kernel(const BwdG
 }
 
 }  // namespace kda
+
+#ifdef KDA_PHASE_TIMERS
+extern "C" int kda_bwd_gated_read_timers(unsigned long long* out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, kda_bwd_gated_timers, sizeof(kda_bwd_gated_timers));
+    if (e == cudaSuccess && reset) {
+        unsigned long long z[16] = {};
+        e = cudaMemcpyToSymbol(kda_bwd_gated_timers, z, sizeof(z));
+    }
+    return (int)e;
+}
+#endif
 
 extern "C" int kda_launch_bwd_gated(const kda::BwdGatedParams* p, int num_chunks, cudaStream_t stream) {
     using namespace kda;

@@ -27,16 +27,16 @@
 #include "umma.cuh"
 
 // Optional per-phase cycle counters (compile with -DKDA_PHASE_TIMERS): thread 0 of every CTA adds the clock64() spent
-// between consecutive marks into [gridDim.x][16] long long placed right after the p.mkk_out array (profiling builds only).
+// between consecutive marks to a device array that kda_fwd_intra_read_timers() copies out (profiling builds only).
 #ifdef KDA_PHASE_TIMERS
-#define PHASE_MARK(i)                                                                 \
-    do {                                                                              \
-        if (tid == 0) {                                                               \
-            const long long now_ = clock64();                                         \
-            atomicAdd(reinterpret_cast<unsigned long long*>(p.mkk_out + (size_t)p.num_tiles * 4096) + blockIdx.x * 16 + (i), \
-                      (unsigned long long)(now_ - phase_t0_));   /* a reduction: nothing waits for it */          \
-            phase_t0_ = now_;                                                         \
-        }                                                                             \
+__device__ unsigned long long kda_fwd_intra_timers[16];
+#define PHASE_MARK(i)                                                                     \
+    do {                                                                                  \
+        if (tid == 0) {                                                                   \
+            const long long now_ = clock64();                                             \
+            atomicAdd(&kda_fwd_intra_timers[i], (unsigned long long)(now_ - phase_t0_));  \
+            phase_t0_ = now_;                                                             \
+        }                                                                                 \
     } while (0)
 #else
 #define PHASE_MARK(i) do {} while (0)
@@ -815,6 +815,17 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
 }  // namespace kda
 
 extern "C" int kda_fwd_intra_smem_bytes() { return kda::SM_TOTAL + 1024; }
+
+#ifdef KDA_PHASE_TIMERS
+extern "C" int kda_fwd_intra_read_timers(unsigned long long* out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, kda_fwd_intra_timers, sizeof(kda_fwd_intra_timers));
+    if (e == cudaSuccess && reset) {
+        unsigned long long z[16] = {};
+        e = cudaMemcpyToSymbol(kda_fwd_intra_timers, z, sizeof(z));
+    }
+    return (int)e;
+}
+#endif
 
 extern "C" int kda_launch_fwd_intra(const kda::IntraParams* p, int num_chunks, cudaStream_t stream) {
     using namespace kda;
