@@ -249,7 +249,11 @@ def cp_section(rank, world, dev, flush, steps=10, T_total=CP_TOKENS, H=CP_HEADS)
     if not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29577")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        # a single rank never communicates: gloo keeps NCCL (and the version banner it prints on stdout) out of it
+        if world == 1:
+            dist.init_process_group("gloo", rank=0, world_size=1)
+        else:
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
 
     def sync_all():
         if world > 1:
@@ -496,6 +500,7 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    os.environ.setdefault("NCCL_DEBUG", "WARN")      # stdout carries ONE JSON line: no library banners
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

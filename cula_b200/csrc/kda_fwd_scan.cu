@@ -50,6 +50,17 @@ struct ScanLayout<true, 1> {
     static constexpr int CTAS_PER_SM = 2;
 };
 
+// Bounded wait that also ends when *votes reaches `quorum` (the CTA has nothing left to compute).
+// Returns 0 = barrier phase completed, 1 = gave up (time-out), 2 = quorum reached.
+__device__ __forceinline__ int mbar_wait_or_quorum(uint64_t* bar, uint32_t parity, volatile int* votes, int quorum) {
+    for (int i = 0; i < (1 << 22); ++i) {
+        if (mbar_test(bar, parity)) return 0;
+        if (*votes >= quorum) return 2;
+        if (i > 64) __nanosleep(64);
+    }
+    return 1;
+}
+
 // TRANSITION: the affine action of a whole shard on the state, S_out = M S_in + C, from the same recurrence with
 // four column groups per (sequence, head): groups 0,1 carry C (zero start, normal u; written to p.ht) and groups
 // 2,3 carry the K x K matrix M = prod_c (D_c - kg_c^T w_c) (identity start, u = 0; written to p.m_out). No output
@@ -62,11 +73,23 @@ kda_fwd_scan_kernel(const ScanParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES + L::STG);
     uint64_t* empty = full + L::STAGES;
+    // Columns of the transition matrix M that have become exactly zero stay zero (their recurrence is linear and has
+    // no source term), so a warp whose 16 columns are all zero votes once and stops computing; when all consumer warps
+    // of an M-carrying CTA have voted, the CTA is finished -- bit-identical results, and with strong gates (the decay
+    // of one chunk underflows fp32) these CTAs free their SMs for the C-carrying ones after a chunk or two.
+    volatile int* zero_votes = reinterpret_cast<volatile int*>(empty + L::STAGES);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool is_m = TRANSITION && blockIdx.x >= 2;     // this CTA carries columns of M
-    const int vh = NVH == 2 ? ((warp >> 2) & 1) : (blockIdx.x & 1), h = blockIdx.y;
+    // Grid: (column group, head, sequence). When the transition scan has more CTAs than SMs it is launched as
+    // (head, sequence, column group) instead: block indices are handed to the SMs in linear order, so all C-carrying
+    // CTAs (groups 0, 1) come first, one per SM, and the M-carrying ones (groups 2, 3) become their co-residents; when
+    // the M CTAs finish early (see zero_votes) every C CTA is left with an SM of its own. (With fewer CTAs than SMs the
+    // original order keeps the four CTAs of a head on neighbouring SMs, which read the same tile packs.)
+    const bool gm = TRANSITION && p.group_major;
+    const int cgrp = gm ? blockIdx.z : blockIdx.x, seq_slot = gm ? blockIdx.y : blockIdx.z;
+    const bool is_m = TRANSITION && cgrp >= 2;           // this CTA carries columns of M
+    const int vh = NVH == 2 ? ((warp >> 2) & 1) : (cgrp & 1), h = gm ? blockIdx.x : blockIdx.y;
     const int pw = warp & 3;                             // 16-column slice of the value half
-    const int n = p.seq_order ? p.seq_order[blockIdx.z] : blockIdx.z;
+    const int n = p.seq_order ? p.seq_order[seq_slot] : seq_slot;
     int bos, len, chunk0;
     if (p.cu_seqlens) {
         bos = p.cu_seqlens[n];
@@ -84,6 +107,7 @@ kda_fwd_scan_kernel(const ScanParams p) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], L::CONSUMERS);
         }
+        *zero_votes = 0;
         fence_mbar_init();
     }
     __syncthreads();
@@ -96,11 +120,22 @@ kda_fwd_scan_kernel(const ScanParams p) {
         // ------------------------------- producer warp -------------------------------
         if (TRANSITION) {
             const int u_off = vh ? TP_U1 : TP_U0;
+            int issued = 0;                       // chunks whose copies have been issued
             for (int c = 0; c < nchunks; ++c) {
                 const int s = c % L::STAGES, use = c / L::STAGES;
                 bool ok = true;
+                int quorum = 0;
                 if (lane == 0) {
-                    if (use > 0) ok = mbar_wait(&empty[s], (use - 1) & 1);
+                    if (is_m && *zero_votes >= L::CONSUMERS) quorum = 1;
+                    if (!quorum && use > 0) {
+                        const int r = mbar_wait_or_quorum(&empty[s], (use - 1) & 1, zero_votes, is_m ? L::CONSUMERS : (1 << 30));
+                        ok = r != 1;
+                        quorum = r == 2;
+                    }
+                }
+                quorum = __shfl_sync(0xffffffffu, quorum, 0);
+                if (quorum) break;
+                if (lane == 0) {
                     if (ok) {
                         const unsigned char* tile = p.tiles + ((size_t)(chunk0 + c) * p.H + h) * TP_BYTES;
                         unsigned char* dst = smem + s * L::STAGE_BYTES;
@@ -116,6 +151,7 @@ kda_fwd_scan_kernel(const ScanParams p) {
                     if (lane == 0) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
                     break;
                 }
+                issued = c + 1;
                 const int cn = c + L::STAGES;                 // not yet being copied: pull it into L2
                 if (cn < nchunks) {
                     const unsigned char* tile = p.tiles + ((size_t)(chunk0 + cn) * p.H + h) * TP_BYTES;
@@ -125,6 +161,11 @@ kda_fwd_scan_kernel(const ScanParams p) {
                         prefetch_l2(tile + off);
                     }
                 }
+            }
+            // the consumers may have left early: do not exit with bulk copies to this CTA's shared memory in flight
+            if (is_m && lane == 0) {
+                for (int cc = max(0, issued - L::STAGES); cc < issued; ++cc)
+                    if (!mbar_wait(&full[cc % L::STAGES], (cc / L::STAGES) & 1)) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
             }
             return;
         }
@@ -142,7 +183,7 @@ kda_fwd_scan_kernel(const ScanParams p) {
                     bulk_g2s(dst, tile, TP_BYTES, &full[s]);          // head + both U halves are contiguous
                 } else {
                     bulk_g2s(dst, tile, TP_HEAD_BYTES, &full[s]);
-                    bulk_g2s(dst + ST_U, tile + ((blockIdx.x & 1) ? TP_U1 : TP_U0), 8192, &full[s]);
+                    bulk_g2s(dst + ST_U, tile + ((cgrp & 1) ? TP_U1 : TP_U0), 8192, &full[s]);
                 }
             }
         }
@@ -186,9 +227,22 @@ kda_fwd_scan_kernel(const ScanParams p) {
 #pragma unroll
     for (int kp = 0; kp < 4; ++kp) x256[kp] = (uint32_t)(((4 * kp + m) ^ r) << 4);
 
+    bool voted = false;          // this warp's columns of M are exactly zero (transition scan only)
     for (int c = 0; c < nchunks; ++c) {
         const int s = c % L::STAGES;
-        if (!mbar_wait(&full[s], (c / L::STAGES) & 1)) {
+        if (is_m) {
+            if (*zero_votes >= L::CONSUMERS) break;
+            const int r = mbar_wait_or_quorum(&full[s], (c / L::STAGES) & 1, zero_votes, L::CONSUMERS);
+            if (r == 2) break;
+            if (r == 1) {
+                atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+                return;
+            }
+            if (voted) {         // nothing to compute: keep the pipeline protocol going for the warps that still work
+                if (lane == 0) mbar_arrive(&empty[s]);
+                continue;
+            }
+        } else if (!mbar_wait(&full[s], (c / L::STAGES) & 1)) {
             atomicExch(p.status, STATUS_WAIT_TIMEOUT);
             return;
         }
@@ -205,6 +259,14 @@ kda_fwd_scan_kernel(const ScanParams p) {
             smax = fmaxf(smax, fmaxf(fmaxf(fabsf(S[jt][0]), fabsf(S[jt][1])), fmaxf(fabsf(S[jt][2]), fabsf(S[jt][3]))));
 #pragma unroll
         for (int o = 16; o; o >>= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+        if (is_m && smax == 0.f) {      // all 16 columns of this warp are exactly zero, and will stay zero
+            voted = true;
+            if (lane == 0) {
+                atomicAdd(const_cast<int*>(zero_votes), 1);
+                mbar_arrive(&empty[s]);
+            }
+            continue;
+        }
         int shift = 13 - (((__float_as_int(smax) >> 23) & 0xff) - 127);
         shift = max(-100, min(100, shift));
         const float s_up = __int_as_float((shift + 127) << 23), s_down = __int_as_float((127 - shift) << 23);
@@ -462,10 +524,15 @@ extern "C" int kda_launch_fwd_scan(const kda::ScanParams* p, cudaStream_t stream
 extern "C" int kda_launch_fwd_transition(const kda::ScanParams* p, cudaStream_t stream) {
     using namespace kda;
     if (p->N <= 0) return 0;
-    dim3 grid(4, p->H, p->N);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    ScanParams q = *p;
+    q.group_major = 4LL * p->H * p->N > sms;     // see the index mapping at the top of the kernel
+    const dim3 grid = q.group_major ? dim3(p->H, p->N, 4) : dim3(4, p->H, p->N);
     constexpr int smem = ScanLayout<true, 1>::SMEM;
     cudaError_t e = cudaFuncSetAttribute(kda_fwd_scan_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    kda_fwd_scan_kernel<false, true><<<grid, SCAN_THREADS, smem, stream>>>(*p);
+    kda_fwd_scan_kernel<false, true><<<grid, SCAN_THREADS, smem, stream>>>(q);
     return (int)cudaGetLastError();
 }

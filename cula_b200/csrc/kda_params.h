@@ -55,6 +55,8 @@ struct ScanParams {
     int T;
     int H;
     int N;                        // number of sequences
+    int group_major;              // transition launch only: grid is (head, sequence, column group) instead of
+                                  // (column group, head, sequence); set by the launcher
 };
 
 struct BwdScanParams {
