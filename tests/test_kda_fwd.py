@@ -287,3 +287,27 @@ def test_bounded_wait_gives_up_and_reports():
     inp = make_inputs(1, 64, 1, seed=1, gate_offset=-6.0)
     o, ht = run_chunk_kda(inp)
     assert torch.isfinite(o).all()
+
+
+def test_strong_softplus_gate_matches_oracle():
+    """safe_gate=False (softplus gate, no lower bound) with a decay of about 3 nats per token -- 48 nats inside a
+    16-row block, well inside the range the per-block anchoring carries exactly."""
+    inp = make_inputs(2, 200, 2, seed=15, gate_offset=3.0, h0_std=0.5)
+    o, ht = run_chunk_kda(inp, safe=False)
+    o_ref, ht_ref = oracle_fwd(inp, safe=False)
+    assert_fwd_close(o, ht, o_ref, ht_ref, ht_tol=2e-3, tag="softplus strong")
+
+
+def test_unbounded_gate_stays_finite():
+    """A pre-gated decay of -9 nats per token is outside what the per-block anchoring can carry (a 16-row block
+    spans 2^195, fp32 ends at 2^127; the safe gate, lower_bound >= -5, guarantees 2^116). The reference refuses such
+    gates outright (cula/kda/chunk_intra.py:761); here the clamped factor tables must at least keep inf * 0 out of the
+    Gram products: everything stays finite (the values are not claimed to be accurate in that regime)."""
+    B, T, H = 1, 130, 2
+    inp = make_inputs(B, T, H, seed=16, h0_std=0.5)
+    gen = torch.Generator().manual_seed(17)
+    inp["g"] = (-9.0 + 0.5 * torch.randn(B, T, H, 128, generator=gen)).float()
+    inp["q"] = F.normalize(inp["q"].float(), dim=-1).to(torch.bfloat16)
+    inp["k"] = F.normalize(inp["k"].float(), dim=-1).to(torch.bfloat16)
+    o, ht = run_chunk_kda(inp, l2=False, gate=False)
+    assert torch.isfinite(o).all() and torch.isfinite(ht).all()
