@@ -100,6 +100,29 @@ def headline_config(workload):
             "sharding": "batch x head shards, one per rank, no collective"}
 
 
+class stdout_to_stderr:
+    """File-descriptor level redirect of stdout to stderr: the NCCL communicator prints its version banner with
+    printf when it is created, and stdout must carry exactly ONE JSON line."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
+def init_nccl(rank, world, dev):
+    import torch.distributed as dist
+    with stdout_to_stderr():
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        dist.barrier()                  # communicator creation (and its banner) happens here at the latest
+        torch.cuda.synchronize()
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -253,7 +276,7 @@ def cp_section(rank, world, dev, flush, steps=10, T_total=CP_TOKENS, H=CP_HEADS)
         if world == 1:
             dist.init_process_group("gloo", rank=0, world_size=1)
         else:
-            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+            init_nccl(rank, world, dev)
 
     def sync_all():
         if world > 1:
@@ -375,7 +398,7 @@ def run_extra(args, rank, world, local_rank):
         if not dist.is_initialized():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", "29577")
-            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+            init_nccl(rank, world, dev)
     _native.lib()
     kw = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
     H = w["H"]
@@ -500,7 +523,6 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
-    os.environ.setdefault("NCCL_DEBUG", "WARN")      # stdout carries ONE JSON line: no library banners
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -517,7 +539,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(rank, world, dev)
     _native.lib()                     # fail loudly if the CUDA library is missing
     # one rank per GPU: keep this rank's threads and its pinned host buffers (allocated below) on the GPU's own
     # NUMA node, so that the ranks' host<->device copies do not all go through one socket's memory
