@@ -33,16 +33,24 @@ def _deps_mtime():
     return max(os.path.getmtime(f) for f in files)
 
 
-def build(force=False, verbose=False):
+TIMERS_LIB = os.path.join(LIB_DIR, "libcula_kda_timers.so")
+
+
+def build(force=False, verbose=False, timers=False):
+    """Build the library. ``timers=True`` builds a second library, libcula_kda_timers.so, with -DKDA_PHASE_TIMERS:
+    the chunk-parallel forward kernel and the gated backward kernel then count clock64() cycles per phase (see
+    cula_b200/phase_timers.py); it is a profiling aid and is never loaded by the package itself."""
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     os.makedirs(LIB_DIR, exist_ok=True)
-    os.makedirs(OBJ_DIR, exist_ok=True)
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _deps_mtime():
-        return LIB
-    extra = ["-Xptxas", "-v"] if verbose else []
+    obj_dir = OBJ_DIR + ("_timers" if timers else "")
+    lib = TIMERS_LIB if timers else LIB
+    os.makedirs(obj_dir, exist_ok=True)
+    if not force and os.path.exists(lib) and os.path.getmtime(lib) >= _deps_mtime():
+        return lib
+    extra = (["-Xptxas", "-v"] if verbose else []) + (["-DKDA_PHASE_TIMERS"] if timers else [])
     procs, objs = [], []
     for src in sources():
-        obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         procs.append((src, subprocess.Popen([nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj],
                                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -54,9 +62,9 @@ def build(force=False, verbose=False):
         failed |= pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-lcudart"], check=True)
-    return LIB
+    subprocess.run([nvcc, "-shared", "-o", lib, *objs, "-lcudart"], check=True)
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, timers="--timers" in sys.argv))
