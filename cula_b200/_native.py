@@ -28,7 +28,7 @@ SIGNATURES = {
     "cula_kda_bwd_scratch_floats": (_i, []),
     "cula_kda_bwd_grad_scale": (_i, [_vp, ctypes.c_longlong, _fp, ctypes.c_longlong, _vp, _fp, _vp]),
     "cula_kda_bwd_scan": (_i, [_vp, _vp, _fp, _fp, _vp, _fp, _fp, _ip, _ip, _ip, _i, _i, _i, _ip, _vp]),
-    "cula_kda_bwd_dense": (_i, [_fp, _fp, _vp, _vp, _vp, _vp, _vp, _i, _fp, _fp, _vp, _fp, _ip, _ip, _i, _i, _i, _vp]),
+    "cula_kda_bwd_dense": (_i, [_fp, _fp, _vp, _vp, _vp, _vp, _vp, _i, _fp, _fp, _vp, _fp, _ip, _ip, _i, _i, _i, _ip, _vp]),
     "cula_kda_bwd_gated": (_i, [_vp, _vp, _vp, _i, _vp, _i, _fp, _fp, _fp, _fp, _fp, _fp, _vp, _vp, _vp, _vp, _fp, _fp,
                                 _ip, _ip, _i, _i, _i, _f, _i, _i, _f, _vp]),
     "cula_kda_noalloc_max_tiles": (_i, []),

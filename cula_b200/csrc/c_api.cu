@@ -189,9 +189,9 @@ extern "C" int cula_kda_bwd_dense(const float* d_h32, const float* d_ds, const v
                                   const void* d_do, const void* d_v, const void* d_beta, int beta_is_fp32,
                                   const float* d_akk, const float* d_gscale, void* d_dv, float* d_scratch,
                                   const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H,
-                                  void* stream) {
+                                  int* d_status, void* stream) {
     if (num_chunks == 0) return 0;
-    if (!d_h32 || !d_ds || !d_vnew || !d_dvn || !d_do || !d_v || !d_beta || !d_akk || !d_gscale || !d_dv || !d_scratch ||
+    if (!d_h32 || !d_ds || !d_vnew || !d_dvn || !d_do || !d_v || !d_beta || !d_akk || !d_gscale || !d_dv || !d_scratch || !d_status ||
         num_chunks < 0 || H <= 0)
         return CULA_KDA_EINVAL;
     if ((d_cu_seqlens == nullptr) != (d_chunk_indices == nullptr)) return CULA_KDA_EINVAL;
@@ -202,7 +202,7 @@ extern "C" int cula_kda_bwd_dense(const float* d_h32, const float* d_ds, const v
     kda::BwdDenseParams p{};
     p.h32 = d_h32; p.ds = d_ds; p.vnew = d_vnew; p.dvn = d_dvn; p.d_o = d_do; p.v = d_v; p.beta = d_beta;
     p.akk = d_akk; p.gscale = d_gscale; p.dv = d_dv; p.scratch = d_scratch;
-    p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices; p.T = T; p.H = H;
+    p.cu_seqlens = d_cu_seqlens; p.chunk_indices = d_chunk_indices; p.T = T; p.H = H; p.status = d_status;
     p.beta_fp32 = beta_is_fp32 & CULA_KDA_BETA_FP32; p.beta_logit = (beta_is_fp32 & CULA_KDA_BETA_LOGIT) != 0;
     return kda_launch_bwd_dense(&p, num_chunks, static_cast<cudaStream_t>(stream));
 }

@@ -1,309 +1,514 @@
-// Chunk-parallel backward, gate-free part: per (chunk, head) the dense products that involve the carried
-// states, as TF32 mma.sync GEMMs on fp32 operands staged in shared memory (value dimension in two halves):
+// Chunk-parallel backward, gate-free part: per (chunk, head) the dense products that involve the carried states.
 //     dQg  = dO S^T                 dW = -dVn S^T              dKg = Vn dS'^T          [64 x 128]
 //     dPs  = tril(dO Vn^T)          dAu = stril(dVn (beta V)^T)                         [64 x 64]
 //     Zu   = A^T dVn  ->  dv = beta Zu (final, bf16),  dbeta_u = rowsum(Zu * V)
 //     dD[k] = sum_v S[k,v] dS'[k,v]
 // dQg, dW, dKg, dPs, dAu, dD, dbeta_u go to an fp32 scratch record per tile for the gated stage.
 //
+// All products run on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory):
+//   * the fp32 states S and dS' (64 KB each per tile, the bulk of the traffic) are fetched by the TMA engine through
+//     tiled tensor maps (cp.async.bulk.tensor, 32 floats x 128 rows per box, 128-byte swizzle) straight into the
+//     K-major operand layout of kind::tf32 -- no thread touches them except for the row sums of dD;
+//   * the 16-bit operands (dO, V bf16; Vn, dVn fp16) are widened to 32-bit containers by the CUDA cores (every bf16 /
+//     fp16 value is exact in tf32) and stacked so that ONE M = 128 instruction serves two products:
+//         [dO; dVn] x S^T        -> TMEM lanes 0-63 dQg, lanes 64-127 -dW
+//         [Vn; V ] x dS'^T       -> lanes 0-63 dKg
+//         [dO; dVn] x [Vn; V]^T  -> lanes 0-63 / columns 0-63 dPs, lanes 64-127 / columns 64-127 the u-part of dA
+//   * Zu = A^T dVn is a kind::f16 product with both operands MN-major (A and dVn are stored token-row-major and the
+//     contraction runs over the token), A stacked twice so that both lane halves of TMEM hold Zu.
+// The value dimension is processed in two halves that accumulate into the same TMEM columns; the TMA loads of both
+// halves of the NEXT tile are in flight during the epilogue of this one, and the 16-bit operands of the next stage
+// wait in registers. The tensor core truncates tf32 operands; the mean truncation error of the state operands is
+// compensated by one factor in the epilogue. Every wait is bounded: on expiry the status word is set, the CTA waits
+// (bounded) for its copies in flight, frees its tensor memory and returns.
+//
 // Covers the state-dependent half of chunk_kda_bwd_kernel_wy_dqkg_fused (cula/kda/chunk_bwd.py:145-313) and the
 // dAqk half of chunk_kda_bwd_kernel_dAv (cula/kda/chunk_bwd.py:63-125).
+#include <cuda.h>
+
 #include "kda_common.cuh"
 #include "kda_params.h"
+#include "umma.cuh"
+
+// Optional per-phase cycle counters (compile with -DKDA_PHASE_TIMERS): thread 0 of every CTA adds the clock64() spent
+// between consecutive marks to a device array that kda_bwd_dense_read_timers() copies out (profiling builds only).
+#ifdef KDA_PHASE_TIMERS
+__device__ unsigned long long kda_bwd_dense_timers[16];
+#define BD_MARK(i)                                                                        \
+    do {                                                                                  \
+        if (threadIdx.x == 0) {                                                           \
+            const long long now_ = clock64();                                             \
+            atomicAdd(&kda_bwd_dense_timers[i], (unsigned long long)(now_ - bd_t0_));     \
+            bd_t0_ = now_;                                                                \
+        }                                                                                 \
+    } while (0)
+#else
+#define BD_MARK(i) do {} while (0)
+#endif
 
 namespace kda {
 
 constexpr int BD_THREADS = 512;
-constexpr int BD_NQ = BD_THREADS / 128;   // column groups: a warp = 16-row tile x column group
-constexpr int BD_NT128 = 128 / BD_NQ / 8; // n-tiles per warp over the 128 key channels
-constexpr int BD_NT64 = 64 / BD_NQ / 8;   // n-tiles per warp over 64 token / value columns
-constexpr int PR = 68;                    // padded fp32 row: fragment loads hit 32 distinct banks
-// shared memory (floats)
-constexpr int BD_S = 0;                   // S_h   [128][68]
-constexpr int BD_DS = BD_S + 128 * PR;    // dS'_h [128][68]
-constexpr int BD_DO = BD_DS + 128 * PR;   // dO_h  [64][68]
-constexpr int BD_VN = BD_DO + 64 * PR;    // Vn_h
-constexpr int BD_DVN = BD_VN + 64 * PR;   // dVn_h
-constexpr int BD_V = BD_DVN + 64 * PR;    // V_h (raw)
-constexpr int BD_A = BD_V + 64 * PR;      // A [64][68]
-constexpr int BD_BETA = BD_A + 64 * PR;   // beta[64]
-constexpr int BD_RED = BD_BETA + 64;      // dbeta_u partials [BD_NQ][64]
-constexpr int BD_FLOATS = BD_RED + BD_NQ * 64;
-constexpr int BD_SMEM = BD_FLOATS * 4;
+// shared-memory map (bytes from a 1024-aligned base); an "atom" is [rows][128 B] with the 16-byte groups of a row
+// XOR-swizzled by (row & 7) -- what the TMA engine writes with the 128-byte swizzle and what the MMA descriptors expect
+constexpr int BD_S = 0;             // S   as B operand: [2 value halves][2 k-atoms][128 rows][128 B] fp32
+constexpr int BD_DS = 65536;        // dS' likewise
+constexpr int BD_A1 = 131072;       // [dO; dVn] of one value half: [2 k-atoms][128 rows][128 B] fp32
+constexpr int BD_VNV = 163840;      // [Vn; V] of one value half, same shape
+constexpr int BD_A4 = 196608;       // A fp16, stored twice: [2][64 tokens j][128 B] -- MN-major A operand of Zu
+constexpr int BD_B4 = 212992;       // dVn fp16 of one value half: [64 tokens j][128 B] -- MN-major B operand of Zu
+constexpr int BD_MISC = 221184;     // beta[64] f32 @0, dbeta_u partials [8][64] f32 @256, 4 mbarriers @2304, TMEM slot @2336, abort @2340
+constexpr int BD_SMEM = BD_MISC + 2560 + 1024;
+constexpr uint32_t BD_HALF_TX = 65536;   // bytes the TMA engine delivers per value half: 2 boxes of S + 2 of dS'
+// TMEM columns
+constexpr uint32_t TC_D1 = 0, TC_D2 = 128, TC_D3 = 256, TC_D4 = 384;
+// mean relative truncation error of a tf32 operand with log-uniform mantissa is -2^-11 / ln 2; products with ONE
+// truncated operand (the states) are scaled back by this factor
+constexpr float TF32_TRUNC_COMP = 1.0003523f;
 
-// Round to tf32 (nearest, ties away from zero -- what cvt.rna.tf32.f32 does for finite values) with two integer
-// instructions: add half an ulp of the 10-bit mantissa, clear the 13 low bits. The PTX conversion is emulated with
-// about twice as many, and this kernel rounds tens of thousands of operands per tile.
-__device__ __forceinline__ float tf32r(float x) {
-    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+__device__ __forceinline__ uint64_t bd_sdesc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return umma::make_sdesc(addr, lbo, sbo) | (2ull << 61);     // 128-byte swizzle
 }
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const float (&a)[4], float b0, float b1) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])), "r"(__float_as_uint(a[3])),
-                   "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t smem_src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 :: "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// byte offset of the 16-byte group `chunk` (0..7) of row `row` inside an atom
+__device__ __forceinline__ uint32_t atom_off(int row, int chunk) {
+    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-// One (chunk, head) tile. next_tile >= 0 names the tile this CTA handles next: its inputs are pulled into L2 midway.
-__device__ __forceinline__ void bd_tile(const BwdDenseParams& p, float* sm, const int tile, const int next_tile) {
+struct BdStage {          // the 16-bit operands of one value half, as loaded: 8 consecutive value columns of one token row
+    uint4 o, v, vn, dvn;
+};
+
+__global__ void __launch_bounds__(BD_THREADS, 1)
+kda_bwd_dense_kernel(const BwdDenseParams p, const int num_tiles, const __grid_constant__ CUtensorMap map_s,
+                     const __grid_constant__ CUtensorMap map_ds, const __grid_constant__ CUtensorMap map_out128,
+                     const __grid_constant__ CUtensorMap map_out64) {
+    extern __shared__ unsigned char bd_smem_raw[];
+    unsigned char* sm = bd_smem_raw + ((1024u - (smem_u32(bd_smem_raw) & 1023u)) & 1023u);
+    const uint32_t smb = smem_u32(sm);
+    float* sBeta = reinterpret_cast<float*>(sm + BD_MISC);
+    float* sRed = reinterpret_cast<float*>(sm + BD_MISC + 256);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BD_MISC + 2304);    // [0,1] states of half 0 / 1 landed; [2,3] MMAs of half 0 / 1 done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + BD_MISC + 2336);
+    volatile int* sAbort = reinterpret_cast<volatile int*>(sm + BD_MISC + 2340);
+
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int mt = warp & 3, nh = warp >> 2;          // 16-row tile, column group
-    const int c = tile / p.H, h = tile - c * p.H;
-    const ChunkInfo ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
-    const size_t tile_idx = (size_t)tile;
     const size_t tok_stride = (size_t)p.H * DV;
-    const size_t base = (size_t)ci.row0 * tok_stride + (size_t)h * DV;
     const float gs = p.gscale[0], gs_inv = p.gscale[1];
-    const float* Sg = p.h32 + tile_idx * (size_t)(DK * DV);
-    const float* dSg = p.ds + tile_idx * (size_t)(DK * DV);
-    const __half* Vng = reinterpret_cast<const __half*>(p.vnew) + tile_idx * (size_t)(BT * DV);
-    const __half* dVng = reinterpret_cast<const __half*>(p.dvn) + tile_idx * (size_t)(BT * DV);
     const __nv_bfloat16* dOg = reinterpret_cast<const __nv_bfloat16*>(p.d_o);
     const __nv_bfloat16* Vg = reinterpret_cast<const __nv_bfloat16*>(p.v);
-    float* scr = p.scratch + tile_idx * (size_t)BWD_SCRATCH_FLOATS;
+    // staging role: token row and 8 value columns (of the 64 of a half)
+    const int srow = tid >> 3, sc8 = tid & 7;
 
-    // A (fp32 [64][64]) and beta once. The staging loops are unrolled so that all loads of a thread are in flight
-    // together (rolled, every iteration pays a full memory latency before its conversions and stores).
-#pragma unroll
-    for (int i = tid; i < 64 * 16; i += BD_THREADS) {
-        const int row = i >> 4, c4 = (i & 15) * 4;
-        const float4 a = *reinterpret_cast<const float4*>(p.akk + tile_idx * 4096 + row * 64 + c4);
-        *reinterpret_cast<float4*>(sm + BD_A + row * PR + c4) = make_float4(tf32r(a.x), tf32r(a.y), tf32r(a.z), tf32r(a.w));
+    if (tid == 0) {
+        for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+        *sAbort = 0;
+        fence_mbar_init();
     }
-    if (tid < 64) {
-        float b = 0.f;
-        if (tid < ci.valid) {
-            size_t bi = (size_t)(ci.row0 + tid) * p.H + h;
-            b = p.beta_fp32 ? reinterpret_cast<const float*>(p.beta)[bi]
-                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[bi]);
-            if (p.beta_logit) b = __fdividef(1.f, 1.f + __expf(-b));
-        }
-        sm[BD_BETA + tid] = b;
-    }
+    if (warp == 0) umma::tmem_alloc(tmem_slot, 512);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
 
-    float accQ[BD_NT128][4], accW[BD_NT128][4], accK[BD_NT128][4], accP[BD_NT64][4], accA[BD_NT64][4];
+    // ---- helpers ----
+    auto issue_state_loads = [&](int t_id, int vh) {        // one thread: one value half of S and dS' of a tile
+        mbar_arrive_expect_tx(&bars[vh], BD_HALF_TX);
 #pragma unroll
-    for (int i = 0; i < BD_NT128; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) accQ[i][e] = accW[i][e] = accK[i][e] = 0.f;
-#pragma unroll
-    for (int i = 0; i < BD_NT64; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) accP[i][e] = accA[i][e] = 0.f;
-    float dD_part = 0.f, dbu0 = 0.f, dbu1 = 0.f;     // dD for row k = tid / BD_NQ (a column slice per thread); dbeta_u for rows 16mt+g, +8
-
-    for (int vh = 0; vh < 2; ++vh) {
-        __syncthreads();        // previous half's fragments are no longer read
-        // ---- stage this value half ----
-#pragma unroll
-        for (int i = tid; i < 128 * 16; i += BD_THREADS) {
-            const int row = i >> 4, c4 = (i & 15) * 4;
-            const float4 a = *reinterpret_cast<const float4*>(Sg + row * DV + vh * 64 + c4);
-            const float4 b = *reinterpret_cast<const float4*>(dSg + row * DV + vh * 64 + c4);
-            *reinterpret_cast<float4*>(sm + BD_S + row * PR + c4) = make_float4(tf32r(a.x), tf32r(a.y), tf32r(a.z), tf32r(a.w));
-            *reinterpret_cast<float4*>(sm + BD_DS + row * PR + c4) = make_float4(tf32r(b.x), tf32r(b.y), tf32r(b.z), tf32r(b.w));
+        for (int a = 0; a < 2; ++a) {
+            tma_load_2d(smb + BD_S + vh * 32768 + a * 16384, &map_s, vh * 64 + a * 32, t_id * 128, &bars[vh]);
+            tma_load_2d(smb + BD_DS + vh * 32768 + a * 16384, &map_ds, vh * 64 + a * 32, t_id * 128, &bars[vh]);
         }
-        for (int i = tid; i < 64 * 8; i += BD_THREADS) {
-            const int row = i >> 3, c8 = (i & 7) * 8;
-            uint4 ro = make_uint4(0, 0, 0, 0), rv = make_uint4(0, 0, 0, 0);
-            if (row < ci.valid) {
-                ro = *reinterpret_cast<const uint4*>(dOg + base + (size_t)row * tok_stride + vh * 64 + c8);
-                rv = *reinterpret_cast<const uint4*>(Vg + base + (size_t)row * tok_stride + vh * 64 + c8);
-            }
-            const uint4 rn = *reinterpret_cast<const uint4*>(Vng + row * DV + vh * 64 + c8);
-            const uint4 rd = *reinterpret_cast<const uint4*>(dVng + row * DV + vh * 64 + c8);
-            const uint32_t wo[4] = {ro.x, ro.y, ro.z, ro.w}, wv[4] = {rv.x, rv.y, rv.z, rv.w};
-            const uint32_t wn[4] = {rn.x, rn.y, rn.z, rn.w}, wd[4] = {rd.x, rd.y, rd.z, rd.w};
+    };
+    auto fetch_stage = [&](int t_id, const ChunkInfo& ci, int h, int vh) -> BdStage {
+        BdStage s;
+        const int row = min(srow, ci.valid - 1);     // a padding row re-reads the last real row and is zeroed below
+        const size_t goff = (size_t)(ci.row0 + row) * tok_stride + (size_t)h * DV + vh * 64 + sc8 * 8;
+        s.o = *reinterpret_cast<const uint4*>(dOg + goff);
+        s.v = *reinterpret_cast<const uint4*>(Vg + goff);
+        const size_t toff = (size_t)t_id * (BT * DV) + srow * DV + vh * 64 + sc8 * 8;
+        s.vn = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.vnew) + toff);
+        s.dvn = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.dvn) + toff);
+        return s;
+    };
+    // widen 8 values to fp32 and store them as two 16-byte groups of an fp32 K-major atom pair
+    auto put8 = [&](int base, int row, float scale, const uint4& raw, bool is_bf16) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        float f[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float2 f = unpack_bf16(wo[e]);
-                sm[BD_DO + row * PR + c8 + 2 * e] = tf32r(gs * f.x);
-                sm[BD_DO + row * PR + c8 + 2 * e + 1] = tf32r(gs * f.y);
-                f = unpack_bf16(wv[e]);
-                sm[BD_V + row * PR + c8 + 2 * e] = tf32r(f.x);
-                sm[BD_V + row * PR + c8 + 2 * e + 1] = tf32r(f.y);
-                f = unpack_f16(wn[e]);
-                sm[BD_VN + row * PR + c8 + 2 * e] = tf32r(f.x);
-                sm[BD_VN + row * PR + c8 + 2 * e + 1] = tf32r(f.y);
-                f = unpack_f16(wd[e]);
-                sm[BD_DVN + row * PR + c8 + 2 * e] = tf32r(f.x);
-                sm[BD_DVN + row * PR + c8 + 2 * e + 1] = tf32r(f.y);
+        for (int e = 0; e < 4; ++e) {
+            const float2 x = is_bf16 ? unpack_bf16(w[e]) : unpack_f16(w[e]);
+            f[2 * e] = scale * x.x;
+            f[2 * e + 1] = scale * x.y;
+        }
+        unsigned char* atom = sm + base + (sc8 >> 2) * 16384;
+        const int ch = (sc8 & 3) * 2;
+        *reinterpret_cast<float4*>(atom + atom_off(row, ch)) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(atom + atom_off(row, ch + 1)) = make_float4(f[4], f[5], f[6], f[7]);
+    };
+    auto store_stage = [&](const BdStage& s, bool real_row) {
+        put8(BD_A1, srow, real_row ? gs : 0.f, s.o, true);          // dO (units of the gradient scale)
+        put8(BD_A1, srow + 64, 1.f, s.dvn, false);                   // dVn
+        put8(BD_VNV, srow, 1.f, s.vn, false);                        // Vn
+        put8(BD_VNV, srow + 64, real_row ? 1.f : 0.f, s.v, true);    // V
+        *reinterpret_cast<uint4*>(sm + BD_B4 + atom_off(srow, sc8)) = s.dvn;
+    };
+    // One thread waits (bounded) for an mbarrier; everybody else parks on the CTA barrier.
+    auto cta_wait = [&](int which, uint32_t parity) -> bool {
+        if (tid == 0) {
+            if (!*sAbort && !mbar_wait(&bars[which], parity)) {
+                atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+                *sAbort = 1;
             }
+            umma::fence_before_sync();
         }
         __syncthreads();
-        // next tile of this CTA: pull its inputs into L2 while the second half computes
-        if (vh == 1 && next_tile >= 0) {
-            const size_t nt_idx = (size_t)next_tile;
-            const int cn = next_tile / p.H, hn = next_tile - cn * p.H;
-            const ChunkInfo cin = chunk_info(cn, p.cu_seqlens, p.chunk_indices, p.T);
-            const size_t nb = (size_t)cin.row0 * tok_stride + (size_t)hn * DV;
-            for (int i = tid; i < 512; i += BD_THREADS) {     // S and dS': 64 KB each, 128-byte lines
-                prefetch_l2(p.h32 + nt_idx * (size_t)(DK * DV) + 32 * i);
-                prefetch_l2(p.ds + nt_idx * (size_t)(DK * DV) + 32 * i);
+        umma::fence_after_sync();
+        return *sAbort == 0;
+    };
+
+    // ---- prologue: first tile's loads ----
+    int tile = blockIdx.x;
+    int h = 0;
+    ChunkInfo ci{};
+    BdStage st{};
+    float4 a_lo = make_float4(0, 0, 0, 0), a_hi = a_lo;
+    uint32_t beta_raw = 0;
+    auto fetch_tile_top = [&](int t_id) {       // geometry, A, beta (raw bits) and the first value half of a tile
+        const int c = t_id / p.H;
+        h = t_id - c * p.H;
+        ci = chunk_info(c, p.cu_seqlens, p.chunk_indices, p.T);
+        st = fetch_stage(t_id, ci, h, 0);
+        const float* ag = p.akk + (size_t)t_id * 4096 + srow * 64 + sc8 * 8;
+        a_lo = *reinterpret_cast<const float4*>(ag);
+        a_hi = *reinterpret_cast<const float4*>(ag + 4);
+        if (tid < 64) {
+            const size_t bi = (size_t)(ci.row0 + min(tid, ci.valid - 1)) * p.H + h;
+            beta_raw = p.beta_fp32 ? reinterpret_cast<const uint32_t*>(p.beta)[bi]
+                                   : (uint32_t)reinterpret_cast<const unsigned short*>(p.beta)[bi] << 16;
+        }
+    };
+    bool issued1 = false;                       // thread 0: the loads of value half 1 of the current tile have been issued
+    if (tile < num_tiles) {
+        if (tid == 0) {
+            issue_state_loads(tile, 0);
+            issue_state_loads(tile, 1);
+            issued1 = true;
+        }
+        fetch_tile_top(tile);
+    }
+
+    const uint32_t idesc_tf32 = umma::make_idesc(umma::FMT_TF32, 128, 128, false, false);
+    const uint32_t idesc_zu = umma::make_idesc(umma::FMT_F16, 128, 64, true, true);
+    uint32_t par = 0;
+    // dD role (warps 1-15; warp 0 issues the MMAs instead): item = (state row k, 16-byte group) of 1024 per value half
+    const int dd_idx = tid - 32;
+
+#ifdef KDA_PHASE_TIMERS
+    long long bd_t0_ = clock64();
+#endif
+    for (; tile < num_tiles; tile += gridDim.x, par ^= 1u) {
+        const int next = tile + gridDim.x;
+        const ChunkInfo cur = ci;
+        const int cur_h = h;
+        float dD_part[3] = {0.f, 0.f, 0.f};
+        // ---- stage A, beta and the first value half. The previous tile's MMAs have completed and its first group of
+        //      output stores has been read out of the staging buffers (checked before its last barrier) ----
+        {
+            const uint4 a16 = make_uint4(pack_f16(a_lo.x, a_lo.y), pack_f16(a_lo.z, a_lo.w), pack_f16(a_hi.x, a_hi.y),
+                                         pack_f16(a_hi.z, a_hi.w));
+            *reinterpret_cast<uint4*>(sm + BD_A4 + atom_off(srow, sc8)) = a16;
+            *reinterpret_cast<uint4*>(sm + BD_A4 + 8192 + atom_off(srow, sc8)) = a16;
+            if (tid < 64) {
+                float b = __uint_as_float(beta_raw);
+                if (p.beta_logit) b = __fdividef(1.f, 1.f + __expf(-b));
+                sBeta[tid] = tid < cur.valid ? b : 0.f;
             }
-            if (tid < 128) {
-                prefetch_l2(reinterpret_cast<const __half*>(p.vnew) + nt_idx * (size_t)(BT * DV) + 64 * tid);
-                prefetch_l2(reinterpret_cast<const __half*>(p.dvn) + nt_idx * (size_t)(BT * DV) + 64 * tid);
-                prefetch_l2(p.akk + nt_idx * 4096 + 32 * tid);
-            } else if (tid < 256) {
-                const int row = (tid - 128) >> 1, half = tid & 1;
-                if (row < cin.valid) {
-                    prefetch_l2(dOg + nb + (size_t)row * tok_stride + 64 * half);
-                    prefetch_l2(Vg + nb + (size_t)row * tok_stride + 64 * half);
+        }
+#pragma unroll 1
+        for (int vh = 0; vh < 2; ++vh) {
+            store_stage(st, srow < cur.valid);
+            fence_proxy_async();
+            __syncthreads();
+            BD_MARK(0 + 6 * vh);      // operands widened into shared memory
+            // operands of the next stage into registers: the second half of this tile, or the top of the next tile
+            if (vh == 0) st = fetch_stage(tile, cur, cur_h, 1);
+            else if (next < num_tiles) fetch_tile_top(next);
+            BD_MARK(1 + 6 * vh);      // next operands requested
+            // ---- one thread: wait for the states of this half, issue the MMAs ----
+            if (tid == 0) {
+                if (vh == 0 && !issued1) {
+                    // the second output group of the previous tile was staged in the half-1 state buffers
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    issue_state_loads(tile, 1);
+                    issued1 = true;
+                }
+                if (!mbar_wait(&bars[vh], par)) {
+                    atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+                    *sAbort = 1;
+                } else {
+                    BD_MARK(2 + 6 * vh);      // wait for the states of this half
+                    umma::fence_after_sync();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t koff = (uint32_t)((ks >> 2) * 16384 + (ks & 3) * 32);
+                        const uint64_t a1 = bd_sdesc(smb + BD_A1 + koff, 16, 1024);
+                        const uint64_t vnv = bd_sdesc(smb + BD_VNV + koff, 16, 1024);
+                        const uint64_t sd = bd_sdesc(smb + BD_S + vh * 32768 + koff, 16, 1024);
+                        const uint64_t dsd = bd_sdesc(smb + BD_DS + vh * 32768 + koff, 16, 1024);
+                        const uint32_t acc = (vh | ks) != 0;
+                        umma::mma_tf32(tmem + TC_D1, a1, sd, idesc_tf32, acc);
+                        umma::mma_tf32(tmem + TC_D2, vnv, dsd, idesc_tf32, acc);
+                        umma::mma_tf32(tmem + TC_D3, a1, vnv, idesc_tf32, acc);
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t a4 = bd_sdesc(smb + BD_A4 + ks * 2048, 8192, 1024);
+                        const uint64_t b4 = bd_sdesc(smb + BD_B4 + ks * 2048, 8192, 1024);
+                        umma::mma_f16(tmem + TC_D4 + vh * 64, a4, b4, idesc_zu, ks != 0);
+                    }
+                    umma::commit(&bars[2 + vh]);
+                    BD_MARK(3 + 6 * vh);      // MMA issue
+                }
+            } else if (warp != 0) {
+                // ---- dD partial of this half from the fp32 states in shared memory, under the MMAs ----
+                if (!mbar_wait(&bars[vh], par)) {
+                    atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+                    *sAbort = 1;
+                }
+#pragma unroll
+                for (int n = 0; n < 3; ++n) {
+                    const int item = dd_idx + 480 * n;
+                    if (item < 1024) {
+                        const int k = item >> 3;
+                        const uint32_t off = vh * 32768 + atom_off(k, item & 7);
+                        float acc = 0.f;
+#pragma unroll
+                        for (int a = 0; a < 2; ++a) {
+                            const float4 x = *reinterpret_cast<const float4*>(sm + BD_S + a * 16384 + off);
+                            const float4 y = *reinterpret_cast<const float4*>(sm + BD_DS + a * 16384 + off);
+                            acc = fmaf(x.x, y.x, fmaf(x.y, y.y, fmaf(x.z, y.z, fmaf(x.w, y.w, acc))));
+                        }
+                        dD_part[n] += acc;
+                    }
                 }
             }
+            BD_MARK(4 + 6 * vh);          // (thread 0: nothing)
+            if (!cta_wait(2 + vh, par)) break;
+            BD_MARK(5 + 6 * vh);          // wait for the MMAs
         }
-        // ---- dD partial: row k = tid ----
+        if (*sAbort) break;
+        // ---- the half-0 state buffers are free: the next tile's first loads run under the epilogue ----
+        if (tid == 0) {
+            issued1 = false;
+            if (next < num_tiles) issue_state_loads(next, 0);
+        }
+        // ---- epilogue: TMEM -> registers -> swizzled staging buffers -> TMA tensor stores into the scratch record ----
         {
-            const int row = tid / BD_NQ, v0 = (tid % BD_NQ) * (64 / BD_NQ);
-            float a = 0.f;
-#pragma unroll 8
-            for (int v = 0; v < 64 / BD_NQ; ++v) {
-                const int vv = v0 + ((v + row) & (64 / BD_NQ - 1));      // rotated start: spreads the banks
-                a = fmaf(sm[BD_S + row * PR + vv], sm[BD_DS + row * PR + vv], a);
-            }
-            dD_part += a;
-        }
-        // ---- contraction over the 64 value columns of this half ----
-        // tf32 fragments come from ldmatrix: an 8 x 8 b16 tile is an 8 x 4 tile of 32-bit words, and lane l receives
-        // word (row l / 4, column l % 4) -- exactly the m16n8k8 tf32 fragment layout. One x4 load fetches a whole
-        // A fragment (rows 0-7 / 8-15 x words 0-3 / 4-7) or the B fragments of two n-tiles.
-        const uint32_t sm_u32 = smem_u32(sm);
-        const int lr = lane & 7, lm = lane >> 3;
-        const uint32_t a_off = (uint32_t)(((16 * mt + lr + 8 * (lm & 1)) * PR + 4 * (lm >> 1)) * 4);   // + k0 * 4
-        const uint32_t b_off = (uint32_t)(((lr + 8 * (lm >> 1)) * PR + 4 * (lm & 1)) * 4);              // + (n0 * PR + k0) * 4
-#pragma unroll 2
-        for (int ks = 0; ks < 8; ++ks) {
-            const int k0 = 8 * ks;
-            float fO[4], fV[4], fD[4];
-            ldsm_x4(sm_u32 + BD_DO * 4 + a_off + k0 * 4, reinterpret_cast<uint32_t&>(fO[0]), reinterpret_cast<uint32_t&>(fO[1]),
-                    reinterpret_cast<uint32_t&>(fO[2]), reinterpret_cast<uint32_t&>(fO[3]));
-            ldsm_x4(sm_u32 + BD_VN * 4 + a_off + k0 * 4, reinterpret_cast<uint32_t&>(fV[0]), reinterpret_cast<uint32_t&>(fV[1]),
-                    reinterpret_cast<uint32_t&>(fV[2]), reinterpret_cast<uint32_t&>(fV[3]));
-            ldsm_x4(sm_u32 + BD_DVN * 4 + a_off + k0 * 4, reinterpret_cast<uint32_t&>(fD[0]), reinterpret_cast<uint32_t&>(fD[1]),
-                    reinterpret_cast<uint32_t&>(fD[2]), reinterpret_cast<uint32_t&>(fD[3]));
-#pragma unroll
-            for (int np = 0; np < BD_NT128 / 2; ++np) {
-                const int n0 = 8 * BD_NT128 * nh + 16 * np;      // key channels n0 .. n0 + 15
-                float s[4], d[4];
-                ldsm_x4(sm_u32 + (BD_S + n0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(s[0]), reinterpret_cast<uint32_t&>(s[1]),
-                        reinterpret_cast<uint32_t&>(s[2]), reinterpret_cast<uint32_t&>(s[3]));
-                ldsm_x4(sm_u32 + (BD_DS + n0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(d[0]), reinterpret_cast<uint32_t&>(d[1]),
-                        reinterpret_cast<uint32_t&>(d[2]), reinterpret_cast<uint32_t&>(d[3]));
-                mma_tf32(accQ[2 * np], fO, s[0], s[1]);
-                mma_tf32(accW[2 * np], fD, s[0], s[1]);
-                mma_tf32(accK[2 * np], fV, d[0], d[1]);
-                mma_tf32(accQ[2 * np + 1], fO, s[2], s[3]);
-                mma_tf32(accW[2 * np + 1], fD, s[2], s[3]);
-                mma_tf32(accK[2 * np + 1], fV, d[2], d[3]);
-            }
-            static_assert(BD_NT64 == 2 && BD_NT128 % 2 == 0, "fragment pairing below assumes two token n-tiles per warp");
+            float* scr = p.scratch + (size_t)tile * BWD_SCRATCH_FLOATS;
+            const int q = warp & 3, cg = warp >> 2;
+            const int i = 32 * (q & 1) + lane;                       // token row of this thread
+            const bool upper = q < 2;                                // TMEM lanes 0-63
+            const uint32_t tl = tmem + ((uint32_t)(32 * q) << 16);
+            uint32_t r[16];
+            // D1: dQg (lanes 0-63) / -dW (lanes 64-127), 32 of the 128 key channels per warp -> boxes in the [dO; dVn] / [Vn; V] buffers
             {
-                const int j0 = 8 * BD_NT64 * nh;                  // token columns j0 .. j0 + 15
-                float vn[4], vv[4];
-                ldsm_x4(sm_u32 + (BD_VN + j0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(vn[0]), reinterpret_cast<uint32_t&>(vn[1]),
-                        reinterpret_cast<uint32_t&>(vn[2]), reinterpret_cast<uint32_t&>(vn[3]));
-                ldsm_x4(sm_u32 + (BD_V + j0 * PR + k0) * 4 + b_off, reinterpret_cast<uint32_t&>(vv[0]), reinterpret_cast<uint32_t&>(vv[1]),
-                        reinterpret_cast<uint32_t&>(vv[2]), reinterpret_cast<uint32_t&>(vv[3]));
-                mma_tf32(accP[0], fO, vn[0], vn[1]);
-                mma_tf32(accA[0], fD, vv[0], vv[1]);
-                mma_tf32(accP[1], fO, vn[2], vn[3]);
-                mma_tf32(accA[1], fD, vv[2], vv[3]);
+                unsigned char* box = sm + BD_A1 + ((upper ? 0 : 4) + cg) * 8192;
+                const float f = upper ? TF32_TRUNC_COMP : -TF32_TRUNC_COMP;
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    umma::ld_32x32b_x16(tl + TC_D1 + 32 * cg + 16 * part, r);
+                    umma::wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        *reinterpret_cast<float4*>(box + atom_off(i, 4 * part + e)) =
+                            make_float4(f * __uint_as_float(r[4 * e]), f * __uint_as_float(r[4 * e + 1]),
+                                        f * __uint_as_float(r[4 * e + 2]), f * __uint_as_float(r[4 * e + 3]));
+                }
+            }
+            fence_proxy_async();
+            __syncthreads();
+            if (tid == 0) {
+#pragma unroll
+                for (int b = 0; b < 8; ++b)
+                    tma_store_3d(&map_out128, smb + BD_A1 + b * 8192, 32 * (b & 3), 64 * (b >> 2), tile);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            BD_MARK(12);                  // dQg, dW staged and their stores issued
+            // D2: dKg (lanes 0-63 only) -> boxes in the half-1 buffer of S
+            if (upper) {
+                unsigned char* box = sm + BD_S + 32768 + cg * 8192;
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    umma::ld_32x32b_x16(tl + TC_D2 + 32 * cg + 16 * part, r);
+                    umma::wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        *reinterpret_cast<float4*>(box + atom_off(i, 4 * part + e)) =
+                            make_float4(TF32_TRUNC_COMP * __uint_as_float(r[4 * e]), TF32_TRUNC_COMP * __uint_as_float(r[4 * e + 1]),
+                                        TF32_TRUNC_COMP * __uint_as_float(r[4 * e + 2]), TF32_TRUNC_COMP * __uint_as_float(r[4 * e + 3]));
+                }
+            }
+            // D3: dPs = tril(dO Vn^T) (lanes 0-63, columns 0-63) / dAu = stril(dVn V^T) beta_j (lanes 64-127, columns 64-127)
+            //     -> boxes in the half-1 buffer of dS'
+            {
+                const int j0 = 16 * cg;
+                umma::ld_32x32b_x16(tl + TC_D3 + (upper ? 0 : 64) + j0, r);
+                umma::wait_ld();
+                unsigned char* box = sm + BD_DS + 32768 + ((upper ? 0 : 2) + (cg >> 1)) * 8192;
+                float o[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int j = j0 + e;
+                    const float x = __uint_as_float(r[e]);
+                    o[e] = upper ? (j <= i ? x : 0.f) : (j < i ? sBeta[j] * x : 0.f);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    *reinterpret_cast<float4*>(box + atom_off(i, (cg & 1) * 4 + e)) = make_float4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
+            }
+            // D4: Zu (both lane halves hold it): lanes 0-63 take value columns 0-63, lanes 64-127 columns 64-127
+            {
+                const int v0 = (upper ? 0 : 64) + 16 * cg;
+                umma::ld_32x32b_x16(tl + TC_D4 + v0, r);
+                umma::wait_ld();
+                float dbu = 0.f;
+                if (i < cur.valid) {
+                    const size_t goff = (size_t)(cur.row0 + i) * tok_stride + (size_t)cur_h * DV + v0;
+                    const uint4 v_lo = *reinterpret_cast<const uint4*>(Vg + goff);
+                    const uint4 v_hi = *reinterpret_cast<const uint4*>(Vg + goff + 8);
+                    const uint32_t vw[8] = {v_lo.x, v_lo.y, v_lo.z, v_lo.w, v_hi.x, v_hi.y, v_hi.z, v_hi.w};
+                    const float bsc = gs_inv * sBeta[i];
+                    uint32_t out[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float2 vv = unpack_bf16(vw[e]);
+                        const float z0 = __uint_as_float(r[2 * e]), z1 = __uint_as_float(r[2 * e + 1]);
+                        dbu = fmaf(z0, vv.x, fmaf(z1, vv.y, dbu));
+                        out[e] = pack_bf16(bsc * z0, bsc * z1);
+                    }
+                    __nv_bfloat16* dvp = reinterpret_cast<__nv_bfloat16*>(p.dv) + goff;
+                    *reinterpret_cast<uint4*>(dvp) = make_uint4(out[0], out[1], out[2], out[3]);
+                    *reinterpret_cast<uint4*>(dvp + 8) = make_uint4(out[4], out[5], out[6], out[7]);
+                }
+                sRed[((upper ? 0 : 4) + cg) * 64 + i] = dbu;
+            }
+            // dD: the eight 16-byte groups of a state row sit in adjacent lanes
+            if (warp != 0) {
+#pragma unroll
+                for (int n = 0; n < 3; ++n) {
+                    const int item = dd_idx + 480 * n;
+                    if (item < 1024) {            // uniform per warp
+                        float v = dD_part[n];
+                        v += __shfl_xor_sync(0xffffffffu, v, 1);
+                        v += __shfl_xor_sync(0xffffffffu, v, 2);
+                        v += __shfl_xor_sync(0xffffffffu, v, 4);
+                        if ((item & 7) == 0) scr[SCR_DD + (item >> 3)] = v;
+                    }
+                }
+            }
+            BD_MARK(13);                  // dKg, dPs, dAu staged; dv stored
+            // the first group of stores must have been read out before the next tile's operands overwrite its buffers
+            if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            fence_proxy_async();
+            umma::fence_before_sync();
+            __syncthreads();          // TMEM, the staging buffers and the dbeta_u partials are complete / free
+            umma::fence_after_sync();
+            if (tid == 0) {
+#pragma unroll
+                for (int b = 0; b < 4; ++b) tma_store_3d(&map_out128, smb + BD_S + 32768 + b * 8192, 32 * b, 128, tile);
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    tma_store_3d(&map_out64, smb + BD_DS + 32768 + b * 8192, 32 * (b & 1), 64 * (b >> 1), tile);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            if (tid < 64) {
+                float v = 0.f;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) v += sRed[x * 64 + tid];
+                scr[SCR_DBU + tid] = v;
             }
         }
-        // ---- Zu = A^T dVn_h : [64 i] x [64 v of this half], contraction over the 64 tokens j ----
-        float accZ[BD_NT64][4];
-#pragma unroll
-        for (int i = 0; i < BD_NT64; ++i)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) accZ[i][e] = 0.f;
-#pragma unroll 2
-        for (int ks = 0; ks < 8; ++ks) {
-            const int j0 = 8 * ks, i0 = 16 * mt;
-            const float fA[4] = {sm[BD_A + (j0 + t) * PR + i0 + g], sm[BD_A + (j0 + t) * PR + i0 + g + 8],
-                                 sm[BD_A + (j0 + t + 4) * PR + i0 + g], sm[BD_A + (j0 + t + 4) * PR + i0 + g + 8]};
-#pragma unroll
-            for (int nt = 0; nt < BD_NT64; ++nt) {
-                const int v0 = 8 * BD_NT64 * nh + 8 * nt;
-                mma_tf32(accZ[nt], fA, sm[BD_DVN + (j0 + t) * PR + v0 + g], sm[BD_DVN + (j0 + t + 4) * PR + v0 + g]);
-            }
-        }
-        {   // dv = beta * Zu (true units), dbeta_u += rowsum(Zu * V)
-            const int r0 = 16 * mt + g, r1 = r0 + 8;
-            const float b0 = sm[BD_BETA + r0], b1 = sm[BD_BETA + r1];
-            __nv_bfloat16* dvp = reinterpret_cast<__nv_bfloat16*>(p.dv);
-#pragma unroll
-            for (int nt = 0; nt < BD_NT64; ++nt) {
-                const int vc = 8 * BD_NT64 * nh + 8 * nt + 2 * t;
-                dbu0 += accZ[nt][0] * sm[BD_V + r0 * PR + vc] + accZ[nt][1] * sm[BD_V + r0 * PR + vc + 1];
-                dbu1 += accZ[nt][2] * sm[BD_V + r1 * PR + vc] + accZ[nt][3] * sm[BD_V + r1 * PR + vc + 1];
-                if (r0 < ci.valid)
-                    *reinterpret_cast<uint32_t*>(dvp + base + (size_t)r0 * tok_stride + vh * 64 + vc) =
-                        pack_bf16(gs_inv * b0 * accZ[nt][0], gs_inv * b0 * accZ[nt][1]);
-                if (r1 < ci.valid)
-                    *reinterpret_cast<uint32_t*>(dvp + base + (size_t)r1 * tok_stride + vh * 64 + vc) =
-                        pack_bf16(gs_inv * b1 * accZ[nt][2], gs_inv * b1 * accZ[nt][3]);
-            }
-        }
+        BD_MARK(14);                      // end-of-tile barrier, second group of stores issued
     }
-    // ---- write the scratch record (units of gs) ----
-    {
-        const int r0 = 16 * mt + g, r1 = r0 + 8;
-#pragma unroll
-        for (int nt = 0; nt < BD_NT128; ++nt) {
-            const int col = 8 * BD_NT128 * nh + 8 * nt + 2 * t;
-            *reinterpret_cast<float2*>(scr + SCR_DQG + r0 * DK + col) = make_float2(accQ[nt][0], accQ[nt][1]);
-            *reinterpret_cast<float2*>(scr + SCR_DQG + r1 * DK + col) = make_float2(accQ[nt][2], accQ[nt][3]);
-            *reinterpret_cast<float2*>(scr + SCR_DW + r0 * DK + col) = make_float2(-accW[nt][0], -accW[nt][1]);
-            *reinterpret_cast<float2*>(scr + SCR_DW + r1 * DK + col) = make_float2(-accW[nt][2], -accW[nt][3]);
-            *reinterpret_cast<float2*>(scr + SCR_DKG + r0 * DK + col) = make_float2(accK[nt][0], accK[nt][1]);
-            *reinterpret_cast<float2*>(scr + SCR_DKG + r1 * DK + col) = make_float2(accK[nt][2], accK[nt][3]);
+    // ---- unwind: copies in flight must land / be read out before the CTA's shared memory goes away ----
+    if (tid == 0) {
+        if (*sAbort) {
+            mbar_wait(&bars[0], par);
+            if (issued1) mbar_wait(&bars[1], par);
         }
-#pragma unroll
-        for (int nt = 0; nt < BD_NT64; ++nt) {
-            const int col = 8 * BD_NT64 * nh + 8 * nt + 2 * t;
-            const float bj0 = sm[BD_BETA + col], bj1 = sm[BD_BETA + col + 1];
-            float p00 = (col <= r0) ? accP[nt][0] : 0.f, p01 = (col + 1 <= r0) ? accP[nt][1] : 0.f;
-            float p10 = (col <= r1) ? accP[nt][2] : 0.f, p11 = (col + 1 <= r1) ? accP[nt][3] : 0.f;
-            float a00 = (col < r0) ? bj0 * accA[nt][0] : 0.f, a01 = (col + 1 < r0) ? bj1 * accA[nt][1] : 0.f;
-            float a10 = (col < r1) ? bj0 * accA[nt][2] : 0.f, a11 = (col + 1 < r1) ? bj1 * accA[nt][3] : 0.f;
-            *reinterpret_cast<float2*>(scr + SCR_DPS + r0 * BT + col) = make_float2(p00, p01);
-            *reinterpret_cast<float2*>(scr + SCR_DPS + r1 * BT + col) = make_float2(p10, p11);
-            *reinterpret_cast<float2*>(scr + SCR_DAU + r0 * BT + col) = make_float2(a00, a01);
-            *reinterpret_cast<float2*>(scr + SCR_DAU + r1 * BT + col) = make_float2(a10, a11);
-        }
-        // dbeta_u: reduce over the 4 lanes of a quad, then over the column groups through shared memory
-        dbu0 += __shfl_xor_sync(0xffffffffu, dbu0, 1); dbu0 += __shfl_xor_sync(0xffffffffu, dbu0, 2);
-        dbu1 += __shfl_xor_sync(0xffffffffu, dbu1, 1); dbu1 += __shfl_xor_sync(0xffffffffu, dbu1, 2);
-        if (t == 0) {
-            sm[BD_RED + nh * 64 + r0] = dbu0;
-            sm[BD_RED + nh * 64 + r1] = dbu1;
-        }
-        __syncthreads();
-        if (tid < 64) {
-            float v = 0.f;
-#pragma unroll
-            for (int x = 0; x < BD_NQ; ++x) v += sm[BD_RED + x * 64 + tid];
-            scr[SCR_DBU + tid] = v;
-        }
-#pragma unroll
-        for (int o = 1; o < BD_NQ; o <<= 1) dD_part += __shfl_xor_sync(0xffffffffu, dD_part, o);
-        if (tid % BD_NQ == 0) scr[SCR_DD + tid / BD_NQ] = dD_part;
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
-}
-
-// Persistent: CTA b handles tiles b, b + gridDim.x, ... so that the next tile's inputs can be prefetched.
-__global__ void __launch_bounds__(BD_THREADS, 1) kda_bwd_dense_kernel(const BwdDenseParams p, const int num_tiles) {
-    extern __shared__ __align__(16) float sm[];
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int next = tile + gridDim.x;
-        bd_tile(p, sm, tile, next < num_tiles ? next : -1);
-        __syncthreads();                                  // shared memory is reused by the next tile
-    }
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 512);
 }
 
 }  // namespace kda
+
+#ifdef KDA_PHASE_TIMERS
+extern "C" int kda_bwd_dense_read_timers(unsigned long long* out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, kda_bwd_dense_timers, sizeof(kda_bwd_dense_timers));
+    if (e == cudaSuccess && reset) {
+        unsigned long long z[16] = {};
+        e = cudaMemcpyToSymbol(kda_bwd_dense_timers, z, sizeof(z));
+    }
+    return (int)e;
+}
+#endif
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// fp32 [tiles * 128 rows][128 columns], fetched as boxes of 32 columns x 128 rows with the 128-byte swizzle
+bool make_state_map(CUtensorMap* map, const float* base, int tiles) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {128, (cuuint64_t)tiles * 128};
+    const cuuint64_t strides[1] = {128 * sizeof(float)};
+    const cuuint32_t box[2] = {32, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The scratch record as a rank-3 tensor [tiles][rows][cols] of fp32, stored from boxes of 32 columns x 64 rows with the
+// 128-byte swizzle. first_float: offset of the first matrix inside a record; rows: number of 64-row matrices x 64.
+bool make_scratch_map(CUtensorMap* map, float* scratch, int first_float, int cols, int rows, int tiles) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)tiles};
+    const cuuint64_t strides[2] = {cols * sizeof(float), kda::BWD_SCRATCH_FLOATS * sizeof(float)};
+    const cuuint32_t box[3] = {32, 64, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, scratch + first_float, dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
 
 extern "C" int kda_launch_bwd_dense(const kda::BwdDenseParams* p, int num_chunks, cudaStream_t stream) {
     using namespace kda;
@@ -314,6 +519,15 @@ extern "C" int kda_launch_bwd_dense(const kda::BwdDenseParams* p, int num_chunks
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = num_chunks * p->H;
-    kda_bwd_dense_kernel<<<tiles < sms ? tiles : sms, BD_THREADS, BD_SMEM, stream>>>(*p, tiles);
+    static_assert(SCR_DW == SCR_DQG + 64 * 128 && SCR_DKG == SCR_DW + 64 * 128 && SCR_DAU == SCR_DPS + 64 * 64,
+                  "the tensor maps below address dQg | dW | dKg and dPs | dAu as stacked matrices");
+    static_assert((BWD_SCRATCH_FLOATS * 4) % 16 == 0 && (SCR_DPS * 4) % 16 == 0, "TMA strides and bases are 16-byte multiples");
+    CUtensorMap map_s, map_ds, map_out128, map_out64;
+    if (!make_state_map(&map_s, p->h32, tiles) || !make_state_map(&map_ds, p->ds, tiles) ||
+        !make_scratch_map(&map_out128, p->scratch, SCR_DQG, 128, 192, tiles) ||
+        !make_scratch_map(&map_out64, p->scratch, SCR_DPS, 64, 128, tiles))
+        return (int)cudaErrorInvalidValue;
+    kda_bwd_dense_kernel<<<tiles < sms ? tiles : sms, BD_THREADS, BD_SMEM, stream>>>(*p, tiles, map_s, map_ds, map_out128,
+                                                                                      map_out64);
     return (int)cudaGetLastError();
 }

@@ -104,6 +104,7 @@ struct BwdDenseParams {
     int H;
     int beta_fp32;
     int beta_logit;               // 1: beta holds the raw logits
+    int* status;                  // device status word (bounded waits)
 };
 
 struct BwdGatedParams {

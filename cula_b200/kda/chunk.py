@@ -196,7 +196,7 @@ def chunk_kda_bwd(q, k, v, g, beta, scale, initial_state, do, dht, cu_seqlens, c
     _native.check(lib.cula_kda_bwd_dense(saved["h32"].data_ptr(), ds.data_ptr(), saved["vnew"].data_ptr(), dvn.data_ptr(),
                                          do.data_ptr(), v.data_ptr(), beta.data_ptr(), _beta_flags(beta, beta_logit),
                                          saved["akk"].data_ptr(), work.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
-                                         cu_p, ci_p, num_chunks, T, H, stream), "cula_kda_bwd_dense")
+                                         cu_p, ci_p, num_chunks, T, H, status, stream), "cula_kda_bwd_dense")
     dq, dk = zeros(q.shape, dtype=q.dtype, device=dev), zeros(k.shape, dtype=k.dtype, device=dev)
     dg, dbeta = zeros(g.shape, dtype=g.dtype, device=dev), zeros(beta.shape, dtype=beta.dtype, device=dev)
     dA = torch.zeros(H, dtype=torch.float32, device=dev) if use_gate_in_kernel else None

@@ -1,4 +1,4 @@
-"""Per-phase cycle counts of the chunk-parallel forward kernel and of the gated backward kernel.
+"""Per-phase cycle counts of the chunk-parallel forward kernel and of the dense and gated backward kernels.
 
     python -m cula_b200.build --timers        # builds cula_b200/lib/libcula_kda_timers.so (-DKDA_PHASE_TIMERS)
     python -m cula_b200.phase_timers [B T H]  # on a B200; default 2 2048 32 (the headline forward configuration)
@@ -22,6 +22,11 @@ FWD_PHASES = ["gate activation", "barrier (group totals)", "in-warp scan, tables
               "MMA wait, half 0 (+ L2 hints)", "operand generation, half 1", "MMA wait, half 1",
               "Y staging + barrier", "triangular inverse", "Akk pack + W/U MMA issue", "W/U MMA wait", "W/U epilogue",
               "loads issued under the MMA wait", "Gram epilogue", "L2 norms, beta", "top of the tile (q/k loads issued)"]
+DENSE_PHASES = ["half 0: operands widened into smem", "half 0: next operands requested",
+                "half 0: store read-out + wait for the states (TMA)", "half 0: MMA issue", "-", "half 0: wait for the MMAs",
+                "half 1: operands widened into smem", "half 1: next operands requested", "half 1: wait for the states (TMA)",
+                "half 1: MMA issue", "-", "half 1: wait for the MMAs", "dQg, dW staged, stores issued",
+                "dKg, dPs, dAu staged, dv stored", "store read-out + end-of-tile barrier"]
 BWD_PHASES = ["loads, gate, norms", "cumulative sum", "stage dW, X", "dA", "T1, dL", "Zw + accumulator set-up", "L2 hints",
               "Gram VJP, row side", "Gram VJP, column side", "reverse cumulative sum", "gate VJP, dg", "L2-norm VJP, stores"]
 
@@ -56,11 +61,14 @@ def main():
                          initial_state=d["initial_state"], output_final_state=True, **kw)
         torch.cuda.synchronize()
         raw.kda_bwd_gated_read_timers(buf, 1)
+        raw.kda_bwd_dense_read_timers(buf, 1)
         o.backward(do)
         torch.cuda.synchronize()
         raw.kda_bwd_gated_read_timers(buf, 0)
         bwd = [x / tiles for x in buf]
-    for title, names, vals in (("kda_fwd_intra_kernel", FWD_PHASES, fwd), ("kda_bwd_gated_kernel", BWD_PHASES, bwd)):
+        raw.kda_bwd_dense_read_timers(buf, 0)
+        dense = [x / tiles for x in buf]
+    for title, names, vals in (("kda_fwd_intra_kernel", FWD_PHASES, fwd), ("kda_bwd_dense_kernel", DENSE_PHASES, dense), ("kda_bwd_gated_kernel", BWD_PHASES, bwd)):
         print(f"{title}: cycles per tile, B={B} T={T} H={H} ({tiles} tiles)")
         for n, v in zip(names, vals):
             print(f"  {n:38s} {v:9.0f}")

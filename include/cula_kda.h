@@ -129,13 +129,15 @@ int cula_kda_bwd_scan(const void* d_tiles, const void* d_do, const float* d_dht,
                       const int* d_cu_seqlens, const int* d_chunk_offsets, const int* d_seq_order,
                       int N, int T, int H, int* d_status, void* stream);
 
-/* Chunk-parallel dense products with the carried states; writes d_dv (bf16, final) and the scratch record.
- * Replaces the state-dependent half of chunk_kda_bwd_wy_dqkg_fused (cula/kda/chunk_bwd.py:557-574) and the dAqk
+/* Chunk-parallel dense products with the carried states (tcgen05 tensor cores; the fp32 states arrive through TMA
+ * tensor maps built per call from d_h32 / d_ds); writes d_dv (bf16, final) and the scratch record. d_status: device
+ * status word of the bounded waits. Replaces the state-dependent half of chunk_kda_bwd_wy_dqkg_fused (cula/kda/chunk_bwd.py:557-574) and the dAqk
  * half of chunk_kda_bwd_dAv. */
 int cula_kda_bwd_dense(const float* d_h32, const float* d_ds, const void* d_vnew, const void* d_dvn,
                        const void* d_do, const void* d_v, const void* d_beta, int beta_is_fp32,
                        const float* d_akk, const float* d_gscale, void* d_dv, float* d_scratch,
-                       const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H, void* stream);
+                       const int* d_cu_seqlens, const int* d_chunk_indices, int num_chunks, int T, int H, int* d_status,
+                       void* stream);
 
 /* Chunk-parallel gated part: Akk / Gram-matrix VJPs, reverse cumulative sum, gate and L2-norm VJPs.
  * Writes d_dq, d_dk (bf16), d_dg (dtype of g), d_dbeta (dtype of beta); accumulates d_dA_log [H] and
