@@ -75,6 +75,11 @@ constexpr int SM_LF = SM_OPB;             // L fp32 [64][68]
 constexpr int SM_AINV = SM_OPB + 17408;   // (I+L)^-1 fp32 [64][68]
 constexpr int SM_TM = SM_OPB + 34816;     // scratch for the block products [32][36]
 constexpr int TROW = 36;
+// staging of the lane-per-token outputs: written in the exact tile-pack image, then sent to HBM by bulk copies (one
+// thread, asynchronous) instead of 16-byte stores that hit a different 128-byte line in every lane
+constexpr int SM_STG_AQK = SM_OPA + 16384;   // [64][128 B]: free from the Gram epilogue on (Y only takes the first 16 KB)
+constexpr int SM_STG_U = SM_OPA;             // U0 | U1, [2][64][128 B]: Y is dead once the W/U MMAs have completed
+constexpr int SM_STG_W = SM_XS;              // [64][256 B]: so is X
 constexpr int SM_AKK16 = SM_LF;           // Akk fp16, stacked twice: [128][128 B], SW128 (K-major A operand); L is dead by then
 static_assert(SM_TM + 32 * TROW * 4 <= SM_XS, "inverse scratch must fit the B operand region");
 
@@ -461,6 +466,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
         reinterpret_cast<float*>(sm + SM_C3)[tid] = fast_exp2(r[3] - r[1]);
         reinterpret_cast<float*>(sm + SM_C3)[DK + tid] = fast_exp2(r[3] - r[2]);
     }
+    if (tid == 0) bulk_wait_read_all();   // the previous tile's staged outputs have left the operand buffers
     __syncthreads();          // tables are visible
     PHASE_MARK(2);      // tables (same slot as the in-warp scan)
 
@@ -598,8 +604,8 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
             for (int gcol = gpar; gcol < 4; gcol += NWARPS / 8) {
                 if (gcol > blk) {                            // warp-uniform: nothing but zeros right of the block
                     if (mine && is_q) {
-                        *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol)) = make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol + 8)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(sm + SM_STG_AQK + swz128(row, 16 * gcol)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(sm + SM_STG_AQK + swz128(row, 16 * gcol + 8)) = make_uint4(0, 0, 0, 0);
                     }
                     continue;
                 }
@@ -617,7 +623,7 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                     if (is_q) {
 #pragma unroll
                         for (int hc = 0; hc < 2; ++hc)
-                            *reinterpret_cast<uint4*>(tile + TP_AQK + swz128(row, 16 * gcol + 8 * hc)) =
+                            *reinterpret_cast<uint4*>(sm + SM_STG_AQK + swz128(row, 16 * gcol + 8 * hc)) =
                                 make_uint4(pack_f16(vals[8 * hc], vals[8 * hc + 1]), pack_f16(vals[8 * hc + 2], vals[8 * hc + 3]),
                                            pack_f16(vals[8 * hc + 4], vals[8 * hc + 5]), pack_f16(vals[8 * hc + 6], vals[8 * hc + 7]));
                     } else {
@@ -796,19 +802,27 @@ __global__ void __launch_bounds__(INTRA_THREADS, 2) kda_fwd_intra_kernel(const I
                                             pack_f16(__uint_as_float(r[8 * hc + 6]), __uint_as_float(r[8 * hc + 7])));
                 out_of_range |= f16x2_not_finite(pk.x) | f16x2_not_finite(pk.y) | f16x2_not_finite(pk.z) | f16x2_not_finite(pk.w);
                 const int cc = chn + 8 * hc;
-                if (is_u) *reinterpret_cast<uint4*>(tile + (cc < 64 ? TP_U0 : TP_U1) + swz128(tok, cc & 63)) = pk;
-                else *reinterpret_cast<uint4*>(tile + TP_W + swz256(tok, cc)) = pk;
+                if (is_u) *reinterpret_cast<uint4*>(sm + SM_STG_U + (cc < 64 ? 0 : 8192) + swz128(tok, cc & 63)) = pk;
+                else *reinterpret_cast<uint4*>(sm + SM_STG_W + swz256(tok, cc)) = pk;
             }
         }
         // w and u inherit the range of v and of (I + L)^-1: fp16 has no room beyond 65504, so say so instead of
         // handing inf to the scan
         if (__any_sync(0xffffffffu, out_of_range) && lane == 0) atomicMax(p.status, STATUS_RANGE);
     }
+    fence_proxy_async();
     umma::fence_before_sync();
-    __syncthreads();      // TMEM columns and shared memory are free for the next tile
+    __syncthreads();      // TMEM columns are free for the next tile; the staged outputs are complete
     umma::fence_after_sync();
+    if (tid == 0) {       // w, u and Aqk leave as three bulk copies; their buffers are next written by the operand generation
+        bulk_s2g(tile + TP_W, sm + SM_STG_W, 16384);
+        bulk_s2g(tile + TP_U0, sm + SM_STG_U, 16384);
+        bulk_s2g(tile + TP_AQK, sm + SM_STG_AQK, 8192);
+        bulk_commit();
+    }
     PHASE_MARK(11);     // W/U epilogue
     }  // tile loop
+    if (tid == 0) bulk_wait_all();        // staged outputs must be on their way before the shared memory goes away
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
 }
 
