@@ -497,35 +497,24 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     __syncthreads();
 
     BG_MARK(5);   // Zw, accumulator initial values
-    // ---- next tile of this CTA: pull its inputs into L2 while the Gram phase computes (the first tile comes cold) ----
+    // ---- next tile of this CTA: pull its inputs into L2 while the Gram phase computes (the first tile comes cold).
+    //      Bulk prefetches: one instruction covers a whole contiguous array or a whole token row ----
     if (next_tile >= 0) {
-        const int cn = next_tile / p.H, hn = next_tile - cn * p.H;
-        const ChunkInfo cin = chunk_info(cn, p.cu_seqlens, p.chunk_indices, p.T);
-        const size_t nb = (size_t)cin.row0 * tok_stride + (size_t)hn * DK;
-        const float* nscr = p.scratch + (size_t)next_tile * (size_t)BWD_SCRATCH_FLOATS;
-        for (int i = tid; i < (BWD_SCRATCH_FLOATS + 31) / 32; i += BG_THREADS) prefetch_l2(nscr + 32 * i);
-        if (tid < 64 * 4) {                               // q, k, g rows: 256 B (bf16) or 512 B (fp32 g) each
-            const int row = tid >> 2, part = tid & 3;
+        if (tid == 0) {
+            bulk_prefetch_l2(p.scratch + (size_t)next_tile * (size_t)BWD_SCRATCH_FLOATS, BWD_SCRATCH_FLOATS * 4);
+            bulk_prefetch_l2(p.akk + (size_t)next_tile * 4096, 4096 * 4);
+            bulk_prefetch_l2(p.mkk + (size_t)next_tile * 4096, 4096 * 4);
+        } else if (tid >= 32 && tid < 32 + 64 * 3) {
+            const int cn = next_tile / p.H, hn = next_tile - cn * p.H;
+            const ChunkInfo cin = chunk_info(cn, p.cu_seqlens, p.chunk_indices, p.T);
+            const int row = (tid - 32) & 63, which = (tid - 32) >> 6;      // q, k, g
             if (row < cin.valid) {
-                const size_t o = nb + (size_t)row * tok_stride;
-                if (part < 2) {
-                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(part ? p.k : p.q) + o;
-                    prefetch_l2(src);
-                    prefetch_l2(src + 64);
-                } else if (p.g_per_head) {
-                    // a few bytes per row: no hint
-                } else if (p.g_fp32) {
-                    const float* src = reinterpret_cast<const float*>(p.g) + o + 64 * (part - 2);
-                    prefetch_l2(src);
-                    prefetch_l2(src + 32);
-                } else {
-                    prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.g) + o + 64 * (part - 2));
-                }
+                const size_t o = (size_t)(cin.row0 + row) * tok_stride + (size_t)hn * DK;
+                if (which < 2) bulk_prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(which ? p.k : p.q) + o, DK * 2);
+                else if (p.g_per_head) { /* a few bytes per row: no hint */ }
+                else if (p.g_fp32) bulk_prefetch_l2(reinterpret_cast<const float*>(p.g) + o, DK * 4);
+                else bulk_prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(p.g) + o, DK * 2);
             }
-        } else if (tid < 64 * 4 + 128) {
-            prefetch_l2(p.akk + (size_t)next_tile * 4096 + 32 * (tid - 256));
-        } else {
-            prefetch_l2(p.mkk + (size_t)next_tile * 4096 + 32 * (tid - 384));
         }
     }
 
