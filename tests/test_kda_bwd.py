@@ -251,3 +251,66 @@ def test_backward_long_sequence_all_gradients(disable_recompute):
     ref = {n: t.grad.cpu() for n, t in ref_in.items()}
     got = {n: t.grad.float().cpu() for n, t in dev_in.items()}
     assert_grads(ref, got, {"default": 5e-3, "A_log": 8e-3, "dt_bias": 8e-3}, "T8192")
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 64, 1), (2, 100, 3), (1, 64 * 160, 2)])
+def test_dense_stage_against_torch_products(B, T, H):
+    """cula_kda_bwd_dense alone, through the C ABI, on random inputs: every field of the scratch record and dv against
+    fp64 matrix products of the same operands. The last shape has more tiles than SMs (persistent tile loop, TMA
+    double buffering across tiles), the middle one a ragged last chunk. tf32 operands: 2e-3 relative RMS."""
+    from cula_b200 import _native
+    lib = _native.lib()
+    g = torch.Generator().manual_seed(B * 1000 + T + H)
+    nt = (T + 63) // 64
+    tiles = B * nt * H
+    h32 = torch.randn(tiles, 128, 128, generator=g)
+    ds = torch.randn(tiles, 128, 128, generator=g)
+    vnew = torch.randn(tiles, 64, 128, generator=g).half()
+    dvn = torch.randn(tiles, 64, 128, generator=g).half()
+    do = torch.randn(B, T, H, 128, generator=g).bfloat16()
+    v = torch.randn(B, T, H, 128, generator=g).bfloat16()
+    beta = torch.rand(B, T, H, generator=g)
+    akk = torch.tril(torch.randn(tiles, 64, 64, generator=g) * 0.2)
+    work = torch.tensor([4.0, 0.25, 0.0, 0.0])           # gradient scale s = 4 and 1 / s
+    # tile = (b * nt + c) * H + h; padding rows of the last chunk carry zeros in the per-tile intermediates
+    valid = torch.full((nt,), 64)
+    valid[-1] = T - 64 * (nt - 1)
+    for c in range(nt):
+        for b in range(B):
+            sl = slice((b * nt + c) * H, (b * nt + c + 1) * H)
+            vnew[sl, int(valid[c]):] = 0
+            dvn[sl, int(valid[c]):] = 0
+    dev = {k: t.cuda() for k, t in dict(h32=h32, ds=ds, vnew=vnew, dvn=dvn, do=do, v=v, beta=beta, akk=akk, work=work).items()}
+    dv = torch.zeros(B, T, H, 128, dtype=torch.bfloat16, device="cuda")
+    nfl = lib.cula_kda_bwd_scratch_floats()
+    scratch = torch.zeros(tiles, nfl, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.cula_kda_bwd_dense(dev["h32"].data_ptr(), dev["ds"].data_ptr(), dev["vnew"].data_ptr(), dev["dvn"].data_ptr(),
+                                dev["do"].data_ptr(), dev["v"].data_ptr(), dev["beta"].data_ptr(), 1, dev["akk"].data_ptr(),
+                                dev["work"].data_ptr(), dv.data_ptr(), scratch.data_ptr(), None, None, B * nt, T, H,
+                                status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    scr = scratch.cpu().double()
+    # reference, tile by tile in fp64
+    pad = nt * 64 - T
+    def tiled(x):       # [B, T, H, 128] -> [tiles, 64, 128], zero padding rows
+        x = F.pad(x.double(), (0, 0, 0, 0, 0, pad)).view(B, nt, 64, H, 128).permute(0, 1, 3, 2, 4)
+        return x.reshape(tiles, 64, 128)
+    dO, V = 4.0 * tiled(do), tiled(v)
+    bt = F.pad(beta.double(), (0, 0, 0, pad)).view(B, nt, 64, H).permute(0, 1, 3, 2).reshape(tiles, 64)
+    S, dS, Vn, dVn, A = h32.double(), ds.double(), vnew.double(), dvn.double(), akk.double()
+    lower, strict = torch.tril(torch.ones(64, 64, dtype=torch.float64)), torch.tril(torch.ones(64, 64, dtype=torch.float64), -1)
+    Zu = A.transpose(1, 2) @ dVn
+    ref = {
+        "dqg": (0, dO @ S.transpose(1, 2)), "dw": (8192, -(dVn @ S.transpose(1, 2))), "dkg": (16384, Vn @ dS.transpose(1, 2)),
+        "dps": (24576, (dO @ Vn.transpose(1, 2)) * lower), "dau": (28672, (dVn @ (bt[:, :, None] * V).transpose(1, 2)) * strict),
+        "dbu": (32768, (Zu * V).sum(-1)), "dd": (32832, (S * dS).sum(-1)),
+    }
+    for name, (off, want) in ref.items():
+        got = scr[:, off:off + want[0].numel()].reshape(want.shape)
+        assert err_ratio(want, got) <= 2e-3, (name, err_ratio(want, got))
+    dv_ref = 0.25 * bt[:, :, None] * Zu
+    dv_got = tiled(dv.cpu())
+    assert err_ratio(dv_ref, dv_got) <= 5e-3, err_ratio(dv_ref, dv_got)      # bf16 output
