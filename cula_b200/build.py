@@ -3,7 +3,8 @@
     python -m cula_b200.build [--force] [--verbose]
 
 The library is built in-tree and loaded with ctypes (cula_b200/_native.py); it has a plain C ABI
-(include/cula_kda.h) and links only against the CUDA runtime.
+(include/cula_kda.h) and links only against the CUDA runtime (the one driver function it needs, the tensor-map encoder
+of the dense backward stage, is looked up through the runtime's driver entry point at first use).
 """
 from __future__ import annotations
 
