@@ -238,10 +238,14 @@ kda_bwd_dense_kernel(const BwdDenseParams p, const int num_tiles, const __grid_c
             fence_proxy_async();
             __syncthreads();
             BD_MARK(0 + 6 * vh);      // operands widened into shared memory
-            // operands of the next stage into registers: the second half of this tile, or the top of the next tile
-            if (vh == 0) st = fetch_stage(tile, cur, cur_h, 1);
-            else if (next < num_tiles) fetch_tile_top(next);
-            BD_MARK(1 + 6 * vh);      // next operands requested
+            // operands of the next stage into registers: the second half of this tile, or the top of the next tile (its
+            // geometry costs a few hundred instructions: the issuing thread does this after the MMAs are on their way)
+            auto fetch_next = [&]() {
+                if (vh == 0) st = fetch_stage(tile, cur, cur_h, 1);
+                else if (next < num_tiles) fetch_tile_top(next);
+            };
+            if (warp != 0 || vh == 0) fetch_next();
+            BD_MARK(1 + 6 * vh);
             // ---- one thread: wait for the states of this half, issue the MMAs ----
             if (tid == 0) {
                 if (vh == 0 && !issued1) {
@@ -300,7 +304,8 @@ kda_bwd_dense_kernel(const BwdDenseParams p, const int num_tiles, const __grid_c
                     }
                 }
             }
-            BD_MARK(4 + 6 * vh);          // (thread 0: nothing)
+            if (warp == 0 && vh == 1) fetch_next();
+            BD_MARK(4 + 6 * vh);          // thread 0: next operands requested
             if (!cta_wait(2 + vh, par)) break;
             BD_MARK(5 + 6 * vh);          // wait for the MMAs
         }

@@ -22,10 +22,11 @@ FWD_PHASES = ["gate activation", "barrier (group totals)", "in-warp scan, tables
               "MMA wait, half 0 (+ L2 hints)", "operand generation, half 1", "MMA wait, half 1",
               "Y staging + barrier", "triangular inverse", "Akk pack + W/U MMA issue", "W/U MMA wait", "W/U epilogue",
               "loads issued under the MMA wait", "Gram epilogue", "L2 norms, beta", "top of the tile (q/k loads issued)"]
-DENSE_PHASES = ["half 0: operands widened into smem", "half 0: next operands requested",
-                "half 0: store read-out + wait for the states (TMA)", "half 0: MMA issue", "-", "half 0: wait for the MMAs",
-                "half 1: operands widened into smem", "half 1: next operands requested", "half 1: wait for the states (TMA)",
-                "half 1: MMA issue", "-", "half 1: wait for the MMAs", "dQg, dW staged, stores issued",
+DENSE_PHASES = ["half 0: operands widened into smem", "-",
+                "half 0: store read-out + wait for the states (TMA)", "half 0: MMA issue", "half 0: next operands requested",
+                "half 0: wait for the MMAs",
+                "half 1: operands widened into smem", "-", "half 1: wait for the states (TMA)",
+                "half 1: MMA issue", "half 1: next tile's operands requested", "half 1: wait for the MMAs", "dQg, dW staged, stores issued",
                 "dKg, dPs, dAu staged, dv stored", "store read-out + end-of-tile barrier"]
 BWD_PHASES = ["loads, gate, norms", "cumulative sum", "stage dW, X", "dA", "T1, dL", "Zw + accumulator set-up", "L2 hints",
               "Gram VJP, row side", "Gram VJP, column side", "reverse cumulative sum", "gate VJP, dg", "L2-norm VJP, stores"]

@@ -149,12 +149,23 @@ def test_cp_backward_emulated_ranks_match_oracle_autograd(world, T, segments):
         assert e <= tol.get(n, 8e-3) and torch.isfinite(got[n]).all(), (n, e)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_cp_two_gpus_nccl(tmp_path):
+def _run_nccl_worker(world, port, tmp_path):
     script = os.path.join(ROOT, "tests", "cp_nccl_worker.py")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29611", script, str(tmp_path)],
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), script, str(tmp_path)],
                          capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "CP_OK" in out.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_cp_two_gpus_nccl(tmp_path):
+    _run_nccl_worker(2, 29611, tmp_path)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_cp_all_gpus_nccl(tmp_path):
+    """Forward, final state and every gradient over 4 (or 8) ranks: shards of 256 (128) tokens, so every rank but the
+    first both receives and passes on a carried state, forward and backward."""
+    _run_nccl_worker(8 if torch.cuda.device_count() >= 8 else 4, 29612, tmp_path)
