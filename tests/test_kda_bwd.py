@@ -136,6 +136,28 @@ def test_backward_varlen(lens):
     assert_grads(ref, got, SUITE_TOL, f"varlen{lens}")
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_backward_varlen_random_sweep(seed):
+    """Seeded random packed batches (1-5 sequences of 1-200 tokens, 1-3 heads): every gradient (with upstream gradients
+    on the outputs and on the final states) against autograd of the oracle. Ragged last chunks of many lengths,
+    sequences shorter than a chunk, a chunk-aligned and a single-token sequence occur across the six draws."""
+    rng = np.random.default_rng(100 + seed)
+    lens = [int(x) for x in rng.integers(1, 201, size=int(rng.integers(1, 6)))]
+    if seed == 0:
+        lens[0] = 64            # at least one chunk-aligned and one single-token sequence in the sweep
+    if seed == 1:
+        lens[-1] = 1
+    H, T = int(rng.integers(1, 4)), sum(lens)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    inp = make_inputs(1, T, H, seed=20 + seed, gate_offset=-7.0)
+    gen = torch.Generator().manual_seed(50 + seed)
+    inp["initial_state"] = torch.randn(len(lens), H, 128, 128, generator=gen)
+    do = torch.randn(1, T, H, 128, generator=gen).to(torch.bfloat16)
+    dht = torch.randn(len(lens), H, 128, 128, generator=gen)
+    ref, got = run_both(inp, do, dht, cu_seqlens=cu)
+    assert_grads(ref, got, SUITE_TOL, f"varlen sweep {lens} H={H}")
+
+
 def test_backward_small_upstream_gradient_and_no_state():
     """dO of order 1e-6 (mean-reduced losses): the power-of-two gradient scale keeps fp16 operands in range.
     Also covers initial_state=None / no final-state gradient."""
