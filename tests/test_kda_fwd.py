@@ -311,3 +311,37 @@ def test_unbounded_gate_stays_finite():
     inp["k"] = F.normalize(inp["k"].float(), dim=-1).to(torch.bfloat16)
     o, ht = run_chunk_kda(inp, l2=False, gate=False)
     assert torch.isfinite(o).all() and torch.isfinite(ht).all()
+
+
+def test_forward_is_capturable_in_a_cuda_graph():
+    """Serving stacks replay the forward from a CUDA graph: nothing in the call may synchronise, allocate outside the
+    graph's pool or read a device value on the host. Captured once, replayed on new input contents, compared bit for
+    bit with the eager call (the kernels are deterministic)."""
+    from cula_b200.kda import check_status, chunk_kda
+    B, T, H = 2, 200, 3
+    kw = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0,
+              output_final_state=True)
+
+    def call(x):
+        return chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], A_log=x["A_log"], dt_bias=x["dt_bias"],
+                         initial_state=x["initial_state"], **kw)
+
+    static = {n: t.cuda() for n, t in make_inputs(B, T, H, seed=5, gate_offset=-6.0, h0_std=0.5).items()}
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad():
+        call(static)                                     # warm-up outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.no_grad(), torch.cuda.graph(graph):
+        o_static, ht_static = call(static)
+    for seed in (6, 7):
+        fresh = {n: t.cuda() for n, t in make_inputs(B, T, H, seed=seed, gate_offset=-6.0, h0_std=0.5).items()}
+        for n in static:
+            static[n].copy_(fresh[n])
+        graph.replay()
+        with torch.no_grad():
+            o_ref, ht_ref = call(fresh)
+        torch.cuda.synchronize()
+        assert torch.equal(o_static, o_ref) and torch.equal(ht_static, ht_ref)
+    check_status()
