@@ -160,3 +160,40 @@ def test_decode_large_batch_and_bad_index_status():
         check_status()
     assert torch.equal(pool[3], before[3])                   # the offending sequence touched nothing
     check_status()                                           # the status word was cleared by the failed check
+
+
+def test_decode_is_capturable_in_a_cuda_graph():
+    """The way a serving engine runs decode: one captured step replayed per token against the state pool. Three
+    replayed steps must equal three eager steps on a copy of the pool, bit for bit."""
+    from cula_b200.kda import check_status, kda_decode
+    N, H, HV = 16, 8, 16
+    q, k, v, a, b, A_log, dt_bias, state = make_decode_inputs(N, H, HV, 128, 128, seed=3)
+    dev = lambda t: t.cuda()
+    static = [dev(x.unsqueeze(1)) for x in (q, k, v, a, b)]
+    A_d, bias_d, idx = dev(A_log), dev(dt_bias), torch.arange(N, dtype=torch.int32).cuda()
+    pool_graph, pool_eager = dev(state), dev(state)
+
+    def step(inputs, pool):
+        return kda_decode(A_log=A_d, dt_bias=bias_d, q=inputs[0], k=inputs[1], v=inputs[2], a=inputs[3], b=inputs[4],
+                          initial_state_source=pool, initial_state_indices=idx, scale=128 ** -0.5,
+                          use_qk_l2norm_in_kernel=True)
+
+    warm = dev(state)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step(static, warm)                                # warm-up outside the capture, on a scratch pool
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_static = step(static, pool_graph)
+    pool_graph.copy_(dev(state))                          # the capture itself does not run the kernels, but be explicit
+    for t in range(3):
+        fresh = [dev(x.unsqueeze(1)) for x in make_decode_inputs(N, H, HV, 128, 128, seed=10 + t)[:5]]
+        for dst, src in zip(static, fresh):
+            dst.copy_(src)
+        graph.replay()
+        o_ref = step(fresh, pool_eager)
+        torch.cuda.synchronize()
+        assert torch.equal(o_static, o_ref) and torch.equal(pool_graph, pool_eager)
+    check_status()
