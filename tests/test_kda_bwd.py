@@ -336,3 +336,52 @@ def test_dense_stage_against_torch_products(B, T, H):
     dv_ref = 0.25 * bt[:, :, None] * Zu
     dv_got = tiled(dv.cpu())
     assert err_ratio(dv_ref, dv_got) <= 5e-3, err_ratio(dv_ref, dv_got)      # bf16 output
+
+
+def test_forward_backward_is_capturable_in_a_cuda_graph():
+    """A whole training step of the operator (forward with recomputation backward) captured once and replayed on new
+    inputs: gradients equal the eager ones (dA_log / ddt_bias come from atomics: compared with a tolerance)."""
+    from cula_b200.kda import check_status, chunk_kda
+    B, T, H = 1, 192, 2
+    names = ("q", "k", "v", "g", "beta", "A_log", "dt_bias", "initial_state")
+
+    def step(x, do):
+        for n in names:
+            x[n].grad = None
+        o, ht = chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], A_log=x["A_log"], dt_bias=x["dt_bias"],
+                          initial_state=x["initial_state"], output_final_state=True, use_qk_l2norm_in_kernel=True,
+                          use_gate_in_kernel=True, safe_gate=True, lower_bound=-5.0)
+        (o.float() * do.float()).sum().backward()
+        return o
+
+    def leaves(seed):
+        return {n: t.cuda().requires_grad_(True) for n, t in make_inputs(B, T, H, seed=seed, gate_offset=-6.0, h0_std=0.5).items()}
+
+    static, do = leaves(30), torch.randn(B, T, H, 128, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step(static, do)                              # warm-up outside the capture (also creates the .grad buffers)
+    torch.cuda.current_stream().wait_stream(side)
+    for n in names:
+        static[n].grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_static = step(static, do)
+    grads_static = {n: static[n].grad for n in names}
+    for seed in (31, 32):
+        fresh = leaves(seed)
+        with torch.no_grad():
+            for n in names:
+                static[n].copy_(fresh[n])
+        graph.replay()
+        o_ref = step(fresh, do)
+        torch.cuda.synchronize()
+        assert torch.equal(o_static, o_ref)
+        for n in names:
+            if n in ("A_log", "dt_bias"):
+                assert err_ratio(fresh[n].grad.float().cpu(), grads_static[n].float().cpu()) <= 1e-5, n
+            else:
+                assert torch.equal(grads_static[n], fresh[n].grad), n
+    check_status()
