@@ -66,6 +66,8 @@ EXTRA_WORKLOADS = {
     "cp_T262144_H32": dict(kind="cp", T=262144, H=32),
     "cp_T32768_H32": dict(kind="cp", T=32768, H=32),
     "decode_N256_H32": dict(kind="decode", N=256, H=32),
+    "gdn_fwd_B2_T2048_H32": dict(kind="gdn", B=2, T=2048, H=32, backward=False),
+    "gdn_fwdbwd_B2_T2048_H32": dict(kind="gdn", B=2, T=2048, H=32, backward=True),
 }
 
 
@@ -417,6 +419,34 @@ def run_extra(args, rank, world, local_rank):
             o.backward(do)
         tokens, metric, launches = B * T * world, "chunk_kda forward+backward tokens/s", 9
         cfg = {"B_per_gpu": B, "T": T, "sharding": "batch x head shards, one per rank, no collective"}
+    elif w["kind"] == "gdn":
+        # the scalar-gate variant (one decay per token and head) on the headline shape: raw gate activated in-kernel
+        from cula_b200.gdn import chunk_gated_delta_rule
+        B, T = w["B"], w["T"]
+        inp = make_inputs(B, T, H, seed=rank, h0_std=0.1)
+        gen = torch.Generator().manual_seed(100 + rank)
+        d = {k: inp[k].to(dev) for k in ("q", "k", "v", "beta", "initial_state")}
+        d["g"] = torch.randn(B, T, H, generator=gen).to(dev)
+        d["A_log"] = (0.1 * torch.randn(H, generator=gen)).to(dev)
+        d["dt_bias"] = (0.1 * torch.randn(H, generator=gen)).to(dev)
+        do = torch.randn(B, T, H, 128, device=dev).to(torch.bfloat16)
+        if w["backward"]:
+            for t in d.values():
+                t.requires_grad_(True)
+
+        def step():
+            for t in d.values():
+                t.grad = None
+            o, _ = chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"],
+                                          output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                                          A_log=d["A_log"], dt_bias=d["dt_bias"])
+            if w["backward"]:
+                o.backward(do)
+        tokens = B * T * world
+        metric = "chunk_gated_delta_rule forward+backward tokens/s" if w["backward"] else "chunk_gated_delta_rule forward tokens/s"
+        launches = 9 if w["backward"] else 2
+        cfg = {"B_per_gpu": B, "T": T, "gate": "one per (token, head), softplus form in-kernel",
+               "sharding": "batch x head shards, one per rank, no collective"}
     elif w["kind"] == "varlen":
         lens = varlen_lengths(w["n_seqs"], w["total"], seed=rank)
         T = sum(lens)
