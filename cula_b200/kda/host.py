@@ -24,7 +24,8 @@ def bind_host_to_gpu(device=None):
 
     With one process per GPU, host buffers that are allocated and pinned AFTER this call land in the memory of that
     node (first-touch policy), so each rank's host<->device copies stay on its own socket instead of all ranks sharing
-    one node's memory controllers and inter-socket links. The core list comes from NVML (the ideal CPU affinity of the
+    one node's memory controllers and inter-socket links; the GPU's node is also made the preferred node of the
+    process's page allocations (`_prefer_memory_near`). The core list comes from NVML (the ideal CPU affinity of the
     device), else from the device's ``local_cpulist`` in sysfs; it is intersected with the cores the process may already
     use, and nothing changes when that would leave no core. Only this process's own affinity mask is touched."""
     import os
@@ -51,11 +52,37 @@ def bind_host_to_gpu(device=None):
                 cpus.update(range(int(lo), int(hi or lo) + 1))
         except Exception:
             cpus = set()
+    _prefer_memory_near(dev)
     chosen = cpus & allowed
     if chosen and chosen != allowed:
         os.sched_setaffinity(0, chosen)
         return sorted(chosen)
     return sorted(allowed)
+
+
+def _prefer_memory_near(dev):
+    """Make the NUMA node the GPU hangs off the PREFERRED node of this process's future page allocations
+    (``set_mempolicy(MPOL_PREFERRED)``: other nodes are still used when it is full), so that host buffers pinned after
+    this call sit next to the GPU even when the cores the process may run on do not. Returns the node, or None when the
+    platform does not say (no ``numa_node`` in sysfs, one node only, the call refused): nothing changes then."""
+    import ctypes
+    import os
+    import platform
+    nr = {"x86_64": 238, "aarch64": 237}.get(platform.machine())
+    try:
+        props = torch.cuda.get_device_properties(dev)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+    except Exception:
+        return None
+    if nr is None or node < 0 or node >= 64 or len(nodes) < 2:
+        return None
+    mask = ctypes.c_ulong(1 << node)
+    libc = ctypes.CDLL(None, use_errno=True)
+    MPOL_PREFERRED = 1
+    rc = libc.syscall(nr, MPOL_PREFERRED, ctypes.byref(mask), 65)
+    return node if rc == 0 else None
 
 
 _STREAMS: dict = {}     # device -> (upload stream, download stream), created once: stream creation costs ~10 us each
