@@ -60,28 +60,37 @@ def bind_host_to_gpu(device=None):
     return sorted(allowed)
 
 
-def _prefer_memory_near(dev):
+def _prefer_memory_near(dev, _probe=None, _syscall=None):
     """Make the NUMA node the GPU hangs off the PREFERRED node of this process's future page allocations
     (``set_mempolicy(MPOL_PREFERRED)``: other nodes are still used when it is full), so that host buffers pinned after
     this call sit next to the GPU even when the cores the process may run on do not. Returns the node, or None when the
-    platform does not say (no ``numa_node`` in sysfs, one node only, the call refused): nothing changes then."""
+    platform does not say (no ``numa_node`` in sysfs, one node only, the call refused): nothing changes then.
+    ``_probe`` () -> (node of the GPU, number of nodes) and ``_syscall`` (nr, mode, mask, maxnode) -> rc replace sysfs
+    and the system call in tests."""
     import ctypes
     import os
     import platform
     nr = {"x86_64": 238, "aarch64": 237}.get(platform.machine())
-    try:
+
+    def probe():
         props = torch.cuda.get_device_properties(dev)
         bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
         node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
         nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        return node, len(nodes)
+
+    try:
+        node, n_nodes = (_probe or probe)()
     except Exception:
         return None
-    if nr is None or node < 0 or node >= 64 or len(nodes) < 2:
+    if nr is None or node < 0 or node >= 64 or n_nodes < 2:
         return None
-    mask = ctypes.c_ulong(1 << node)
-    libc = ctypes.CDLL(None, use_errno=True)
     MPOL_PREFERRED = 1
-    rc = libc.syscall(nr, MPOL_PREFERRED, ctypes.byref(mask), 65)
+    if _syscall is not None:
+        rc = _syscall(nr, MPOL_PREFERRED, 1 << node, 65)
+    else:
+        mask = ctypes.c_ulong(1 << node)
+        rc = ctypes.CDLL(None, use_errno=True).syscall(nr, MPOL_PREFERRED, ctypes.byref(mask), 65)
     return node if rc == 0 else None
 
 

@@ -212,3 +212,23 @@ def test_noalloc_entry_point_rejects_bad_arguments_without_a_gpu():
     assert call(num_chunks=200, T=64 * 200, H=2) == -3                                       # 400 tiles > 256
     assert call(q=p + 2) == -2 and call(o=p + 8) == -2                                       # 16-byte alignment
     assert call(num_chunks=0) == 0 and call(N=0) == 0                                        # nothing to do
+
+
+def test_host_binding_helpers_without_topology_and_with_a_fake_one():
+    """bind_host_to_gpu / _prefer_memory_near: nothing changes where the platform exposes no topology (this box: no
+    GPU, no NUMA information); with a faked two-node topology the preferred-node policy is requested for the GPU's node
+    with MPOL_PREFERRED and a one-bit mask, and a refused call reports None."""
+    import os
+    import platform
+    from cula_b200.kda import host
+    before = os.sched_getaffinity(0)
+    assert host.bind_host_to_gpu("cuda:0") == sorted(before) and os.sched_getaffinity(0) == before
+    assert host._prefer_memory_near("cuda:0") is None
+    calls = []
+    ok = lambda *a: calls.append(a) or 0
+    assert host._prefer_memory_near("cuda:0", _probe=lambda: (0, 1), _syscall=ok) is None and not calls     # one node only
+    assert host._prefer_memory_near("cuda:0", _probe=lambda: (-1, 2), _syscall=ok) is None and not calls    # node unknown
+    if platform.machine() in ("x86_64", "aarch64"):
+        assert host._prefer_memory_near("cuda:0", _probe=lambda: (1, 2), _syscall=ok) == 1
+        assert calls == [({"x86_64": 238, "aarch64": 237}[platform.machine()], 1, 0b10, 65)]
+        assert host._prefer_memory_near("cuda:0", _probe=lambda: (1, 2), _syscall=lambda *a: -1) is None
