@@ -299,6 +299,22 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
     BG_MARK(2);   // stage dW, X
     const int mt = warp & 3, nh = warp >> 2;     // 16-row tile and column group of this warp in the GEMM phases
     const int r0 = 16 * mt + g8, r1 = r0 + 8;
+    // Fragments that are read the way they are stored (A: row = token, K contiguous; B: row = n, K contiguous) come from
+    // ldmatrix: an 8 x 8 b16 tile is an 8 x 4 tile of 32-bit words and lane l receives word (row l / 4, column l % 4),
+    // which is the m16n8k8 tf32 fragment layout -- one x4 load is a whole A fragment or the B fragments of two n-tiles
+    // instead of four scalar shared-memory loads each (the LSU is this kernel's busiest pipe).
+    const uint32_t sm_u32 = smem_u32(sm);
+    const int lr = lane & 7, lm = lane >> 3;
+    auto ldsm_a = [&](int base_floats, int stride, int row0, int k0, float (&f)[4]) {
+        ldsm_x4(sm_u32 + (uint32_t)((base_floats + (row0 + lr + 8 * (lm & 1)) * stride + k0 + 4 * (lm >> 1)) * 4),
+                reinterpret_cast<uint32_t&>(f[0]), reinterpret_cast<uint32_t&>(f[1]), reinterpret_cast<uint32_t&>(f[2]),
+                reinterpret_cast<uint32_t&>(f[3]));
+    };
+    auto ldsm_b2 = [&](int base_floats, int stride, int n0, int k0, float (&f)[4]) {     // f[0..1]: n-tile n0, f[2..3]: n-tile n0 + 8
+        ldsm_x4(sm_u32 + (uint32_t)((base_floats + (n0 + lr + 8 * (lm >> 1)) * stride + k0 + 4 * (lm & 1)) * 4),
+                reinterpret_cast<uint32_t&>(f[0]), reinterpret_cast<uint32_t&>(f[1]), reinterpret_cast<uint32_t&>(f[2]),
+                reinterpret_cast<uint32_t&>(f[3]));
+    };
 
     // ---- 3. dA = dAu + stril(dW X^T) -> c2 (zero on and above the diagonal) ----
     {
@@ -309,12 +325,12 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
 #pragma unroll 4
             for (int ks = 0; ks < 16; ++ks) {
                 const int k0 = 8 * ks;
-                const float fa[4] = {acc1[r0 * AS + k0 + t4], acc1[r1 * AS + k0 + t4], acc1[r0 * AS + k0 + t4 + 4], acc1[r1 * AS + k0 + t4 + 4]};
-#pragma unroll
-                for (int nt = 0; nt < BG_NT64; ++nt) {
-                    const int j = 8 * BG_NT64 * nh + 8 * nt + g8;
-                    bg_mma(acc[nt], fa, acc3[j * AS + k0 + t4], acc3[j * AS + k0 + t4 + 4]);
-                }
+                float fa[4], fb[4];
+                ldsm_a(BG_ACC1, AS, 16 * mt, k0, fa);
+                static_assert(BG_NT64 == 2, "one x4 load covers the B fragments of the warp's two n-tiles");
+                ldsm_b2(BG_ACC3, AS, 8 * BG_NT64 * nh, k0, fb);
+                bg_mma(acc[0], fa, fb[0], fb[1]);
+                bg_mma(acc[1], fa, fb[2], fb[3]);
             }
         }
 #pragma unroll
@@ -337,12 +353,11 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
         for (int nt = 0; nt < BG_NT64; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
         for (int ks = 0; ks < 2 * mt + 2; ++ks) {          // dA[i][j] = 0 for j >= i: later k-steps contribute nothing
             const int k0 = 8 * ks;
-            const float fa[4] = {c2[r0 * AR + k0 + t4], c2[r1 * AR + k0 + t4], c2[r0 * AR + k0 + t4 + 4], c2[r1 * AR + k0 + t4 + 4]};
-#pragma unroll
-            for (int nt = 0; nt < BG_NT64; ++nt) {
-                const int mm = 8 * BG_NT64 * nh + 8 * nt + g8;
-                bg_mma(acc[nt], fa, sA[mm * AR + k0 + t4], sA[mm * AR + k0 + t4 + 4]);
-            }
+            float fa[4], fb[4];
+            ldsm_a(BG_C2, AR, 16 * mt, k0, fa);
+            ldsm_b2(BG_A, AR, 8 * BG_NT64 * nh, k0, fb);
+            bg_mma(acc[0], fa, fb[0], fb[1]);
+            bg_mma(acc[1], fa, fb[2], fb[3]);
         }
 #pragma unroll
         for (int nt = 0; nt < BG_NT64; ++nt) {
@@ -536,8 +551,9 @@ __device__ __forceinline__ void bg_tile(const BwdGatedParams& p, float* sm, cons
             for (int nt = 0; nt < BG_NT6; ++nt) rIv[nt] = sG[16 * I * GS + dB0 + 8 * nt];
             for (int ks = 0; ks < 2 * I + 2; ++ks) {
                 const int j0 = 8 * ks + t4, j1 = j0 + 4;
-                const float aP[4] = {c1[i0 * AR + j0], c1[i1 * AR + j0], c1[i0 * AR + j1], c1[i1 * AR + j1]};
-                const float aR[4] = {c2[i0 * AR + j0], c2[i1 * AR + j0], c2[i0 * AR + j1], c2[i1 * AR + j1]};
+                float aP[4], aR[4];
+                ldsm_a(BG_C1, AR, 16 * I, 8 * ks, aP);
+                ldsm_a(BG_C2, AR, 16 * I, 8 * ks, aR);
                 const float k0s = rstd_k[j0], k1s = rstd_k[j1];
 #pragma unroll
                 for (int nt = 0; nt < BG_NT6; ++nt) {
