@@ -68,6 +68,7 @@ EXTRA_WORKLOADS = {
     "decode_N256_H32": dict(kind="decode", N=256, H=32),
     "gdn_fwd_B2_T2048_H32": dict(kind="gdn", B=2, T=2048, H=32, backward=False),
     "gdn_fwdbwd_B2_T2048_H32": dict(kind="gdn", B=2, T=2048, H=32, backward=True),
+    "layer_ops_B2_T2048_H32": dict(kind="layer", B=2, T=2048, H=32),
 }
 
 
@@ -91,6 +92,86 @@ def varlen_lengths(n_seqs=64, total=65536, seed=0):
 FLOP_PER_TOKEN_HEAD = 180224          # dense-tile convention, forward
 BYTES_PER_TOKEN_HEAD = 1282           # compulsory forward traffic: q,k,v,g bf16 + beta + o
 TILE_PACK_BYTES = 74240
+
+
+def layer_ops_section(dev, B, T, H, steps):
+    """Layer-side operators on the headline shape (rows = B*T tokens, 128 channels per head): milliseconds per call and
+    algorithmic GB/s (bytes every call must read and write once) as a fraction of the measured copy peak. L2 is flushed
+    before every timed call; the median of `steps` calls is reported; every call is replayed from a CUDA graph so that the
+    device time, not the Python around a 30-microsecond kernel, is what the events see."""
+    from cula_b200.kda.gate import fused_kda_gate
+    from cula_b200.kda.layer_ops import rms_norm_gated, short_conv
+    peaks = load_peaks()
+    gen = torch.Generator().manual_seed(0)
+    n_el = B * T * H * 128
+    g_raw = torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16).to(dev).requires_grad_(True)
+    A_log = (0.1 * torch.randn(H, generator=gen)).to(dev).requires_grad_(True)
+    dt_bias = (0.1 * torch.randn(H * 128, generator=gen)).to(dev).requires_grad_(True)
+    x_conv = torch.randn(B, T, H * 128, generator=gen).to(torch.bfloat16).to(dev).requires_grad_(True)
+    w_conv = (0.5 * torch.randn(H * 128, 4, generator=gen)).to(dev).requires_grad_(True)
+    x_norm = torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16).to(dev).requires_grad_(True)
+    g_norm = torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16).to(dev).requires_grad_(True)
+    w_norm = torch.ones(128, device=dev, requires_grad=True)
+    ops = {
+        # name: (callable, forward bytes per element, forward+backward bytes per element)
+        "fused_kda_gate (lower-bound form, fp32 out)": (lambda: fused_kda_gate(g_raw, A_log, dt_bias, lower_bound=-5.0), 2 + 4, 2 + 4 + 2 + 4 + 2),
+        "short_conv (width 4) + SiLU": (lambda: short_conv(x_conv, w_conv)[0], 2 + 2, 2 + 2 + 2 + 2 + 2),
+        "rms_norm_gated (sigmoid gate)": (lambda: rms_norm_gated(x_norm, g_norm, w_norm), 2 + 2 + 2, 6 + 2 + 2 + 2 + 2 + 2),
+    }
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn):
+        """Device time of fn(): captured in a CUDA graph once and replayed (these calls are tens of microseconds long,
+        less than the Python around them costs on the host), L2 flushed before every replay."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        ts = []
+        for i in range(3 + steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    out = {}
+    total_fwd = 0.0
+    leaves = (g_raw, A_log, dt_bias, x_conv, w_conv, x_norm, g_norm, w_norm)
+    for name, (fn, b_f, b_fb) in ops.items():
+        with torch.no_grad():
+            y = fn()
+        dy = torch.randn_like(y)
+
+        def fwd_only():
+            with torch.no_grad():
+                fn()
+
+        def fwd_bwd():
+            for t in leaves:
+                t.grad = None
+            fn().backward(dy)
+        ms_f = timed(fwd_only)
+        ms_fb = timed(fwd_bwd)
+        total_fwd += ms_f
+        out[name] = {"fwd_ms": ms_f, "fwd_GBps": n_el * b_f / ms_f / 1e6, "fwd_frac_of_copy_peak": n_el * b_f / ms_f / 1e6 / peaks["hbm_gbs"],
+                     "fwd_bwd_ms": ms_fb, "fwd_bwd_GBps": n_el * b_fb / ms_fb / 1e6,
+                     "fwd_bwd_frac_of_copy_peak": n_el * b_fb / ms_fb / 1e6 / peaks["hbm_gbs"]}
+    return {"metric": "layer-side operators, forward tokens/s (sum of the three)", "value": B * T / (total_fwd * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": total_fwd, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "layer_ops_B2_T2048_H32", "B": B, "T": T, "H": H, "K": 128,
+                       "l2": "256 MB flush buffer written before every timed call"},
+            "peak_GBps": peaks["hbm_gbs"], "peak_source": peaks["source"], "ops": out}
 
 
 def headline_config(workload):
@@ -473,6 +554,12 @@ def run_extra(args, rank, world, local_rank):
         tokens, metric, launches = N * world, "kda_decode tokens/s", 1
         state_bytes = 2 * N * H * 128 * 128 * 4
         cfg = {"sequences_per_gpu": N, "state_layout": "vk", "state_bytes_read_plus_written": state_bytes}
+    elif w["kind"] == "layer":
+        # the streaming operators around the path (gate activation, short convolution + SiLU, gated RMS norm), each
+        # timed alone, forward and forward+backward, against the bytes it has to move
+        if rank == 0:
+            print(json.dumps(layer_ops_section(dev, w["B"], w["T"], H, args.steps)), flush=True)
+        return
     else:   # context parallel: ONE sequence of T tokens split over the ranks
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
         sampler = ClockSampler(local_rank)

@@ -21,6 +21,13 @@ __device__ __forceinline__ void lo_load8(const __nv_bfloat16* p, float (&v)[8]) 
     f = unpack_bf16(a.z); v[4] = f.x; v[5] = f.y;
     f = unpack_bf16(a.w); v[6] = f.x; v[7] = f.y;
 }
+__device__ __forceinline__ void lo_unpack8(const uint4& a, float (&v)[8]) {
+    float2 f;
+    f = unpack_bf16(a.x); v[0] = f.x; v[1] = f.y;
+    f = unpack_bf16(a.y); v[2] = f.x; v[3] = f.y;
+    f = unpack_bf16(a.z); v[4] = f.x; v[5] = f.y;
+    f = unpack_bf16(a.w); v[6] = f.x; v[7] = f.y;
+}
 __device__ __forceinline__ void lo_store8(__nv_bfloat16* p, const float (&v)[8]) {
     *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
 }
@@ -67,22 +74,35 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
 #pragma unroll
     for (int k = 0; k < CONV_MAXW - 1; ++k) conv_load_row(a, ci.seq, seq_start, t0 - (CONV_MAXW - 1) + k, ch, win[k + 1]);
     if (!BWD) {
-        for (int t = t0; t < t1; ++t) {
+        // the rows of eight tokens are requested before the first of them is used (a thread walks its chunk serially:
+        // one load per step would pay a full memory latency per token); rows past the chunk re-read its last row
+        constexpr int NB = 8;
+        for (int tb = t0; tb < t1; tb += NB) {
+            uint4 raw[NB];
 #pragma unroll
-            for (int k = 0; k < CONV_MAXW - 1; ++k)
+            for (int i = 0; i < NB; ++i)
+                raw[i] = *reinterpret_cast<const uint4*>(a.x + (size_t)min(tb + i, t1 - 1) * a.D + ch);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
-            lo_load8(a.x + (size_t)t * a.D + ch, win[CONV_MAXW - 1]);
-            float o[8];
+            for (int i = 0; i < NB; ++i) {
+                const int t = tb + i;
+                if (t < t1) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float pre = b[e];
+                    for (int k = 0; k < CONV_MAXW - 1; ++k)
 #pragma unroll
-                for (int i = 0; i < CONV_MAXW; ++i)
-                    if (i < W) pre = fmaf(w[e][i], win[CONV_MAXW - W + i][e], pre);
-                o[e] = a.silu ? pre * sigmoid_f(pre) : pre;
+                        for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+                    lo_unpack8(raw[i], win[CONV_MAXW - 1]);
+                    float o[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        float pre = b[e];
+#pragma unroll
+                        for (int i2 = 0; i2 < CONV_MAXW; ++i2)
+                            if (i2 < W) pre = fmaf(w[e][i2], win[CONV_MAXW - W + i2][e], pre);
+                        o[e] = a.silu ? pre * sigmoid_f(pre) : pre;
+                    }
+                    lo_store8(a.y + (size_t)t * a.D + ch, o);
+                }
             }
-            lo_store8(a.y + (size_t)t * a.D + ch, o);
         }
         if (a.cache_out && t1 == seq_end) {      // the last W inputs of the sequence, newest last, zero-padded on the left
             float* c = a.cache_out + ((size_t)ci.seq * a.D + ch) * W;
@@ -103,7 +123,20 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
 #pragma unroll
             for (int i = 0; i < CONV_MAXW; ++i) dw_acc[e][i] = dwin[i][e] = 0.f;
         }
-        for (int t = t0; t < t1 + (W - 1); ++t) {
+        constexpr int NBB = 4;          // rows of four tokens (x and dy) in flight before the first is used
+        const int t_end = t1 + (W - 1), t_last = seq_end - 1;
+        for (int tb = t0; tb < t_end; tb += NBB) {
+          uint4 raw_x[NBB], raw_dy[NBB];
+#pragma unroll
+          for (int i = 0; i < NBB; ++i) {
+              const size_t off = (size_t)min(tb + i, t_last) * a.D + ch;      // clamped: tokens past the sequence are not used
+              raw_x[i] = *reinterpret_cast<const uint4*>(a.x + off);
+              raw_dy[i] = *reinterpret_cast<const uint4*>(a.dy + off);
+          }
+#pragma unroll
+          for (int i = 0; i < NBB; ++i) {
+            const int t = tb + i;
+            if (t >= t_end) break;
 #pragma unroll
             for (int k = 0; k < CONV_MAXW - 1; ++k)
 #pragma unroll
@@ -114,8 +147,8 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
             const bool live = t < seq_end;
             float dyv[8];
             if (live) {
-                lo_load8(a.x + (size_t)t * a.D + ch, win[CONV_MAXW - 1]);
-                lo_load8(a.dy + (size_t)t * a.D + ch, dyv);
+                lo_unpack8(raw_x[i], win[CONV_MAXW - 1]);
+                lo_unpack8(raw_dy[i], dyv);
             }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -149,6 +182,7 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
                 }
                 lo_store8(a.dx + (size_t)u * a.D + ch, o);
             }
+          }
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
