@@ -60,36 +60,49 @@ __global__ void __launch_bounds__(GATE_THREADS) kda_gate_kernel(const GateArgs a
         dbias[e] = 0.f;
     }
     if (active) {
-        for (long long m = blockIdx.y; m < a.M; m += gridDim.y) {
-            const size_t idx = (size_t)m * HK + ch;
-            float gv[8], o[8];
-            load8(a.g, a.g_fp32, idx, gv);
-            if (!BWD) {
+        // rows are taken four at a time and all their loads are issued before the first is used: a thread has only a
+        // handful of rows, and one load per dependent step would make each of them pay a full memory latency
+        constexpr int NB = 4;
+        for (long long mb = blockIdx.y; mb < a.M; mb += (long long)NB * gridDim.y) {
+            float gv[NB][8], dy[NB][8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float x = gv[e] + bias[e];
-                    o[e] = a.use_lower_bound ? a.lower_bound * __fdividef(1.f, 1.f + __expf(-alpha * x)) : -alpha * softplus_f(x);
-                }
-                store8(a.out, a.out_fp32, idx, o);
-            } else {
-                float dy[8];
-                load8(a.dy, a.dy_fp32, idx, dy);
+            for (int i = 0; i < NB; ++i) {
+                const long long m = min(mb + (long long)i * gridDim.y, a.M - 1);      // clamped: the surplus rows are not used
+                const size_t idx = (size_t)m * HK + ch;
+                load8(a.g, a.g_fp32, idx, gv[i]);
+                if (BWD) load8(a.dy, a.dy_fp32, idx, dy[i]);
+            }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float x = gv[e] + bias[e];
-                    float v;
-                    if (a.use_lower_bound) {
-                        const float sg = __fdividef(1.f, 1.f + __expf(-alpha * x));
-                        v = dy[e] * a.lower_bound * sg * (1.f - sg) * alpha;      // d/dx of lb sigmoid(alpha x)
-                        dA = fmaf(v, x, dA);                                      // d/dA_log = d/d(alpha) * alpha
-                    } else {
-                        v = -dy[e] * alpha * __fdividef(1.f, 1.f + __expf(-x));
-                        dA = fmaf(dy[e], -alpha * softplus_f(x), dA);
+            for (int i = 0; i < NB; ++i) {
+                const long long m = mb + (long long)i * gridDim.y;
+                if (m >= a.M) break;
+                const size_t idx = (size_t)m * HK + ch;
+                float o[8];
+                if (!BWD) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float x = gv[i][e] + bias[e];
+                        o[e] = a.use_lower_bound ? a.lower_bound * __fdividef(1.f, 1.f + __expf(-alpha * x)) : -alpha * softplus_f(x);
                     }
-                    dbias[e] += v;
-                    o[e] = v;
+                    store8(a.out, a.out_fp32, idx, o);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float x = gv[i][e] + bias[e];
+                        float v;
+                        if (a.use_lower_bound) {
+                            const float sg = __fdividef(1.f, 1.f + __expf(-alpha * x));
+                            v = dy[i][e] * a.lower_bound * sg * (1.f - sg) * alpha;      // d/dx of lb sigmoid(alpha x)
+                            dA = fmaf(v, x, dA);                                         // d/dA_log = d/d(alpha) * alpha
+                        } else {
+                            v = -dy[i][e] * alpha * __fdividef(1.f, 1.f + __expf(-x));
+                            dA = fmaf(dy[i][e], -alpha * softplus_f(x), dA);
+                        }
+                        dbias[e] += v;
+                        o[e] = v;
+                    }
+                    store8(a.out, a.g_fp32, idx, o);
                 }
-                store8(a.out, a.g_fp32, idx, o);
             }
         }
     }
@@ -135,7 +148,9 @@ extern "C" int kda_launch_gate(const kda::GateArgs* a, int backward, cudaStream_
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int groups = a->H * a->K / 8;
     const int gx = (groups + GATE_THREADS - 1) / GATE_THREADS;
-    long long gy = (8LL * sms + gx - 1) / gx;          // about eight CTAs per SM in flight
+    // about eight CTAs per SM in flight; the backward pass ends in one atomic per thread and channel, so it runs a
+    // quarter as many, longer-lived CTAs
+    long long gy = ((backward ? 2LL : 8LL) * sms + gx - 1) / gx;
     if (gy > a->M) gy = a->M;
     if (gy > 65535) gy = 65535;
     dim3 grid(gx, (unsigned)gy);

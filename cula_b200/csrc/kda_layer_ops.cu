@@ -215,25 +215,42 @@ __global__ void __launch_bounds__(LO_THREADS) kda_rms_norm_gated_kernel(const No
             wv[v][e] = a.w[col];
             dw_acc[v][e] = 0.f;
         }
-    for (long long row = warp0; row < a.R; row += nwarps) {
+    // Rows are taken NB at a time per warp and all their loads are issued before the first is used (a warp has dozens
+    // of rows and one row per dependent step would pay a full memory latency each).
+    constexpr int NB = VPL == 1 ? 4 : (VPL == 2 ? 2 : 1);
+    for (long long rb = warp0; rb < a.R; rb += (long long)NB * nwarps) {
+      uint4 rx[NB][VPL], rg[NB][VPL], rd[NB][VPL];
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        const size_t base = (size_t)min(rb + (long long)i * nwarps, a.R - 1) * a.D;       // clamped: surplus rows are not used
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            if (narrow) {
+                const uint2 x2 = *reinterpret_cast<const uint2*>(a.x + base + 4 * lane);
+                const uint2 g2 = *reinterpret_cast<const uint2*>(a.g + base + 4 * lane);
+                rx[i][v] = make_uint4(x2.x, x2.y, 0u, 0u);
+                rg[i][v] = make_uint4(g2.x, g2.y, 0u, 0u);
+                if (BWD) {
+                    const uint2 d2 = *reinterpret_cast<const uint2*>(a.dy + base + 4 * lane);
+                    rd[i][v] = make_uint4(d2.x, d2.y, 0u, 0u);
+                }
+            } else {
+                rx[i][v] = *reinterpret_cast<const uint4*>(a.x + base + 256 * v + 8 * lane);
+                rg[i][v] = *reinterpret_cast<const uint4*>(a.g + base + 256 * v + 8 * lane);
+                if (BWD) rd[i][v] = *reinterpret_cast<const uint4*>(a.dy + base + 256 * v + 8 * lane);
+            }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        const long long row = rb + (long long)i * nwarps;
+        if (row >= a.R) break;
         const size_t base = (size_t)row * a.D;
         float xv[VPL][8], gv[VPL][8];
-        if (narrow) {       // 4 elements per lane: the upper half of the 8-wide vectors stays zero
-            const uint2 xr = *reinterpret_cast<const uint2*>(a.x + base + 4 * lane);
-            const uint2 gr = *reinterpret_cast<const uint2*>(a.g + base + 4 * lane);
-            float2 f;
-            f = unpack_bf16(xr.x); xv[0][0] = f.x; xv[0][1] = f.y;
-            f = unpack_bf16(xr.y); xv[0][2] = f.x; xv[0][3] = f.y;
-            f = unpack_bf16(gr.x); gv[0][0] = f.x; gv[0][1] = f.y;
-            f = unpack_bf16(gr.y); gv[0][2] = f.x; gv[0][3] = f.y;
 #pragma unroll
-            for (int e = 4; e < 8; ++e) xv[0][e] = gv[0][e] = 0.f;
-        } else {
-#pragma unroll
-            for (int v = 0; v < VPL; ++v) {
-                lo_load8(a.x + base + 256 * v + 8 * lane, xv[v]);
-                lo_load8(a.g + base + 256 * v + 8 * lane, gv[v]);
-            }
+        for (int v = 0; v < VPL; ++v) {
+            lo_unpack8(rx[i][v], xv[v]);      // narrow rows: the upper half of the 8-wide vectors is zero
+            lo_unpack8(rg[i][v], gv[v]);
         }
         float rstd;
         if (!BWD) {
@@ -260,17 +277,8 @@ __global__ void __launch_bounds__(LO_THREADS) kda_rms_norm_gated_kernel(const No
                 }
         } else {
             float dyv[VPL][8], dn[VPL][8], dgo[VPL][8], dot = 0.f;
-            if (narrow) {
-                const uint2 dr = *reinterpret_cast<const uint2*>(a.dy + base + 4 * lane);
-                float2 f;
-                f = unpack_bf16(dr.x); dyv[0][0] = f.x; dyv[0][1] = f.y;
-                f = unpack_bf16(dr.y); dyv[0][2] = f.x; dyv[0][3] = f.y;
 #pragma unroll
-                for (int e = 4; e < 8; ++e) dyv[0][e] = 0.f;
-            } else {
-#pragma unroll
-                for (int v = 0; v < VPL; ++v) lo_load8(a.dy + base + 256 * v + 8 * lane, dyv[v]);
-            }
+            for (int v = 0; v < VPL; ++v) lo_unpack8(rd[i][v], dyv[v]);
 #pragma unroll
             for (int v = 0; v < VPL; ++v)
 #pragma unroll
@@ -306,16 +314,23 @@ __global__ void __launch_bounds__(LO_THREADS) kda_rms_norm_gated_kernel(const No
 #pragma unroll
             for (int v = 0; v < VPL; ++v) lo_store8(dst + base + 256 * v + 8 * lane, out[v]);
         }
+      }
     }
     if (BWD) {
+        // the weight gradient: the CTA's warps are summed in shared memory first, then one global atomic per column and CTA
+        __shared__ float s_dw[1024];
+        for (int c = threadIdx.x; c < a.D; c += LO_THREADS) s_dw[c] = 0.f;
+        __syncthreads();
 #pragma unroll
         for (int v = 0; v < VPL; ++v)
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 if (narrow && e >= 4) continue;
                 const int col = narrow ? 4 * lane + e : 256 * v + 8 * lane + e;
-                atomicAdd(&a.dw[col], dw_acc[v][e]);
+                atomicAdd(&s_dw[col], dw_acc[v][e]);
             }
+        __syncthreads();
+        for (int c = threadIdx.x; c < a.D; c += LO_THREADS) atomicAdd(&a.dw[c], s_dw[c]);
     }
 }
 
