@@ -62,11 +62,18 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
     const int seq_start = a.cu_seqlens ? a.cu_seqlens[ci.seq] : ci.seq * a.T;
     const int seq_end = a.cu_seqlens ? a.cu_seqlens[ci.seq + 1] : (ci.seq + 1) * a.T;
     const int W = a.W, t0 = ci.row0, t1 = ci.row0 + ci.valid;
-    float w[8][CONV_MAXW], b[8];
+    // w: the taps, zero beyond W. wr: the same taps right-aligned in a window of CONV_MAXW slots (wr[e][k] multiplies
+    // window slot k), so that every index into the register arrays below is a compile-time constant whatever W is --
+    // an index that depends on W would put the window into local memory
+    float w[8][CONV_MAXW], wr[8][CONV_MAXW], b[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
 #pragma unroll
-        for (int i = 0; i < CONV_MAXW; ++i) w[e][i] = i < W ? a.w[(size_t)(ch + e) * W + i] : 0.f;   // taps are right-aligned below
+        for (int i = 0; i < CONV_MAXW; ++i) {
+            w[e][i] = i < W ? a.w[(size_t)(ch + e) * W + i] : 0.f;
+            const int tap = i - (CONV_MAXW - W);
+            wr[e][i] = tap >= 0 ? a.w[(size_t)(ch + e) * W + tap] : 0.f;
+        }
         b[e] = a.bias ? a.bias[ch + e] : 0.f;
     }
     // window[k] = x[t - (CONV_MAXW-1) + k]; tap i of a width-W kernel multiplies window[CONV_MAXW - W + i]
@@ -96,8 +103,7 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
                     for (int e = 0; e < 8; ++e) {
                         float pre = b[e];
 #pragma unroll
-                        for (int i2 = 0; i2 < CONV_MAXW; ++i2)
-                            if (i2 < W) pre = fmaf(w[e][i2], win[CONV_MAXW - W + i2][e], pre);
+                        for (int k = 0; k < CONV_MAXW; ++k) pre = fmaf(wr[e][k], win[k][e], pre);
                         o[e] = a.silu ? pre * sigmoid_f(pre) : pre;
                     }
                     lo_store8(a.y + (size_t)t * a.D + ch, o);
@@ -107,11 +113,13 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
         if (a.cache_out && t1 == seq_end) {      // the last W inputs of the sequence, newest last, zero-padded on the left
             float* c = a.cache_out + ((size_t)ci.seq * a.D + ch) * W;
 #pragma unroll
-            for (int i = 0; i < CONV_MAXW; ++i)
-                if (i < W) {
+            for (int k = 0; k < CONV_MAXW; ++k) {
+                const int tap = k - (CONV_MAXW - W);
+                if (tap >= 0) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) c[e * W + i] = win[CONV_MAXW - W + i][e];
+                    for (int e = 0; e < 8; ++e) c[e * W + tap] = win[k][e];
                 }
+            }
         }
     } else {
         // walk three tokens past the chunk (inside the sequence): dx[u] = sum_i w[i] dpre[u + (W-1) - i] needs them
@@ -156,15 +164,13 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
                 if (live) {
                     float pre = b[e];
 #pragma unroll
-                    for (int i = 0; i < CONV_MAXW; ++i)
-                        if (i < W) pre = fmaf(w[e][i], win[CONV_MAXW - W + i][e], pre);
+                    for (int k = 0; k < CONV_MAXW; ++k) pre = fmaf(wr[e][k], win[k][e], pre);
                     const float s = sigmoid_f(pre);
                     dp = a.silu ? dyv[e] * s * (1.f + pre * (1.f - s)) : dyv[e];
                     if (t < t1) {            // parameter gradients: each token counted once, by its own chunk
                         db_acc[e] += dp;
 #pragma unroll
-                        for (int i = 0; i < CONV_MAXW; ++i)
-                            if (i < W) dw_acc[e][i] = fmaf(dp, win[CONV_MAXW - W + i][e], dw_acc[e][i]);
+                        for (int k = 0; k < CONV_MAXW; ++k) dw_acc[e][k] = fmaf(dp, win[k][e], dw_acc[e][k]);     // by window slot
                     }
                 }
                 dwin[CONV_MAXW - 1][e] = dp;
@@ -187,8 +193,10 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
 #pragma unroll
-            for (int i = 0; i < CONV_MAXW; ++i)
-                if (i < W) atomicAdd(&a.dw[(size_t)(ch + e) * W + i], dw_acc[e][i]);
+            for (int k = 0; k < CONV_MAXW; ++k) {
+                const int tap = k - (CONV_MAXW - W);
+                if (tap >= 0) atomicAdd(&a.dw[(size_t)(ch + e) * W + tap], dw_acc[e][k]);
+            }
             if (a.dbias) atomicAdd(&a.dbias[ch + e], db_acc[e]);
         }
     }
