@@ -68,11 +68,16 @@ __global__ void __launch_bounds__(LO_THREADS) kda_short_conv_kernel(const ConvAr
     float w[8][CONV_MAXW], wr[8][CONV_MAXW], b[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
+        if (W == CONV_MAXW) {      // the usual width: one 16-byte load per channel, both alignments coincide
+            const float4 v = *reinterpret_cast<const float4*>(a.w + (size_t)(ch + e) * CONV_MAXW);
+            w[e][0] = wr[e][0] = v.x; w[e][1] = wr[e][1] = v.y; w[e][2] = wr[e][2] = v.z; w[e][3] = wr[e][3] = v.w;
+        } else {
 #pragma unroll
-        for (int i = 0; i < CONV_MAXW; ++i) {
-            w[e][i] = i < W ? a.w[(size_t)(ch + e) * W + i] : 0.f;
-            const int tap = i - (CONV_MAXW - W);
-            wr[e][i] = tap >= 0 ? a.w[(size_t)(ch + e) * W + tap] : 0.f;
+            for (int i = 0; i < CONV_MAXW; ++i) {
+                w[e][i] = i < W ? a.w[(size_t)(ch + e) * W + i] : 0.f;
+                const int tap = i - (CONV_MAXW - W);
+                wr[e][i] = tap >= 0 ? a.w[(size_t)(ch + e) * W + tap] : 0.f;
+            }
         }
         b[e] = a.bias ? a.bias[ch + e] : 0.f;
     }
